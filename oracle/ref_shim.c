@@ -1,0 +1,343 @@
+/*
+ * TEST INFRASTRUCTURE ONLY -- not part of the shipped library.
+ *
+ * Flat C entry points that drive the UNMODIFIED reference `quant` module of NART's art runtime
+ * through its own public op API (workspace_new_op / op_setting_*_set / op_config / op_prepare /
+ * op_run), one op per call, on plain host arrays in the reference's NCHW layout.  The reference
+ * sources are compiled where they lie by oracle/Makefile into oracle/_ref/libnart_ref.so together
+ * with this file; nothing of the reference is copied into this repository.
+ *
+ * The way the op API is driven follows the reference's own C example
+ * (examples/01-nart-case-cpu-example/src/main.c:25-74) and the settings each quant op reads in
+ * its config function (art/modules/quant/src/op/conv_2d.c:27-70, pool.c:58-86, eltwise.c:51-92,
+ * add.c:48-74, quantize.c:119-135, dequantize.c:84-101, ip.cpp:73-100).
+ *
+ * Constraints of the reference that this shim works around without changing results:
+ *   - conv_2d sizes its int32 scratch without the batch factor and aborts for batch > 1
+ *     (conv_2d_uint8_impl.c:32,104): images are run one at a time through one prepared op.
+ *   - without a bias input the x86 accumulator is never cleared (conv_2d_uint8_impl.c:114-124):
+ *     a zero bias is supplied when the caller passes NULL.
+ *   - only walpha[0] is read (conv_2d_uint8_impl.c:61): per-tensor weight scale only.
+ *   - im2col_i16 never writes the padding cells of its column buffer (every memset in
+ *     utils/im2col.cpp:487-855 is commented out) and the buffer comes from malloc, so the result
+ *     depends on what the heap held before: the scratch is cleared once after prepare, which is
+ *     the state a fresh process gives it.
+ */
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "art/module.h"
+#include "art/op.h"
+#include "art/op_settings.h"
+#include "art/op_tp.h"
+#include "art/quant/quant_module.h"
+#include "art/quant/quant_op_settings.h"
+#include "art/quant/quant_op_tp.h"
+#include "art/quant/quant_helper.h"
+/* the quant module's private op struct, for access to its im2col scratch */
+#include "src/op/conv_2d.h"
+
+#define REF_API __attribute__((visibility("default")))
+
+static workspace_t *g_ws = NULL;
+
+static workspace_t *ws(void)
+{
+    if (!g_ws)
+        g_ws = workspace_new(&quant_module_tp, NULL);
+    return g_ws;
+}
+
+static tensor_t *new_tensor(uint32_t dtype, int dim_size, const int *dims)
+{
+    tensor_t *t = tensor_new(cpu_mem_tp, dtype);
+    int i;
+    t->shape.dim_size = dim_size;
+    for (i = 0; i < dim_size; ++i)
+        t->shape.dim[i] = (uint32_t)dims[i];
+    if (dim_size == 1) {
+        t->shape.batch_axis = 0;
+        t->shape.channel_axis = -1;
+    } else {
+        t->shape.batch_axis = 0;
+        t->shape.channel_axis = 1;
+    }
+    tensor_alloc(t);
+    return t;
+}
+
+static void set_in_quant(op_t *op, int n, const float *alpha, const uint8_t *zp, const uint8_t *bits)
+{
+    CHECK(op_setting_array_set(op, SETTING_QUANT_IALPHA, dtFLOAT32, n, alpha));
+    CHECK(op_setting_array_set(op, SETTING_QUANT_IZERO_POINT, dtUINT8, n, zp));
+    CHECK(op_setting_array_set(op, SETTING_QUANT_IBITS, dtUINT8, n, bits));
+}
+
+static void set_out_quant(op_t *op, float alpha, uint8_t zp, uint8_t bits)
+{
+    CHECK(op_setting_array_set(op, SETTING_QUANT_OALPHA, dtFLOAT32, 1, &alpha));
+    CHECK(op_setting_array_set(op, SETTING_QUANT_OZERO_POINT, dtUINT8, 1, &zp));
+    CHECK(op_setting_array_set(op, SETTING_QUANT_OBITS, dtUINT8, 1, &bits));
+}
+
+static void set_w_quant(op_t *op, float alpha, uint8_t zp, uint8_t bits)
+{
+    CHECK(op_setting_array_set(op, SETTING_QUANT_WALPHA, dtFLOAT32, 1, &alpha));
+    CHECK(op_setting_array_set(op, SETTING_QUANT_WZERO_POINT, dtUINT8, 1, &zp));
+    CHECK(op_setting_array_set(op, SETTING_QUANT_WBITS, dtUINT8, 1, &bits));
+}
+
+/* The header's own scale decomposition, exported so tests can pin the restatement to it. */
+REF_API void ref_get_quant_scale(float x, int bits, uint32_t *mult, int8_t *shift)
+{
+    if (bits == 32) {
+        get_quant_scale_int32(x, mult, shift);
+    } else if (bits == -16) { /* the uint16 variant used by max-pool */
+        uint16_t m16 = 0;
+        get_quant_scale_int16(x, &m16, shift);
+        *mult = m16;
+    } else {
+        get_quant_scale(x, mult, shift, bits);
+    }
+}
+
+REF_API int64_t ref_rshift_rn(int64_t x, uint8_t bits) { return rshift_rn(x, bits); }
+
+/* conv_2d, uint8 path (art/modules/quant/src/op/conv_2d_uint8_impl.c:39-165). x: [n][c][h][w],
+ * wt: [k][c/group][r][s] uint8, bias: int32[k] or NULL, y: [n][k][oh][ow]. */
+REF_API int ref_conv2d_u8(
+    const uint8_t *x, int n, int c, int h, int w, const uint8_t *wt, const int32_t *bias, int k,
+    int r, int s, int pad_h, int pad_w, int stride_h, int stride_w, int group, float ialpha,
+    uint8_t izp, float walpha, uint8_t wzp, float oalpha, uint8_t ozp, uint8_t obits, uint8_t *y)
+{
+    int xd[4] = { 1, c, h, w }, wd[4] = { k, c / group, r, s }, bd[1] = { k };
+    tensor_t *tx = new_tensor(dtUINT8, 4, xd);
+    tensor_t *tw = new_tensor(dtUINT8, 4, wd);
+    tensor_t *tb = new_tensor(dtINT32, 1, bd);
+    tensor_t *in[3] = { tx, tw, tb };
+    float ia[3] = { ialpha, walpha, 1.f };
+    uint8_t iz[3] = { izp, wzp, 0 }, ib[3] = { 8, 8, 32 };
+    size_t xsz = (size_t)c * h * w, ysz;
+    int i;
+    op_t *op = workspace_new_op(ws(), OP_CONV_2D, 3, in);
+    if (!op)
+        return -1;
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_NUM_OUTPUT, dtUINT32, (uint32_t)k));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_KERNEL_H, dtUINT32, (uint32_t)r));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_KERNEL_W, dtUINT32, (uint32_t)s));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_PAD_H, dtUINT32, (uint32_t)pad_h));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_PAD_W, dtUINT32, (uint32_t)pad_w));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_STRIDE_H, dtUINT32, (uint32_t)stride_h));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_STRIDE_W, dtUINT32, (uint32_t)stride_w));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_GROUP, dtUINT32, (uint32_t)group));
+    set_in_quant(op, 3, ia, iz, ib);
+    set_w_quant(op, walpha, wzp, 8);
+    set_out_quant(op, oalpha, ozp, obits);
+    CHECK(op_config(op));
+    op_prepare(op);
+    {
+        op_conv_2d_t *conv_op = (op_conv_2d_t *)op;
+        memset(mem_cpu_data(conv_op->temp_data), 0, mem_sizeof(conv_op->temp_data));
+    }
+    memcpy(mem_cpu_data(tw->mem), wt, (size_t)k * (c / group) * r * s);
+    if (bias)
+        memcpy(mem_cpu_data(tb->mem), bias, sizeof(int32_t) * k);
+    else
+        memset(mem_cpu_data(tb->mem), 0, sizeof(int32_t) * k);
+    ysz = shape_count(&op->output_tensors[0].shape);
+    for (i = 0; i < n; ++i) {
+        memcpy(mem_cpu_data(tx->mem), x + xsz * i, xsz);
+        op_run(op);
+        memcpy(y + ysz * i, mem_cpu_data(op->output_tensors[0].mem), ysz);
+    }
+    op_delete(op);
+    tensor_delete(tx);
+    tensor_delete(tw);
+    tensor_delete(tb);
+    return 0;
+}
+
+/* ip (fully connected), uint8 path (art/modules/quant/src/op/ip.cpp:133-209).
+ * x: [n][chw], wt: [k][chw], y: [n][k]. */
+REF_API int ref_ip_u8(
+    const uint8_t *x, int n, int chw, const uint8_t *wt, const int32_t *bias, int k, float ialpha,
+    uint8_t izp, float walpha, uint8_t wzp, float oalpha, uint8_t ozp, uint8_t obits, uint8_t *y)
+{
+    int xd[4] = { n, chw, 1, 1 }, wd[4] = { k, chw, 1, 1 }, bd[1] = { k };
+    tensor_t *tx = new_tensor(dtUINT8, 4, xd);
+    tensor_t *tw = new_tensor(dtUINT8, 4, wd);
+    tensor_t *tb = new_tensor(dtINT32, 1, bd);
+    tensor_t *in[3] = { tx, tw, tb };
+    float ia[3] = { ialpha, walpha, 1.f };
+    uint8_t iz[3] = { izp, wzp, 0 }, ib[3] = { 8, 8, 32 };
+    op_t *op = workspace_new_op(ws(), OP_IP, 3, in);
+    if (!op)
+        return -1;
+    CHECK(op_setting_single_set(op, SETTING_IP_NUM_OUTPUT, dtUINT32, (uint32_t)k));
+    set_in_quant(op, 3, ia, iz, ib);
+    set_w_quant(op, walpha, wzp, 8);
+    set_out_quant(op, oalpha, ozp, obits);
+    CHECK(op_config(op));
+    op_prepare(op);
+    memcpy(mem_cpu_data(tx->mem), x, (size_t)n * chw);
+    memcpy(mem_cpu_data(tw->mem), wt, (size_t)k * chw);
+    if (bias)
+        memcpy(mem_cpu_data(tb->mem), bias, sizeof(int32_t) * k);
+    else
+        memset(mem_cpu_data(tb->mem), 0, sizeof(int32_t) * k);
+    op_run(op);
+    memcpy(y, mem_cpu_data(op->output_tensors[0].mem), (size_t)n * k);
+    op_delete(op);
+    tensor_delete(tx);
+    tensor_delete(tw);
+    tensor_delete(tb);
+    return 0;
+}
+
+/* eltwise SUM (eltwise.c:137-174) when use_add == 0, add (add.c:83-148) when use_add != 0.
+ * xs: n_in arrays of `count` bytes; the shape is passed as [1][count][1][1]. */
+REF_API int ref_eltwise_sum_u8(
+    const uint8_t *const *xs, int n_in, size_t count, const float *ialpha, const uint8_t *izp,
+    const float *coeff, float oalpha, uint8_t ozp, uint8_t obits, int use_add, uint8_t *y)
+{
+    int d[4] = { 1, (int)count, 1, 1 }, i;
+    tensor_t *in[8];
+    uint8_t ib[8];
+    op_t *op;
+    if (n_in > 8 || (use_add && n_in != 2))
+        return -1;
+    for (i = 0; i < n_in; ++i) {
+        in[i] = new_tensor(dtUINT8, 4, d);
+        memcpy(mem_cpu_data(in[i]->mem), xs[i], count);
+        ib[i] = 8;
+    }
+    op = workspace_new_op(ws(), use_add ? OP_ADD : OP_ELTWISE, n_in, in);
+    if (!op)
+        return -1;
+    if (!use_add) {
+        CHECK(op_setting_single_set(
+            op, SETTING_ELTWISE_OPERATION, dtUINT32, (uint32_t)SETTING_ELTWISE_OP_SUM));
+        if (coeff)
+            CHECK(op_setting_array_set(op, SETTING_ELTWISE_COEFF, dtFLOAT32, n_in, coeff));
+    }
+    set_in_quant(op, n_in, ialpha, izp, ib);
+    set_out_quant(op, oalpha, ozp, obits);
+    CHECK(op_config(op));
+    op_prepare(op);
+    op_run(op);
+    memcpy(y, mem_cpu_data(op->output_tensors[0].mem), count);
+    op_delete(op);
+    for (i = 0; i < n_in; ++i)
+        tensor_delete(in[i]);
+    return 0;
+}
+
+/* relu (relu.c:76-115). */
+REF_API int ref_relu_u8(
+    const uint8_t *x, size_t count, float ialpha, uint8_t izp, float oalpha, uint8_t ozp,
+    uint8_t obits, uint8_t *y)
+{
+    int d[4] = { 1, (int)count, 1, 1 };
+    tensor_t *tx = new_tensor(dtUINT8, 4, d);
+    tensor_t *in[1] = { tx };
+    uint8_t ib = 8;
+    op_t *op = workspace_new_op(ws(), OP_RELU, 1, in);
+    if (!op)
+        return -1;
+    memcpy(mem_cpu_data(tx->mem), x, count);
+    set_in_quant(op, 1, &ialpha, &izp, &ib);
+    set_out_quant(op, oalpha, ozp, obits);
+    CHECK(op_config(op));
+    op_prepare(op);
+    op_run(op);
+    memcpy(y, mem_cpu_data(op->output_tensors[0].mem), count);
+    op_delete(op);
+    tensor_delete(tx);
+    return 0;
+}
+
+/* pool, method 0 = MAX (pool.c:96-168), 1 = AVE (pool.c:170-249).  Output dims are written to
+ * out_hw[2] as the reference's own shape inference decides them (art/src/op.c:903-967); y must
+ * hold at least n*c*out_h*out_w bytes (call once with y == NULL to get the dims). */
+REF_API int ref_pool_u8(
+    const uint8_t *x, int n, int c, int h, int w, int method, int kernel_h, int kernel_w, int pad_h,
+    int pad_w, int stride_h, int stride_w, int ceil_mode, float ialpha, uint8_t izp, float oalpha,
+    uint8_t ozp, uint8_t obits, uint8_t *y, int *out_hw)
+{
+    int d[4] = { n, c, h, w };
+    tensor_t *tx = new_tensor(dtUINT8, 4, d);
+    tensor_t *in[1] = { tx };
+    uint8_t ib = 8;
+    op_t *op = workspace_new_op(ws(), OP_POOL, 1, in);
+    if (!op)
+        return -1;
+    CHECK(op_setting_single_set(op, SETTING_POOL_METHOD, dtUINT32, (uint32_t)method));
+    CHECK(op_setting_single_set(op, SETTING_POOL_KERNEL_H, dtUINT32, (uint32_t)kernel_h));
+    CHECK(op_setting_single_set(op, SETTING_POOL_KERNEL_W, dtUINT32, (uint32_t)kernel_w));
+    CHECK(op_setting_single_set(op, SETTING_POOL_PAD_H, dtUINT32, (uint32_t)pad_h));
+    CHECK(op_setting_single_set(op, SETTING_POOL_PAD_W, dtUINT32, (uint32_t)pad_w));
+    CHECK(op_setting_single_set(op, SETTING_POOL_STRIDE_H, dtUINT32, (uint32_t)stride_h));
+    CHECK(op_setting_single_set(op, SETTING_POOL_STRIDE_W, dtUINT32, (uint32_t)stride_w));
+    CHECK(op_setting_single_set(op, SETTING_POOL_CEIL_MODE, dtBOOL, (int)(ceil_mode != 0)));
+    set_in_quant(op, 1, &ialpha, &izp, &ib);
+    set_out_quant(op, oalpha, ozp, obits);
+    CHECK(op_config(op));
+    out_hw[0] = (int)op->output_tensors[0].shape.dim[2];
+    out_hw[1] = (int)op->output_tensors[0].shape.dim[3];
+    if (y) {
+        op_prepare(op);
+        memcpy(mem_cpu_data(tx->mem), x, (size_t)n * c * h * w);
+        op_run(op);
+        memcpy(
+            y, mem_cpu_data(op->output_tensors[0].mem),
+            shape_count(&op->output_tensors[0].shape));
+    }
+    op_delete(op);
+    tensor_delete(tx);
+    return 0;
+}
+
+/* quantize float32 -> uint8, qtype BIASED (quantize.c:145-157). */
+REF_API int ref_quantize_u8(
+    const float *x, size_t count, float oalpha, uint8_t ozp, uint8_t obits, uint8_t *y)
+{
+    int d[4] = { 1, (int)count, 1, 1 };
+    tensor_t *tx = new_tensor(dtFLOAT32, 4, d);
+    tensor_t *in[1] = { tx };
+    op_t *op = workspace_new_op(ws(), OP_QUANT_QUANTIZE, 1, in);
+    if (!op)
+        return -1;
+    memcpy(mem_cpu_data(tx->mem), x, count * sizeof(float));
+    set_out_quant(op, oalpha, ozp, obits);
+    CHECK(op_setting_single_set(op, SETTING_QUANT_QTYPE, dtINT32, (int32_t)SETTING_QUANT_BIASED));
+    CHECK(op_config(op));
+    op_prepare(op);
+    op_run(op);
+    memcpy(y, mem_cpu_data(op->output_tensors[0].mem), count);
+    op_delete(op);
+    tensor_delete(tx);
+    return 0;
+}
+
+/* dequantize uint8 -> float32 (dequantize.c:111-123). */
+REF_API int ref_dequantize_u8(const uint8_t *x, size_t count, float ialpha, uint8_t izp, float *y)
+{
+    int d[4] = { 1, (int)count, 1, 1 };
+    tensor_t *tx = new_tensor(dtUINT8, 4, d);
+    tensor_t *in[1] = { tx };
+    uint8_t ib = 8;
+    op_t *op = workspace_new_op(ws(), OP_QUANT_DEQUANTIZE, 1, in);
+    if (!op)
+        return -1;
+    memcpy(mem_cpu_data(tx->mem), x, count);
+    set_in_quant(op, 1, &ialpha, &izp, &ib);
+    CHECK(op_setting_single_set(op, SETTING_QUANT_QTYPE, dtINT32, (int32_t)SETTING_QUANT_BIASED));
+    CHECK(op_config(op));
+    op_prepare(op);
+    op_run(op);
+    memcpy(y, mem_cpu_data(op->output_tensors[0].mem), count * sizeof(float));
+    op_delete(op);
+    tensor_delete(tx);
+    return 0;
+}
