@@ -1,0 +1,476 @@
+// A prepared, runnable op list bound to one device -- what the reference calls a parade
+// (art/src/parade.c:169-197 of ModelTC/NART: parade_prepare, parade_run) -- assembled through
+// the C-ABI.  Tensors live on the device as NHWC uint8; the case inputs and outputs cross the
+// boundary in the reference's NCHW layout through staging buffers, with the layout change (and
+// quantize / dequantize where asked) done by device kernels.
+#include <string.h>
+
+#include <memory>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace b200;
+
+namespace {
+
+struct CaseTensor {
+    int c = 0, h = 0, w = 0;
+    int c_phys = 0;          // channels of the device NHWC buffer (>= c; the 3-channel image is padded to 4)
+    uint8_t *dev = nullptr;  // [max_batch][h][w][c_phys]
+    size_t bytes_per_image() const { return (size_t)h * w * c_phys; }
+};
+
+enum class OpKind { Conv, Eltwise, Relu, Pool };
+
+struct CaseOp {
+    OpKind kind;
+    std::vector<int> ins;
+    int out = -1;
+    // conv / ip
+    b200_conv_t *conv = nullptr;
+    // eltwise
+    std::vector<float> ialpha, coeff;
+    std::vector<uint8_t> izp;
+    bool has_coeff = false;
+    float oalpha = 1.f;
+    uint8_t ozp = 0, obits = 8;
+    int relu = 0;
+    // relu / max-pool lookup table
+    uint8_t lut[256];
+    uint8_t *lut_dev = nullptr;
+    // pool
+    int method = 0;
+    PoolGeom pg;
+    PoolAvgTab ptab;
+};
+
+struct CaseIO {
+    int tensor = -1;
+    bool is_f32 = false;
+    float alpha = 1.f;
+    uint8_t zp = 0, bits = 8;
+    void *staging = nullptr;   // device, host layout (NCHW), max_batch images
+    size_t bytes_per_image = 0;
+};
+
+}  // namespace
+
+struct b200_case {
+    std::vector<CaseTensor> tensors;
+    std::vector<CaseOp> ops;
+    std::vector<CaseIO> inputs, outputs;
+    int max_batch = 0;
+    bool prepared = false;
+    int device = 0;
+};
+
+namespace {
+
+int new_tensor(b200_case *cs, int c, int h, int w, int c_phys)
+{
+    CaseTensor t;
+    t.c = c; t.h = h; t.w = w; t.c_phys = c_phys;
+    cs->tensors.push_back(t);
+    return (int)cs->tensors.size() - 1;
+}
+
+int check_building(b200_case *cs, const char *what)
+{
+    if (!cs)
+        return fail(B200_ERR_INVALID, "%s: case is NULL", what);
+    if (cs->prepared)
+        return fail(B200_ERR_INVALID, "%s: the case is already prepared", what);
+    return B200_OK;
+}
+
+int check_tensor(const b200_case *cs, int id, const char *what)
+{
+    if (id < 0 || id >= (int)cs->tensors.size())
+        return fail(B200_ERR_INVALID, "%s: tensor id %d does not exist", what, id);
+    return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_case_create(b200_case_t **cs)
+{
+    if (!cs)
+        return fail(B200_ERR_INVALID, "case_create: NULL argument");
+    *cs = new b200_case();
+    cudaGetDevice(&(*cs)->device);
+    return B200_OK;
+}
+
+int b200_case_destroy(b200_case_t *cs)
+{
+    if (!cs)
+        return B200_OK;
+    for (auto &t : cs->tensors)
+        cudaFree(t.dev);
+    for (auto &op : cs->ops) {
+        if (op.conv)
+            b200_conv2d_destroy(op.conv);
+        cudaFree(op.lut_dev);
+    }
+    for (auto &io : cs->inputs)
+        cudaFree(io.staging);
+    for (auto &io : cs->outputs)
+        cudaFree(io.staging);
+    delete cs;
+    return B200_OK;
+}
+
+int b200_case_input_u8(b200_case_t *cs, int32_t c, int32_t h, int32_t w, int32_t *tensor)
+{
+    B200_TRY(check_building(cs, "case_input_u8"));
+    if (!tensor || c <= 0 || h <= 0 || w <= 0)
+        return fail(B200_ERR_INVALID, "case_input_u8: bad argument");
+    // few-channel images are padded to a multiple of 4 so that every pixel is word aligned
+    int c_phys = c % 4 == 0 ? c : (c + 3) / 4 * 4;
+    CaseIO io;
+    io.tensor = new_tensor(cs, c, h, w, c_phys);
+    io.is_f32 = false;
+    io.bytes_per_image = (size_t)c * h * w;
+    cs->inputs.push_back(io);
+    *tensor = io.tensor;
+    return B200_OK;
+}
+
+int b200_case_input_f32(
+    b200_case_t *cs, int32_t c, int32_t h, int32_t w, float oalpha, uint8_t ozp, uint8_t obits,
+    int32_t *tensor)
+{
+    B200_TRY(check_building(cs, "case_input_f32"));
+    if (!tensor || c <= 0 || h <= 0 || w <= 0 || obits < 1 || obits > 8 || !(oalpha > 0.f))
+        return fail(B200_ERR_INVALID, "case_input_f32: bad argument");
+    CaseIO io;
+    io.tensor = new_tensor(cs, c, h, w, c);
+    io.is_f32 = true;
+    io.alpha = oalpha; io.zp = ozp; io.bits = obits;
+    io.bytes_per_image = (size_t)c * h * w * sizeof(float);
+    cs->inputs.push_back(io);
+    *tensor = io.tensor;
+    return B200_OK;
+}
+
+int b200_case_conv2d(
+    b200_case_t *cs, int32_t in, const b200_conv_params *params, const uint8_t *weights,
+    const int32_t *bias, int32_t *out)
+{
+    B200_TRY(check_building(cs, "case_conv2d"));
+    B200_TRY(check_tensor(cs, in, "case_conv2d"));
+    if (!params || !weights || !out)
+        return fail(B200_ERR_INVALID, "case_conv2d: NULL argument");
+    const CaseTensor ti = cs->tensors[in];
+    if (params->c != ti.c || params->h != ti.h || params->w != ti.w)
+        return fail(
+            B200_ERR_INVALID, "case_conv2d: params %dx%dx%d do not match input tensor %dx%dx%d",
+            params->c, params->h, params->w, ti.c, ti.h, ti.w);
+    CaseOp op;
+    op.kind = OpKind::Conv;
+    op.ins = { in };
+    b200_conv_params p = *params;
+    std::vector<uint8_t> wpad;
+    const uint8_t *wsrc = weights;
+    if (ti.c_phys != ti.c) {
+        // the device buffer carries padding channels: give them zero weights (stored 128)
+        if (p.group != 1)
+            return fail(B200_ERR_UNSUPPORTED, "case_conv2d: grouped conv on a channel-padded input");
+        const size_t taps = (size_t)p.r * p.s;
+        wpad.assign((size_t)p.k * ti.c_phys * taps, 128);
+        for (int k = 0; k < p.k; ++k)
+            memcpy(&wpad[(size_t)k * ti.c_phys * taps], &weights[(size_t)k * ti.c * taps], (size_t)ti.c * taps);
+        p.c = ti.c_phys;
+        wsrc = wpad.data();
+    }
+    B200_TRY(b200_conv2d_create(&p, wsrc, bias, &op.conv));
+    int32_t oh, ow;
+    b200_conv2d_out_dims(op.conv, &oh, &ow);
+    op.out = new_tensor(cs, p.k, oh, ow, p.k);
+    *out = op.out;
+    cs->ops.push_back(op);
+    return B200_OK;
+}
+
+int b200_case_ip(
+    b200_case_t *cs, int32_t in, int32_t k, float ialpha, uint8_t izp, const float *walpha,
+    int32_t n_walpha, uint8_t wzp, float oalpha, uint8_t ozp, uint8_t obits,
+    const uint8_t *weights, const int32_t *bias, int32_t *out)
+{
+    B200_TRY(check_building(cs, "case_ip"));
+    B200_TRY(check_tensor(cs, in, "case_ip"));
+    if (!weights || !out)
+        return fail(B200_ERR_INVALID, "case_ip: NULL argument");
+    const CaseTensor ti = cs->tensors[in];
+    if (ti.c_phys != ti.c)
+        return fail(B200_ERR_UNSUPPORTED, "case_ip: channel-padded input");
+    CaseOp op;
+    op.kind = OpKind::Conv;
+    op.ins = { in };
+    B200_TRY(b200_ip_create(
+        ti.c, ti.h, ti.w, k, ialpha, izp, walpha, n_walpha, wzp, oalpha, ozp, obits, weights, bias, &op.conv));
+    op.out = new_tensor(cs, k, 1, 1, k);
+    *out = op.out;
+    cs->ops.push_back(op);
+    return B200_OK;
+}
+
+int b200_case_eltwise_sum(
+    b200_case_t *cs, const int32_t *ins, int32_t n_in, const float *ialpha, const uint8_t *izp,
+    const float *coeff, float oalpha, uint8_t ozp, uint8_t obits, int32_t relu, int32_t *out)
+{
+    B200_TRY(check_building(cs, "case_eltwise_sum"));
+    if (!ins || !ialpha || !izp || !out || n_in < 1 || n_in > 4)
+        return fail(B200_ERR_INVALID, "case_eltwise_sum: bad argument");
+    CaseOp op;
+    op.kind = OpKind::Eltwise;
+    for (int i = 0; i < n_in; ++i) {
+        B200_TRY(check_tensor(cs, ins[i], "case_eltwise_sum"));
+        const CaseTensor &a = cs->tensors[ins[0]], &b = cs->tensors[ins[i]];
+        if (a.c != b.c || a.h != b.h || a.w != b.w || a.c_phys != b.c_phys)
+            return fail(B200_ERR_INVALID, "case_eltwise_sum: input %d has a different shape", i);
+        op.ins.push_back(ins[i]);
+        op.ialpha.push_back(ialpha[i]);
+        op.izp.push_back(izp[i]);
+        op.coeff.push_back(coeff ? coeff[i] : 1.0f);
+    }
+    op.has_coeff = coeff != nullptr;
+    op.oalpha = oalpha; op.ozp = ozp; op.obits = obits; op.relu = relu;
+    const CaseTensor a = cs->tensors[ins[0]];
+    op.out = new_tensor(cs, a.c, a.h, a.w, a.c_phys);
+    *out = op.out;
+    cs->ops.push_back(op);
+    return B200_OK;
+}
+
+int b200_case_relu(
+    b200_case_t *cs, int32_t in, float ialpha, uint8_t izp, float oalpha, uint8_t ozp,
+    uint8_t obits, int32_t *out)
+{
+    B200_TRY(check_building(cs, "case_relu"));
+    B200_TRY(check_tensor(cs, in, "case_relu"));
+    if (!out)
+        return fail(B200_ERR_INVALID, "case_relu: NULL argument");
+    CaseOp op;
+    op.kind = OpKind::Relu;
+    op.ins = { in };
+    B200_TRY(relu_build_lut(ialpha, izp, oalpha, ozp, obits, op.lut));
+    const CaseTensor a = cs->tensors[in];
+    op.out = new_tensor(cs, a.c, a.h, a.w, a.c_phys);
+    *out = op.out;
+    cs->ops.push_back(op);
+    return B200_OK;
+}
+
+int b200_case_pool(
+    b200_case_t *cs, int32_t in, int32_t method, int32_t kernel_h, int32_t kernel_w, int32_t pad_h,
+    int32_t pad_w, int32_t stride_h, int32_t stride_w, int32_t ceil_mode, float ialpha,
+    uint8_t izp, float oalpha, uint8_t ozp, uint8_t obits, int32_t *out)
+{
+    B200_TRY(check_building(cs, "case_pool"));
+    B200_TRY(check_tensor(cs, in, "case_pool"));
+    if (!out)
+        return fail(B200_ERR_INVALID, "case_pool: NULL argument");
+    const CaseTensor a = cs->tensors[in];
+    CaseOp op;
+    op.kind = OpKind::Pool;
+    op.ins = { in };
+    op.method = method;
+    B200_TRY(pool_prepare(
+        a.h, a.w, method, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, ceil_mode, ialpha,
+        izp, oalpha, ozp, obits, &op.pg, op.lut, &op.ptab));
+    op.out = new_tensor(cs, a.c, op.pg.oh, op.pg.ow, a.c_phys);
+    *out = op.out;
+    cs->ops.push_back(op);
+    return B200_OK;
+}
+
+int b200_case_output_u8(b200_case_t *cs, int32_t tensor)
+{
+    B200_TRY(check_building(cs, "case_output_u8"));
+    B200_TRY(check_tensor(cs, tensor, "case_output_u8"));
+    const CaseTensor &t = cs->tensors[tensor];
+    CaseIO io;
+    io.tensor = tensor;
+    io.is_f32 = false;
+    io.bytes_per_image = (size_t)t.c * t.h * t.w;
+    cs->outputs.push_back(io);
+    return B200_OK;
+}
+
+int b200_case_output_f32(b200_case_t *cs, int32_t tensor, float ialpha, uint8_t izp)
+{
+    B200_TRY(check_building(cs, "case_output_f32"));
+    B200_TRY(check_tensor(cs, tensor, "case_output_f32"));
+    const CaseTensor &t = cs->tensors[tensor];
+    CaseIO io;
+    io.tensor = tensor;
+    io.is_f32 = true;
+    io.alpha = ialpha; io.zp = izp;
+    io.bytes_per_image = (size_t)t.c * t.h * t.w * sizeof(float);
+    cs->outputs.push_back(io);
+    return B200_OK;
+}
+
+int b200_case_prepare(b200_case_t *cs, int32_t max_batch)
+{
+    B200_TRY(check_building(cs, "case_prepare"));
+    if (max_batch <= 0)
+        return fail(B200_ERR_INVALID, "case_prepare: max_batch must be positive");
+    cs->max_batch = max_batch;
+    for (auto &t : cs->tensors) {
+        // 256 spare bytes: vector loads of the last pixel may read past a ragged channel count
+        size_t bytes = t.bytes_per_image() * max_batch + 256;
+        B200_TRY(b200_malloc((void **)&t.dev, bytes));
+        B200_CUDA_TRY(cudaMemset(t.dev, 0, bytes));
+    }
+    for (auto *ios : { &cs->inputs, &cs->outputs })
+        for (auto &io : *ios)
+            B200_TRY(b200_malloc(&io.staging, io.bytes_per_image * max_batch));
+    for (auto &op : cs->ops) {
+        if (op.kind == OpKind::Relu || (op.kind == OpKind::Pool && op.method == 0)) {
+            B200_TRY(b200_malloc((void **)&op.lut_dev, 256));
+            B200_CUDA_TRY(cudaMemcpy(op.lut_dev, op.lut, 256, cudaMemcpyHostToDevice));
+        }
+    }
+    cs->prepared = true;
+    return B200_OK;
+}
+
+int b200_case_tensor_dims(const b200_case_t *cs, int32_t tensor, int32_t *c, int32_t *h, int32_t *w)
+{
+    if (!cs || !c || !h || !w)
+        return fail(B200_ERR_INVALID, "case_tensor_dims: NULL argument");
+    B200_TRY(check_tensor(cs, tensor, "case_tensor_dims"));
+    *c = cs->tensors[tensor].c;
+    *h = cs->tensors[tensor].h;
+    *w = cs->tensors[tensor].w;
+    return B200_OK;
+}
+
+static const CaseIO *get_io(const b200_case_t *cs, int is_output, int index)
+{
+    const std::vector<CaseIO> &v = is_output ? cs->outputs : cs->inputs;
+    if (index < 0 || index >= (int)v.size())
+        return nullptr;
+    return &v[index];
+}
+
+int b200_case_io_bytes(const b200_case_t *cs, int32_t is_output, int32_t index, size_t *bytes_per_image)
+{
+    if (!cs || !bytes_per_image)
+        return fail(B200_ERR_INVALID, "case_io_bytes: NULL argument");
+    const CaseIO *io = get_io(cs, is_output, index);
+    if (!io)
+        return fail(B200_ERR_INVALID, "case_io_bytes: no such %s %d", is_output ? "output" : "input", index);
+    *bytes_per_image = io->bytes_per_image;
+    return B200_OK;
+}
+
+int b200_case_io_device_ptr(const b200_case_t *cs, int32_t is_output, int32_t index, void **dev_ptr)
+{
+    if (!cs || !dev_ptr)
+        return fail(B200_ERR_INVALID, "case_io_device_ptr: NULL argument");
+    const CaseIO *io = get_io(cs, is_output, index);
+    if (!io || !cs->prepared)
+        return fail(B200_ERR_INVALID, "case_io_device_ptr: no such buffer (is the case prepared?)");
+    *dev_ptr = io->staging;
+    return B200_OK;
+}
+
+int b200_case_tensor_device_ptr(const b200_case_t *cs, int32_t tensor, void **dev_ptr)
+{
+    if (!cs || !dev_ptr)
+        return fail(B200_ERR_INVALID, "case_tensor_device_ptr: NULL argument");
+    B200_TRY(check_tensor(cs, tensor, "case_tensor_device_ptr"));
+    *dev_ptr = cs->tensors[tensor].dev;
+    return B200_OK;
+}
+
+int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
+{
+    if (!cs || !cs->prepared)
+        return fail(B200_ERR_INVALID, "case_run: the case is not prepared");
+    if (batch < 0 || batch > cs->max_batch)
+        return fail(B200_ERR_INVALID, "case_run: batch %d outside 0..%d", batch, cs->max_batch);
+    if (batch == 0)
+        return B200_OK;
+    for (auto &io : cs->inputs) {
+        CaseTensor &t = cs->tensors[io.tensor];
+        if (io.is_f32)
+            B200_TRY(b200_quantize_u8(
+                (const float *)io.staging, t.dev, batch, t.c, t.h, t.w, io.alpha, io.zp, io.bits, 1, stream));
+        else
+            B200_TRY(b200_nchw_to_nhwc_u8(
+                (const uint8_t *)io.staging, t.dev, batch, t.c, t.h, t.w, t.c_phys, 0, stream));
+    }
+    for (auto &op : cs->ops) {
+        CaseTensor &to = cs->tensors[op.out];
+        const CaseTensor &ti = cs->tensors[op.ins[0]];
+        switch (op.kind) {
+        case OpKind::Conv:
+            B200_TRY(b200_conv2d_run(op.conv, ti.dev, batch, to.dev, stream));
+            break;
+        case OpKind::Eltwise: {
+            const uint8_t *xs[4];
+            for (size_t i = 0; i < op.ins.size(); ++i)
+                xs[i] = cs->tensors[op.ins[i]].dev;
+            B200_TRY(b200_eltwise_sum_u8(
+                xs, (int)op.ins.size(), to.bytes_per_image() * batch, op.ialpha.data(), op.izp.data(),
+                op.has_coeff ? op.coeff.data() : nullptr, op.oalpha, op.ozp, op.obits, op.relu, to.dev, stream));
+            break;
+        }
+        case OpKind::Relu:
+            B200_TRY(lut_u8_launch(ti.dev, to.dev, to.bytes_per_image() * batch, op.lut_dev, as_stream(stream)));
+            break;
+        case OpKind::Pool:
+            B200_TRY(pool_launch(ti.dev, to.dev, batch, ti.c_phys, op.method, op.pg, op.lut_dev, op.ptab, as_stream(stream)));
+            break;
+        }
+    }
+    for (auto &io : cs->outputs) {
+        const CaseTensor &t = cs->tensors[io.tensor];
+        if (io.is_f32)
+            B200_TRY(b200_dequantize_u8(t.dev, (float *)io.staging, batch, t.c, t.h, t.w, io.alpha, io.zp, 1, stream));
+        else
+            B200_TRY(b200_nhwc_to_nchw_u8(t.dev, (uint8_t *)io.staging, batch, t.c, t.h, t.w, t.c_phys, stream));
+    }
+    return B200_OK;
+}
+
+int b200_case_run_host(
+    b200_case_t *cs, int32_t batch, const void *const *inputs, void *const *outputs,
+    b200_stream_t stream)
+{
+    if (!cs || !cs->prepared)
+        return fail(B200_ERR_INVALID, "case_run_host: the case is not prepared");
+    if (!inputs || !outputs)
+        return fail(B200_ERR_INVALID, "case_run_host: NULL argument");
+    if (batch < 0 || batch > cs->max_batch)
+        return fail(B200_ERR_INVALID, "case_run_host: batch %d outside 0..%d", batch, cs->max_batch);
+    for (size_t i = 0; i < cs->inputs.size(); ++i)
+        B200_TRY(b200_memcpy_h2d(cs->inputs[i].staging, inputs[i], cs->inputs[i].bytes_per_image * batch, stream));
+    B200_TRY(b200_case_run_device(cs, batch, stream));
+    for (size_t i = 0; i < cs->outputs.size(); ++i)
+        B200_TRY(b200_memcpy_d2h(outputs[i], cs->outputs[i].staging, cs->outputs[i].bytes_per_image * batch, stream));
+    B200_TRY(b200_stream_synchronize(stream));
+    int word = 0;
+    B200_TRY(b200_device_status(stream, &word));
+    if (word != 0)
+        return fail(B200_ERR_DEVICE_WAIT, "case_run_host: a device-side wait ran out (code 0x%x)", word);
+    return B200_OK;
+}
+
+int b200_case_launch_count(const b200_case_t *cs, int32_t *launches)
+{
+    if (!cs || !launches)
+        return fail(B200_ERR_INVALID, "case_launch_count: NULL argument");
+    *launches = (int)(cs->inputs.size() + cs->ops.size() + cs->outputs.size());
+    return B200_OK;
+}
+
+}  // extern "C"

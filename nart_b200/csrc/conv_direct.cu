@@ -1,0 +1,231 @@
+// CUDA-core convolution kernels (dp4a) for the shapes that are not dense contractions: grouped and
+// depthwise convs, tiny channel counts (the 3-channel stem), and any shape the tensor-core path
+// declines.  Arithmetic follows op_conv_2d_u8xu8_run of the reference CPU module
+// (art/modules/quant/src/op/conv_2d_uint8_impl.c:39-165 of ModelTC/NART):
+//   acc = bias[k] + sum (x - izp) * (w - wzp),  taps outside the image contribute 0,
+//   y   = sat_u(rshift_rn(acc * mult_k, shift_k) + ozp, obits).
+// The kernels multiply the raw uint8 activation by the signed weight (dp4a.u32.s32) and read an
+// out-of-image tap as the byte `izp`; with bias_fold[k] = bias[k] - izp * sum(w[k]) this gives the
+// same int32 accumulator.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace b200 {
+
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
+{
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Generic tiled kernel.  Block = 256 threads = 32 output pixels x 8 quads of output channels
+// (32 channels of one group).  The reduction runs over "items" = 4-channel words of
+// [r][s][cg4]; the weights of the block's 32 channels are staged through shared memory in
+// chunks of 64 items as [item][channel] so that a quad reads one 16-byte vector per item.
+// ---------------------------------------------------------------------------------------------
+constexpr int DK = 32;       // output channels per block
+constexpr int DP = 32;       // output pixels per block
+constexpr int DCHUNK = 64;   // items per shared-memory stage
+
+template <bool WORD_LOADS>
+__global__ void __launch_bounds__(256) conv_direct_kernel(
+    ConvGeom g, int cg4, const uint8_t *__restrict__ x, const uint32_t *__restrict__ wq,
+    const int32_t *__restrict__ bias_fold, const uint32_t *__restrict__ mult,
+    const int32_t *__restrict__ shift, uint8_t *__restrict__ y, int32_t *__restrict__ acc_out, int n)
+{
+    __shared__ __align__(16) uint32_t wsm[DCHUNK][DK];
+    const int tid = threadIdx.x;
+    const int kq = tid & 7;
+    const int pl = tid >> 3;
+    const int kg = g.k / g.group, cg = g.c / g.group;
+    const int ktiles = (kg + DK - 1) / DK;
+    const int grp = blockIdx.y / ktiles;
+    const int kt = blockIdx.y % ktiles;
+    const int k_in_g0 = kt * DK;               // first channel of the tile inside the group
+    const int kvalid = min(DK, kg - k_in_g0);  // channels of this tile that exist
+    const int k0 = grp * kg + k_in_g0;
+    const size_t npix = (size_t)n * g.oh * g.ow;
+    const size_t pix = (size_t)blockIdx.x * DP + pl;
+    const bool pvalid = pix < npix;
+    int ox = 0, oy = 0, img = 0;
+    if (pvalid) {
+        ox = (int)(pix % g.ow);
+        oy = (int)((pix / g.ow) % g.oh);
+        img = (int)(pix / ((size_t)g.ow * g.oh));
+    }
+    const int iy0 = oy * g.stride_h - g.pad_h, ix0 = ox * g.stride_w - g.pad_w;
+    const int cwords = cg4 / 4;
+    const int items = g.r * g.s * cwords;
+    const uint32_t izp4 = (uint32_t)g.izp * 0x01010101u;
+    const uint8_t *ximg = x + (size_t)img * g.h * g.w * g.c + (size_t)grp * cg;
+
+    int acc[4] = { 0, 0, 0, 0 };
+    for (int item0 = 0; item0 < items; item0 += DCHUNK) {
+        const int nitem = min(DCHUNK, items - item0);
+        __syncthreads();
+        for (int i = tid; i < DCHUNK * DK; i += 256) {
+            int it = i / DK, kl = i % DK;
+            uint32_t v = 0;
+            if (it < nitem && kl < kvalid)
+                v = __ldg(wq + (size_t)(k0 + kl) * items + item0 + it);
+            wsm[it][kl] = v;
+        }
+        __syncthreads();
+        if (pvalid) {
+            int tap = item0 / cwords, cw = item0 % cwords;
+            for (int it = 0; it < nitem; ++it) {
+                int rr = tap / g.s, ss = tap % g.s;
+                int iy = iy0 + rr, ix = ix0 + ss;
+                uint32_t xv = izp4;
+                if (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w) {
+                    const uint8_t *px = ximg + ((size_t)iy * g.w + ix) * g.c + cw * 4;
+                    if (WORD_LOADS) {
+                        xv = __ldg(reinterpret_cast<const uint32_t *>(px));
+                    } else {
+                        xv = 0;
+#pragma unroll
+                        for (int b = 0; b < 4; ++b)
+                            if (cw * 4 + b < cg)
+                                xv |= (uint32_t)__ldg(px + b) << (8 * b);
+                    }
+                }
+                uint4 wv = *reinterpret_cast<const uint4 *>(&wsm[it][kq * 4]);
+                acc[0] = dp4a_us(xv, wv.x, acc[0]);
+                acc[1] = dp4a_us(xv, wv.y, acc[1]);
+                acc[2] = dp4a_us(xv, wv.z, acc[2]);
+                acc[3] = dp4a_us(xv, wv.w, acc[3]);
+                if (++cw == cwords) {
+                    cw = 0;
+                    ++tap;
+                }
+            }
+        }
+    }
+    if (!pvalid)
+        return;
+    int q[4] = { 0, 0, 0, 0 };
+    int nk = min(4, kvalid - kq * 4);
+    for (int j = 0; j < 4; ++j) {
+        if (j >= nk)
+            break;
+        int k = k0 + kq * 4 + j;
+        int a = acc[j] + bias_fold[k];
+        if (acc_out)
+            acc_out[pix * g.k + k] = a;
+        q[j] = sat_relu(requant_raw(a, mult[k], shift[k], g.ozp), g.qmax, g.relu_lo);
+    }
+    uint8_t *py = y + pix * g.k + k0 + kq * 4;
+    if (nk == 4 && (((size_t)g.k | (size_t)k0) & 3) == 0) {
+        *reinterpret_cast<uint32_t *>(py) = pack4(q[0], q[1], q[2], q[3]);
+    } else {
+        for (int j = 0; j < nk; ++j)
+            py[j] = (uint8_t)q[j];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Depthwise kernel (group == c == k, c % 16 == 0).  A thread owns 16 consecutive channels of one
+// output pixel: one 16-byte activation vector and one 16-byte weight vector per tap, products
+// formed per channel.  Weights are [r][s][c] int8.  HBM-bound: each activation byte is read once
+// from DRAM (neighbouring taps hit L1/L2), each output byte written once.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) conv_depthwise_kernel(
+    ConvGeom g, const uint8_t *__restrict__ x, const int8_t *__restrict__ w_rsc,
+    const int32_t *__restrict__ bias_fold, const uint32_t *__restrict__ mult,
+    const int32_t *__restrict__ shift, uint8_t *__restrict__ y, int n)
+{
+    const int cv = g.c / 16;
+    const size_t total = (size_t)n * g.oh * g.ow * cv;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int ci = (int)(idx % cv);
+        const size_t pix = idx / cv;
+        const int ox = (int)(pix % g.ow);
+        const int oy = (int)((pix / g.ow) % g.oh);
+        const int img = (int)(pix / ((size_t)g.ow * g.oh));
+        const int iy0 = oy * g.stride_h - g.pad_h, ix0 = ox * g.stride_w - g.pad_w;
+        int acc[16];
+        {
+            const int4 *b4 = reinterpret_cast<const int4 *>(bias_fold + ci * 16);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int4 b = __ldg(b4 + j);
+                acc[4 * j] = b.x; acc[4 * j + 1] = b.y; acc[4 * j + 2] = b.z; acc[4 * j + 3] = b.w;
+            }
+        }
+        for (int rr = 0; rr < g.r; ++rr) {
+            const int iy = iy0 + rr;
+            for (int ss = 0; ss < g.s; ++ss) {
+                const int ix = ix0 + ss;
+                uint4 wv = __ldg(reinterpret_cast<const uint4 *>(w_rsc + ((size_t)(rr * g.s + ss) * g.c) + ci * 16));
+                uint4 xv;
+                if (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w) {
+                    xv = __ldg(reinterpret_cast<const uint4 *>(
+                        x + (((size_t)img * g.h + iy) * g.w + ix) * g.c + ci * 16));
+                } else {
+                    uint32_t z = (uint32_t)g.izp * 0x01010101u;
+                    xv = make_uint4(z, z, z, z);
+                }
+                const uint32_t xw[4] = { xv.x, xv.y, xv.z, xv.w };
+                const uint32_t ww[4] = { wv.x, wv.y, wv.z, wv.w };
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    int xb = (int)((xw[j / 4] >> (8 * (j % 4))) & 0xff);
+                    int wb = (int)(int8_t)((ww[j / 4] >> (8 * (j % 4))) & 0xff);
+                    acc[j] += xb * wb;
+                }
+            }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) {
+            int q[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                int k = ci * 16 + wd * 4 + e;
+                q[e] = sat_relu(requant_raw(acc[wd * 4 + e], __ldg(mult + k), __ldg(shift + k), g.ozp), g.qmax, g.relu_lo);
+            }
+            o[wd] = pack4(q[0], q[1], q[2], q[3]);
+        }
+        *reinterpret_cast<uint4 *>(y + pix * g.k + ci * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+int conv_direct_launch(
+    const ConvGeom &g, const ConvDirectPlan &p, const uint8_t *x, int n, uint8_t *y, int32_t *acc_out,
+    cudaStream_t st)
+{
+    if (n == 0)
+        return B200_OK;
+    const size_t npix = (size_t)n * g.oh * g.ow;
+    const int kg = g.k / g.group, cg = g.c / g.group;
+    const bool depthwise = p.w_dw_dev && !acc_out && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
+    if (depthwise) {
+        size_t total = npix * (g.c / 16);
+        size_t blocks = (total + 255) / 256;
+        size_t cap = (size_t)sm_count() * 8;
+        int grid = (int)(blocks < cap ? blocks : cap);
+        conv_depthwise_kernel<<<grid, 256, 0, st>>>(
+            g, x, p.w_dw_dev, p.bias_fold_dev, p.mult_dev, p.shift_dev, y, n);
+    } else {
+        const int ktiles = (kg + DK - 1) / DK;
+        size_t gx = (npix + DP - 1) / DP;
+        if (gx > 0x7fffffffull || (size_t)g.group * ktiles > 65535)
+            return fail(B200_ERR_UNSUPPORTED, "conv(direct): grid too large");
+        dim3 grid((unsigned)gx, (unsigned)(g.group * ktiles));
+        const bool word = (g.c % 4 == 0) && (cg % 4 == 0) && (((uintptr_t)x & 3) == 0);
+        const uint32_t *wq = reinterpret_cast<const uint32_t *>(p.w_dev);
+        if (word)
+            conv_direct_kernel<true><<<grid, 256, 0, st>>>(
+                g, p.cg4, x, wq, p.bias_fold_dev, p.mult_dev, p.shift_dev, y, acc_out, n);
+        else
+            conv_direct_kernel<false><<<grid, 256, 0, st>>>(
+                g, p.cg4, x, wq, p.bias_fold_dev, p.mult_dev, p.shift_dev, y, acc_out, n);
+    }
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+}  // namespace b200

@@ -1,0 +1,223 @@
+// conv_2d / ip plans: the one-time work the reference does (or repeats) in prepare and run --
+// zero-point subtraction of the weights, scale decomposition, bias preload
+// (art/modules/quant/src/op/conv_2d.c:95-147, conv_2d_uint8_impl.c:61-124 of ModelTC/NART) --
+// done once here: weights repacked for the kernels, per-channel (mult, shift) tables, folded
+// bias.  b200_conv2d_run then only launches.
+#include <string.h>
+
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+struct b200_conv {
+    b200::ConvGeom g;
+    int algo = B200_CONV_ALGO_DIRECT;
+    int device = 0;
+    b200::ConvDirectPlan direct;
+    b200::ConvIgemmPlan *igemm = nullptr;
+};
+
+using namespace b200;
+
+namespace {
+
+template <typename T>
+int upload(const std::vector<T> &v, T **dev)
+{
+    *dev = nullptr;
+    if (v.empty())
+        return B200_OK;
+    B200_CUDA_TRY(cudaMalloc((void **)dev, v.size() * sizeof(T)));
+    B200_CUDA_TRY(cudaMemcpy(*dev, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
+    return B200_OK;
+}
+
+void destroy_conv(b200_conv *cv)
+{
+    if (!cv)
+        return;
+    cudaFree(cv->direct.w_dev);
+    cudaFree(cv->direct.w_dw_dev);
+    cudaFree(cv->direct.bias_fold_dev);
+    cudaFree(cv->direct.mult_dev);
+    cudaFree(cv->direct.shift_dev);
+    if (cv->igemm)
+        conv_igemm_destroy(cv->igemm);
+    delete cv;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_conv2d_create(
+    const b200_conv_params *p, const uint8_t *weights, const int32_t *bias, b200_conv_t **out)
+{
+    if (!p || !weights || !out)
+        return fail(B200_ERR_INVALID, "conv: NULL argument");
+    *out = nullptr;
+    if (p->c <= 0 || p->h <= 0 || p->w <= 0 || p->k <= 0 || p->r <= 0 || p->s <= 0 || p->group <= 0
+        || p->stride_h <= 0 || p->stride_w <= 0 || p->pad_h < 0 || p->pad_w < 0)
+        return fail(B200_ERR_INVALID, "conv: non-positive dimension");
+    if (p->c % p->group || p->k % p->group)
+        return fail(B200_ERR_INVALID, "conv: c=%d and k=%d must be multiples of group=%d", p->c, p->k, p->group);
+    if (p->h + 2 * p->pad_h < p->r || p->w + 2 * p->pad_w < p->s)
+        return fail(B200_ERR_INVALID, "conv: kernel larger than the padded input");
+    if (p->obits < 1 || p->obits > 8)
+        return fail(B200_ERR_INVALID, "conv: obits=%d outside 1..8", (int)p->obits);
+    if (!p->walpha || (p->n_walpha != 1 && p->n_walpha != p->k))
+        return fail(B200_ERR_INVALID, "conv: n_walpha must be 1 or k");
+    if (p->wzp != 128)
+        return fail(
+            B200_ERR_UNSUPPORTED,
+            "conv: wzp=%d; only int8 weights stored as value+128 with wzp=128 are built", (int)p->wzp);
+    if (!(p->ialpha > 0.f) || !(p->oalpha > 0.f))
+        return fail(B200_ERR_INVALID, "conv: ialpha and oalpha must be positive");
+    if (p->algo != B200_CONV_ALGO_AUTO && p->algo != B200_CONV_ALGO_DIRECT && p->algo != B200_CONV_ALGO_IGEMM)
+        return fail(B200_ERR_INVALID, "conv: unknown algo %d", p->algo);
+
+    b200_conv *cv = new b200_conv();
+    ConvGeom &g = cv->g;
+    g.c = p->c; g.h = p->h; g.w = p->w; g.k = p->k; g.r = p->r; g.s = p->s;
+    g.pad_h = p->pad_h; g.pad_w = p->pad_w; g.stride_h = p->stride_h; g.stride_w = p->stride_w;
+    g.group = p->group;
+    g.oh = (p->h + 2 * p->pad_h - p->r) / p->stride_h + 1;   // art/src/op.c:547-555
+    g.ow = (p->w + 2 * p->pad_w - p->s) / p->stride_w + 1;
+    g.izp = p->izp; g.ozp = p->ozp; g.qmax = (1 << p->obits) - 1;
+    g.relu_lo = p->relu ? p->ozp : 0;
+    cudaGetDevice(&cv->device);
+
+    const int cg = g.c / g.group, taps = g.r * g.s;
+    const size_t wcount = (size_t)g.k * cg * taps;
+    // int32 accumulation wraps modulo 2^32 in every order, like the reference's int32 GEMM
+    // (gemm/default/gemm.c:306-355), so no bound on the reduction length is needed.
+    std::vector<int8_t> w_s8(wcount);   // [k][cg][r][s], value = stored - 128
+    for (size_t i = 0; i < wcount; ++i)
+        w_s8[i] = (int8_t)((int)weights[i] - 128);
+
+    std::vector<uint32_t> mult(g.k);
+    std::vector<int32_t> shift(g.k);
+    for (int k = 0; k < g.k; ++k) {
+        float wa = p->walpha[p->n_walpha == 1 ? 0 : k];
+        if (!(wa > 0.f)) {
+            destroy_conv(cv);
+            return fail(B200_ERR_INVALID, "conv: walpha[%d] must be positive", k);
+        }
+        float scale = p->ialpha * wa / p->oalpha;   // conv_2d_uint8_impl.c:75, fp32, left to right
+        uint32_t m;
+        int8_t s;
+        get_quant_scale(scale, 32, &m, &s);
+        if (m == 0 || s < 1 || s > 62) {
+            destroy_conv(cv);
+            return fail(
+                B200_ERR_UNSUPPORTED, "conv: scale %g of channel %d gives shift %d outside 1..62", (double)scale, k, (int)s);
+        }
+        mult[k] = m;
+        shift[k] = s;
+    }
+
+    // ---- direct-kernel tables (always built: the accumulator-dumping entry uses them) --------
+    const int cg4 = (cg + 3) / 4 * 4;
+    std::vector<int8_t> w_pack((size_t)g.k * taps * cg4, 0);
+    std::vector<int32_t> bias_fold(g.k);
+    for (int k = 0; k < g.k; ++k) {
+        long long wsum = 0;
+        for (int c = 0; c < cg; ++c)
+            for (int t = 0; t < taps; ++t) {
+                int8_t v = w_s8[((size_t)k * cg + c) * taps + t];
+                w_pack[((size_t)k * taps + t) * cg4 + c] = v;
+                wsum += v;
+            }
+        long long bf = (long long)(bias ? bias[k] : 0) - (long long)g.izp * wsum;
+        bias_fold[k] = (int32_t)(uint32_t)(unsigned long long)bf;   // modulo 2^32
+    }
+    cv->direct.cg4 = cg4;
+    int rc = upload(w_pack, &cv->direct.w_dev);
+    if (rc == B200_OK) rc = upload(bias_fold, &cv->direct.bias_fold_dev);
+    if (rc == B200_OK) rc = upload(mult, &cv->direct.mult_dev);
+    if (rc == B200_OK) rc = upload(shift, &cv->direct.shift_dev);
+    if (rc == B200_OK && g.group == g.c && g.group == g.k && g.c % 16 == 0) {
+        std::vector<int8_t> w_dw((size_t)taps * g.c);
+        for (int c = 0; c < g.c; ++c)
+            for (int t = 0; t < taps; ++t)
+                w_dw[(size_t)t * g.c + c] = w_s8[(size_t)c * taps + t];
+        rc = upload(w_dw, &cv->direct.w_dw_dev);
+    }
+    if (rc != B200_OK) {
+        destroy_conv(cv);
+        return rc;
+    }
+
+    // ---- tensor-core plan ---------------------------------------------------------------------
+    char why[256] = "";
+    const bool ig_ok = conv_igemm_supported(g, why, sizeof(why)) != 0;
+    if (p->algo == B200_CONV_ALGO_IGEMM && !ig_ok) {
+        destroy_conv(cv);
+        return fail(B200_ERR_UNSUPPORTED, "conv: implicit-GEMM path declined: %s", why);
+    }
+    if (ig_ok && p->algo != B200_CONV_ALGO_DIRECT) {
+        rc = conv_igemm_create(g, w_s8, bias, mult.data(), shift.data(), &cv->igemm);
+        if (rc != B200_OK) {
+            destroy_conv(cv);
+            return rc;
+        }
+        cv->algo = B200_CONV_ALGO_IGEMM;
+    }
+    *out = cv;
+    return B200_OK;
+}
+
+int b200_ip_create(
+    int32_t c, int32_t h, int32_t w, int32_t k, float ialpha, uint8_t izp, const float *walpha,
+    int32_t n_walpha, uint8_t wzp, float oalpha, uint8_t ozp, uint8_t obits,
+    const uint8_t *weights, const int32_t *bias, b200_conv_t **conv)
+{
+    // ip.cpp:133-209: y[n][k] = requant(bias[k] + sum_j (x[n][j] - izp) * (w[k][j] - wzp)) over the
+    // flattened c*h*w input -- a convolution whose kernel is the whole image.
+    b200_conv_params p;
+    memset(&p, 0, sizeof(p));
+    p.c = c; p.h = h; p.w = w; p.k = k; p.r = h; p.s = w;
+    p.pad_h = p.pad_w = 0; p.stride_h = p.stride_w = 1; p.group = 1;
+    p.ialpha = ialpha; p.izp = izp; p.wzp = wzp; p.ozp = ozp; p.obits = obits; p.oalpha = oalpha;
+    p.walpha = walpha; p.n_walpha = n_walpha; p.relu = 0; p.algo = B200_CONV_ALGO_AUTO;
+    return b200_conv2d_create(&p, weights, bias, conv);
+}
+
+int b200_conv2d_out_dims(const b200_conv_t *conv, int32_t *oh, int32_t *ow)
+{
+    if (!conv || !oh || !ow)
+        return fail(B200_ERR_INVALID, "conv: NULL argument");
+    *oh = conv->g.oh;
+    *ow = conv->g.ow;
+    return B200_OK;
+}
+
+int b200_conv2d_algo(const b200_conv_t *conv) { return conv ? conv->algo : B200_ERR_INVALID; }
+
+int b200_conv2d_run(b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, b200_stream_t stream)
+{
+    if (!conv || n < 0 || (n > 0 && (!x || !y)))
+        return fail(B200_ERR_INVALID, "conv: bad argument");
+    if (n == 0)
+        return B200_OK;
+    if (conv->algo == B200_CONV_ALGO_IGEMM)
+        return conv_igemm_launch(conv->igemm, x, n, y, as_stream(stream));
+    return conv_direct_launch(conv->g, conv->direct, x, n, y, nullptr, as_stream(stream));
+}
+
+int b200_conv2d_run_acc(
+    b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, int32_t *acc, b200_stream_t stream)
+{
+    if (!conv || !x || !y || !acc || n < 0)
+        return fail(B200_ERR_INVALID, "conv: bad argument");
+    return conv_direct_launch(conv->g, conv->direct, x, n, y, acc, as_stream(stream));
+}
+
+int b200_conv2d_destroy(b200_conv_t *conv)
+{
+    destroy_conv(conv);
+    return B200_OK;
+}
+
+}  // extern "C"

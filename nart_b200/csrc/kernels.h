@@ -1,0 +1,72 @@
+// Internal interfaces between the translation units of libnart_b200: prepared descriptors and
+// launchers that the flat C-ABI calls and the case runner share.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <vector>
+
+#include "nart_b200.h"
+
+namespace b200 {
+
+// ---- pool -----------------------------------------------------------------------------------
+struct PoolGeom {
+    int n, c, h, w, oh, ow;
+    int kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w;
+    int izp, ozp, qmax;
+};
+struct PoolAvgTab {
+    static constexpr int kMax = 4;
+    int mult[kMax][kMax];
+    int shift[kMax][kMax];
+};
+int pool_prepare(
+    int h, int w, int method, int kernel_h, int kernel_w, int pad_h, int pad_w, int stride_h,
+    int stride_w, int ceil_mode, float ialpha, uint8_t izp, float oalpha, uint8_t ozp,
+    uint8_t obits, PoolGeom *g, uint8_t lut[256], PoolAvgTab *tab);
+int pool_launch(
+    const uint8_t *x, uint8_t *y, int n, int c, int method, const PoolGeom &g, const uint8_t *lut_dev,
+    const PoolAvgTab &tab, cudaStream_t st);
+
+// ---- relu -----------------------------------------------------------------------------------
+int relu_build_lut(
+    float ialpha, uint8_t izp, float oalpha, uint8_t ozp, uint8_t obits, uint8_t lut[256]);
+int lut_u8_launch(const uint8_t *x, uint8_t *y, size_t count, const uint8_t *lut_dev, cudaStream_t st);
+
+// ---- conv -----------------------------------------------------------------------------------
+// Geometry and quantization of one prepared convolution, shared by both kernels.
+struct ConvGeom {
+    int c, h, w, k, r, s;
+    int pad_h, pad_w, stride_h, stride_w, group;
+    int oh, ow;
+    int izp, ozp, qmax, relu_lo;
+};
+
+// Direct (CUDA-core) convolution: weights [k][r][s][cg4] int8 (cg4 = c/group rounded up to 4,
+// zero filled), bias_fold[k] = bias[k] - izp * sum(w[k]) so that out-of-image taps, read as izp,
+// contribute nothing.
+struct ConvDirectPlan {
+    int8_t *w_dev = nullptr;
+    int8_t *w_dw_dev = nullptr;   // depthwise only: [r][s][c] int8
+    int32_t *bias_fold_dev = nullptr;
+    uint32_t *mult_dev = nullptr;
+    int32_t *shift_dev = nullptr;
+    int cg4 = 0;
+};
+int conv_direct_launch(
+    const ConvGeom &g, const ConvDirectPlan &p, const uint8_t *x, int n, uint8_t *y, int32_t *acc_out,
+    cudaStream_t st);
+
+// Implicit-GEMM (tcgen05) convolution plan; defined in conv_igemm_sm100.cu.
+struct ConvIgemmPlan;
+int conv_igemm_supported(const ConvGeom &g, char *why, size_t why_len);
+int conv_igemm_create(
+    const ConvGeom &g, const std::vector<int8_t> &w_s8 /* [k][c][r][s] */, const int32_t *bias,
+    const uint32_t *mult, const int32_t *shift, ConvIgemmPlan **plan);
+int conv_igemm_launch(ConvIgemmPlan *plan, const uint8_t *x, int n, uint8_t *y, cudaStream_t st);
+void conv_igemm_destroy(ConvIgemmPlan *plan);
+
+}  // namespace b200

@@ -1,0 +1,216 @@
+"""GPU parity, through the C-ABI: every op of the path against the CPU restatement (oracle/port.c)
+and the reference-produced fixtures, bit for bit."""
+import os
+
+import numpy as np
+import pytest
+
+from cases import EDGE_SHAPES, SWEEP, conv_inputs
+from gpu_util import assert_same, to_dev_nhwc, to_host_nchw
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "quant_ref.npz"))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import torch
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    from nart_b200 import ops as o   # raises if libnart_b200.so is missing: there is no fallback
+    return o
+
+
+def algos_for(ops, c, k, group):
+    a = [ops.ALGO_DIRECT]
+    if os.environ.get("B200_TEST_ALGOS") == "direct":   # debugging aid: CUDA-core path only
+        return a
+    if group == 1 and c % 32 == 0 and k % 16 == 0:
+        a.append(ops.ALGO_IGEMM)
+    return a
+
+
+def run_conv(ops, x, wt, bias, st, pd, g, algo, return_acc=False, **q):
+    conv = ops.Conv2d(wt, bias, in_hw=x.shape[2:], stride=(st, st), pad=(pd, pd), group=g, algo=algo, **q)
+    assert conv.algo == algo
+    out = conv(to_dev_nhwc(x), return_acc=return_acc)
+    assert ops.device_status() == 0
+    if return_acc:
+        return to_host_nchw(out[0]), to_host_nchw(out[1])
+    return to_host_nchw(out)
+
+
+@pytest.mark.parametrize("algo_i", [0, 1])
+def test_conv_config0_golden(ops, algo_i):
+    n, c, h, w, k, r, s, st, pd, g = EDGE_SHAPES[0]
+    algo = algos_for(ops, c, k, g)[algo_i]
+    x, wt, bias, walpha = conv_inputs(0, n, c, h, w, k, r, s, g)
+    q = dict(ialpha=0.02, izp=128, wzp=128, oalpha=0.05, ozp=0)
+    assert_same(run_conv(ops, x, wt, bias, st, pd, g, algo, walpha=walpha[:1], **q), GOLD["c0_scalar"], "scalar")
+    assert_same(run_conv(ops, x, wt, bias, st, pd, g, algo, walpha=walpha, relu=True, **q), GOLD["c0_per_channel"], "per-channel")
+    q2 = dict(ialpha=0.02, izp=117, wzp=128, oalpha=0.4, ozp=77)
+    assert_same(run_conv(ops, x, wt, bias, st, pd, g, algo, walpha=walpha[:1], **q2), GOLD["c0_zp_scalar"], "zp")
+    assert_same(run_conv(ops, x, wt, bias, st, pd, g, algo, walpha=walpha[:1], relu=True, **q2), GOLD["c0_zp_relu"], "zp relu")
+
+
+@pytest.mark.parametrize("i", range(1, len(EDGE_SHAPES)))
+def test_conv_edge_shapes(ops, port, i):
+    n, c, h, w, k, r, s, st, pd, g = EDGE_SHAPES[i]
+    x, wt, bias, walpha = conv_inputs(100 + i, n, c, h, w, k, r, s, g)
+    q = dict(ialpha=0.037, izp=(37 * i) % 256, wzp=128, oalpha=0.05 * np.sqrt(c // g * r * s) / 4, ozp=(11 * i) % 200)
+    for algo in algos_for(ops, c, k, g):
+        y = run_conv(ops, x, wt, bias, st, pd, g, algo, walpha=walpha[:1], **q)
+        assert_same(y, GOLD["edge%d" % i], "edge%d algo%d" % (i, algo))
+        # per-channel scales + fused relu against the restatement
+        want = port.conv2d_u8(x, wt, bias, (st, st), (pd, pd), g, walpha=walpha, relu=True, **q)
+        y = run_conv(ops, x, wt, bias, st, pd, g, algo, walpha=walpha, relu=True, **q)
+        assert_same(y, want, "edge%d algo%d per-channel relu" % (i, algo))
+
+
+def test_conv_accumulators(ops, port):
+    x, wt, bias, walpha = conv_inputs(77, 2, 32, 9, 11, 48, 3, 3)
+    q = dict(ialpha=0.02, izp=131, wzp=128, oalpha=0.3, ozp=5)
+    want_y, want_acc = port.conv2d_u8(x, wt, bias, (1, 1), (1, 1), 1, walpha=walpha, return_acc=True, **q)
+    y, acc = run_conv(ops, x, wt, bias, 1, 1, 1, ops.ALGO_DIRECT, return_acc=True, walpha=walpha, **q)
+    assert_same(acc, want_acc, "acc")
+    assert_same(y, want_y, "y")
+
+
+@pytest.mark.parametrize("c,k,h,ks,st", SWEEP)
+@pytest.mark.parametrize("batch", [1, 3])
+def test_conv_sweep_shapes(ops, port, c, k, h, ks, st, batch):
+    """BASELINE config 1 shapes at small batch (the restatement finishes in seconds)."""
+    x, wt, bias, walpha = conv_inputs(c + h + ks + st, batch, c, h, h, k, ks, ks)
+    q = dict(ialpha=0.02, izp=128, wzp=128, oalpha=0.05 * np.sqrt(c * ks * ks) / 8, ozp=0)
+    want = port.conv2d_u8(x, wt, bias, (st, st), (ks // 2, ks // 2), 1, walpha=walpha, relu=True, **q)
+    for algo in algos_for(ops, c, k, 1):
+        y = run_conv(ops, x, wt, bias, st, ks // 2, 1, algo, walpha=walpha, relu=True, **q)
+        assert_same(y, want, "sweep algo%d" % algo)
+
+
+def test_conv_large_scale_generic_requant_path(ops, port):
+    """Scales >= 0.25 give shift <= 32: the 64-bit requantize branch."""
+    x, wt, bias, walpha = conv_inputs(5, 2, 16, 6, 6, 16, 3, 3)
+    for oalpha in (1e-4, 3e-6):
+        q = dict(ialpha=0.02, izp=128, wzp=128, oalpha=oalpha, ozp=100)
+        want = port.conv2d_u8(x, wt, bias, (1, 1), (1, 1), 1, walpha=walpha, **q)
+        for algo in algos_for(ops, 16, 16, 1):
+            assert_same(run_conv(ops, x, wt, bias, 1, 1, 1, algo, walpha=walpha, **q), want, "oalpha %g" % oalpha)
+
+
+def test_conv_empty_batch_and_errors(ops):
+    import torch
+    x, wt, bias, walpha = conv_inputs(1, 1, 16, 5, 5, 16, 3, 3)
+    conv = ops.Conv2d(wt, bias, in_hw=(5, 5), pad=(1, 1), ialpha=0.02, izp=1, walpha=walpha, oalpha=0.1, ozp=0)
+    y = conv(torch.empty((0, 5, 5, 16), dtype=torch.uint8, device="cuda"))
+    assert y.shape == (0, 5, 5, 16)
+    with pytest.raises(ValueError):
+        conv(torch.zeros((1, 6, 5, 16), dtype=torch.uint8, device="cuda"))
+
+
+def test_ip(ops, port):
+    rng = np.random.default_rng(7)
+    rng.integers(0, 256, (2, 32, 14, 14), dtype=np.uint8); rng.integers(0, 256, (2, 32, 14, 14), dtype=np.uint8)
+    rng.standard_normal((2, 3, 20, 20))
+    xi = rng.integers(0, 256, (4, 512), dtype=np.uint8)
+    wi = (rng.integers(-127, 128, (100, 512)) + 128).astype(np.uint8)
+    bi = rng.integers(-4096, 4097, 100).astype(np.int32)
+    ip = ops.InnerProduct(wi, bi, in_chw=(512, 1, 1), ialpha=0.02, izp=100, walpha=0.005, oalpha=0.1, ozp=50)
+    y = ip(to_dev_nhwc(xi.reshape(4, 512, 1, 1)))
+    assert_same(y.cpu().numpy().reshape(4, 100), GOLD["ip"], "ip 1x1")
+    # spatial input: the reference flattens NCHW
+    x = rng.integers(0, 256, (3, 16, 3, 3), dtype=np.uint8)
+    w2 = (rng.integers(-127, 128, (24, 144)) + 128).astype(np.uint8)
+    want = port.ip_u8(x, w2, None, 0.05, 7, [0.004], 128, 0.5, 9)
+    ip2 = ops.InnerProduct(w2, None, in_chw=(16, 3, 3), ialpha=0.05, izp=7, walpha=0.004, oalpha=0.5, ozp=9)
+    assert_same(ip2(to_dev_nhwc(x)).cpu().numpy().reshape(3, 24), want, "ip 3x3")
+
+
+def test_layout_roundtrip(ops):
+    import torch
+    rng = np.random.default_rng(3)
+    for shape in ((2, 3, 17, 19), (1, 64, 7, 7), (3, 40, 5, 6), (2, 16, 1, 1)):
+        x = rng.integers(0, 256, shape, dtype=np.uint8)
+        d = ops.nchw_to_nhwc(torch.from_numpy(x).cuda())
+        assert_same(d.cpu().numpy(), x.transpose(0, 2, 3, 1), "nchw->nhwc %s" % (shape,))
+        assert_same(ops.nhwc_to_nchw(d).cpu().numpy(), x, "nhwc->nchw %s" % (shape,))
+    x = rng.integers(0, 256, (2, 3, 9, 9), dtype=np.uint8)
+    d = ops.nchw_to_nhwc(torch.from_numpy(x).cuda(), c_pad=4, fill=9)
+    assert (d[..., 3] == 9).all() and np.array_equal(d[..., :3].cpu().numpy(), x.transpose(0, 2, 3, 1))
+    assert_same(ops.nhwc_to_nchw(d, c=3).cpu().numpy(), x, "strip pad")
+
+
+def test_quantize_dequantize(ops, port):
+    import torch
+    rng = np.random.default_rng(7)
+    a = rng.integers(0, 256, (2, 32, 14, 14), dtype=np.uint8)
+    rng.integers(0, 256, (2, 32, 14, 14), dtype=np.uint8)
+    f = (rng.standard_normal((2, 3, 20, 20)) * 3).astype(np.float32)
+    q = ops.quantize(torch.from_numpy(f).cuda(), 0.037, 117)
+    assert_same(to_host_nchw(q), GOLD["quantize"], "quantize nhwc")
+    q = ops.quantize(torch.from_numpy(f).cuda(), 0.037, 117, nhwc=False)
+    assert_same(q.cpu().numpy(), GOLD["quantize"], "quantize nchw")
+    d = ops.dequantize(to_dev_nhwc(a), 0.037, 117)
+    assert_same(d.cpu().numpy().view(np.uint32), GOLD["dequantize"].view(np.uint32), "dequantize")
+    # values on and around the rounding boundaries, saturation at both ends
+    alpha, zp = np.float32(0.1), 10
+    grid = ((np.arange(-40, 600, dtype=np.float32) * np.float32(0.5)) - zp) * alpha
+    vals = np.concatenate([grid, np.nextafter(grid, np.float32(1e9)), np.nextafter(grid, np.float32(-1e9))]).astype(np.float32)
+    vals = vals[: vals.size // 4 * 4].reshape(1, 4, -1, 1)
+    got = ops.quantize(torch.from_numpy(vals).cuda(), float(alpha), zp)
+    assert_same(to_host_nchw(got), port.quantize_u8(vals, float(alpha), zp), "quantize boundaries")
+    big = (rng.standard_normal((2, 64, 30, 31)) * 4).astype(np.float32)
+    assert_same(to_host_nchw(ops.quantize(torch.from_numpy(big).cuda(), 0.05, 128)), port.quantize_u8(big, 0.05, 128), "quantize big")
+
+
+def test_eltwise_all_byte_pairs(ops, port):
+    a = np.repeat(np.arange(256, dtype=np.uint8), 256).reshape(1, 256, 16, 16)
+    b = np.tile(np.arange(256, dtype=np.uint8), 256).reshape(1, 256, 16, 16)
+    import torch
+    for ia, iz, oa, oz in (([0.037, 0.081], [117, 9], 0.093, 31), ([0.1, 0.01], [0, 255], 0.05, 128), ([0.02, 0.02], [3, 250], 0.3, 0)):
+        for relu in (False, True):
+            want = port.eltwise_sum_u8([a, b], ia, iz, oa, oz, relu=relu)
+            got = ops.eltwise_sum([torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()], ia, iz, oa, oz, relu=relu)
+            assert_same(got.cpu().numpy(), want, "eltwise %s relu=%s" % (ia, relu))
+    rng = np.random.default_rng(7)
+    a = rng.integers(0, 256, (2, 32, 14, 14), dtype=np.uint8)
+    b = rng.integers(0, 256, (2, 32, 14, 14), dtype=np.uint8)
+    got = ops.add(torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(), [0.037, 0.081], [117, 9], 0.093, 31)
+    assert_same(got.cpu().numpy(), GOLD["add"], "add golden")
+    # ragged length (tail path) and three inputs
+    xs = [rng.integers(0, 256, 1000 + 7, dtype=np.uint8) for _ in range(3)]
+    want = port.eltwise_sum_u8(xs, [0.03, 0.05, 0.02], [1, 2, 3], 0.08, 17, coeff=[1.0, 0.5, 2.0])
+    got = ops.eltwise_sum([torch.from_numpy(v).cuda() for v in xs], [0.03, 0.05, 0.02], [1, 2, 3], 0.08, 17, coeff=[1.0, 0.5, 2.0])
+    assert_same(got.cpu().numpy(), want, "eltwise 3 inputs")
+
+
+def test_relu(ops, port):
+    import torch
+    x = np.arange(256, dtype=np.uint8).repeat(3).reshape(1, 1, 3, 256)
+    for ia, iz, oa, oz in ((0.037, 117, 0.037, 117), (0.037, 117, 0.05, 20), (0.4, 0, 0.1, 255)):
+        got = ops.relu(torch.from_numpy(x).cuda(), ia, iz, oa, oz)
+        assert_same(got.cpu().numpy(), port.relu_u8(x, ia, iz, oa, oz), "relu")
+
+
+def test_pool(ops, port):
+    rng = np.random.default_rng(7)
+    a = rng.integers(0, 256, (2, 32, 14, 14), dtype=np.uint8)
+    for name, m, cm in (("pool_max", 0, 0), ("pool_max_ceil", 0, 1), ("pool_ave", 1, 0), ("pool_ave_ceil", 1, 1)):
+        got = ops.pool(to_dev_nhwc(a), m, (3, 3), (1, 1), (2, 2), cm, 0.037, 117, 0.093, 31)
+        assert_same(to_host_nchw(got), GOLD[name], name)
+    got = ops.pool(to_dev_nhwc(a), 1, (14, 14), (0, 0), (1, 1), 0, 0.037, 117, 0.093, 31)
+    assert_same(to_host_nchw(got), GOLD["pool_gap"], "gap")
+    # ragged channel counts (4- and 1-byte vector paths), odd sizes
+    for c in (20, 7, 64):
+        x = rng.integers(0, 256, (3, c, 13, 9), dtype=np.uint8)
+        for m in (0, 1):
+            want = port.pool_u8(x, m, (3, 2), (1, 0), (2, 1), 1, 0.05, 33, 0.07, 12)
+            got = ops.pool(to_dev_nhwc(x), m, (3, 2), (1, 0), (2, 1), 1, 0.05, 33, 0.07, 12)
+            assert_same(to_host_nchw(got), want, "pool c=%d m=%d" % (c, m))
+    # the ResNet shapes: 3x3 s2 p1 max on 112x112 (ceil_mode false) and 7x7 global average
+    x = rng.integers(0, 256, (2, 64, 112, 112), dtype=np.uint8)
+    want = port.pool_u8(x, 0, (3, 3), (1, 1), (2, 2), 0, 0.05, 3, 0.05, 3)
+    assert want.shape[2:] == (56, 56)
+    assert_same(to_host_nchw(ops.pool(to_dev_nhwc(x), 0, (3, 3), (1, 1), (2, 2), 0, 0.05, 3, 0.05, 3)), want, "resnet maxpool")
+    x = rng.integers(0, 256, (4, 2048, 7, 7), dtype=np.uint8)
+    want = port.pool_u8(x, 1, (7, 7), (0, 0), (1, 1), 0, 0.05, 3, 0.02, 0)
+    assert_same(to_host_nchw(ops.pool(to_dev_nhwc(x), 1, (7, 7), (0, 0), (1, 1), 0, 0.05, 3, 0.02, 0)), want, "resnet gap")
