@@ -1,9 +1,899 @@
+// Implicit-GEMM int8 convolution on the 5th-generation tensor cores (sm_100a):
+//   D[pixels, Cout] (int32, TMEM) += A[pixels, R*S*C] (uint8 activations) x B[Cout, R*S*C]^T (int8)
+// with tcgen05.mma kind::i8, operands staged by TMA into swizzled shared memory, accumulators in
+// tensor memory, and the reference's zero-point correction, bias, requantize and ReLU clamp
+// fused into the epilogue (art/modules/quant/src/op/conv_2d_uint8_impl.c:107-164 of ModelTC/NART).
+//
+// GEMM view.  An M tile is 128 output pixels arranged as a TW x TH x TN box of
+// (ow, oh, image); for filter tap (r, s) and a BK-channel slice the A operand is the box of input
+// pixels one tiled TMA load fetches from the NHWC tensor (coordinates may run outside the image:
+// TMA fills zeros).  Strided convs address the input through one tensor map per (row, column)
+// parity so that every load stays a plain dense box.  B is the weight matrix repacked once to
+// [Cout][R][S][C] int8.  K is walked tap by tap, BK channels at a time.
+//
+// Zero point.  The MMA multiplies the raw uint8 activation, and TMA pads with the byte 0, whereas
+// the reference pads with the real value 0, i.e. the byte izp.  With
+//   raw = sum_{valid taps} x * w      true = sum_{valid taps} (x - izp) * w = raw - izp * sum_{valid} w
+// the correction depends only on which taps are inside the image, i.e. on the output pixel's
+// border class.  The host builds off[class][k] = bias[k] - izp * sum_{taps valid in class} w[k] and
+// the epilogue adds the row of the pixel's class.
+//
+// Warp roles (192 threads, one CTA per SM, persistent over tiles):
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      tensor-memory allocation, MMA issue (one elected lane)
+//   warps 2..5  epilogue: tcgen05.ld -> offsets -> requantize -> swizzled smem -> TMA store
+// Two accumulator stages in tensor memory let the epilogue of tile i overlap the mainloop of
+// tile i+1.  No cluster launch, no multicast.  Every wait is bounded: when one runs out the
+// kernel records a code in the status word, all roles leave their loops, tensor memory is freed
+// and the kernel returns.
+#include <cuda.h>
+#include <string.h>
+
+#include <vector>
+
 #include "common.cuh"
 #include "kernels.h"
+
 namespace b200 {
-struct ConvIgemmPlan {};
-int conv_igemm_supported(const ConvGeom &, char *why, size_t n) { snprintf(why, n, "stub"); return 0; }
-int conv_igemm_create(const ConvGeom &, const std::vector<int8_t> &, const int32_t *, const uint32_t *, const int32_t *, ConvIgemmPlan **) { return B200_ERR_UNSUPPORTED; }
-int conv_igemm_launch(ConvIgemmPlan *, const uint8_t *, int, uint8_t *, cudaStream_t) { return B200_ERR_UNSUPPORTED; }
-void conv_igemm_destroy(ConvIgemmPlan *) {}
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kTileM = 128;
+constexpr int kMaxStages = 8;
+constexpr int kAccStages = 2;
+constexpr long long kWaitCycles = 4000000000ll;   // ~2 s at 1.9 GHz
+
+// device status codes (which wait gave up)
+constexpr int kErrProducerWait = 0x101;
+constexpr int kErrMmaFullWait = 0x102;
+constexpr int kErrMmaTmemWait = 0x103;
+constexpr int kErrEpilogueWait = 0x104;
+
+struct alignas(64) IgemmMaps {
+    CUtensorMap a[4];   // activations, one per (row parity, column parity) of a strided conv
+    CUtensorMap b;      // weights [Cout][R*S*C]
+    CUtensorMap y;      // output NHWC
+};
+
+struct IgemmArgs {
+    // problem
+    int n, oh, ow, cout;
+    int r, s, pad_h, pad_w, stride_h, stride_w;
+    int c;               // input channels
+    // tiling
+    int tw, th, tn;      // M-tile box (ow, oh, image), tw*th*tn == 128
+    int tiles_w, tiles_h, tiles_n, n_tiles_n;   // tile counts along ow, oh, image and Cout
+    int bk;              // channels per k-block (32, 64, 128) == swizzle span of the operands
+    int bn;              // output channels per tile (multiple of 16, <= 256)
+    int stages;          // smem pipeline depth
+    int ob;              // bytes per row of an output staging sub-tile (<= 128, divides bn)
+    uint32_t idesc;      // tcgen05 instruction descriptor
+    uint32_t tmem_cols;  // columns to allocate (power of two >= 2*bn)
+    // epilogue tables
+    const int32_t *off;      // [n_cls][kpad]
+    const uint32_t *mult;    // [kpad]
+    const int32_t *shift;    // [kpad]
+    const uint8_t *row_cls;  // [oh]
+    const uint8_t *col_cls;  // [ow]
+    int n_col_cls, kpad;
+    int ozp, qmax, relu_lo;
+    int use_tma_store;       // 0: plain stores (Cout not a multiple of 16)
+    uint8_t *y;
+    int *status;
+};
+
+// ---- PTX wrappers --------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: returns false when the barrier did not flip within kWaitCycles or another role
+// has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+{
+    if (mbar_try_wait(bar, parity))
+        return true;
+    const long long t0 = clock64();
+    int spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 255) == 0) {
+            if (*abort_flag != 0 || clock64() - t0 > kWaitCycles)
+                return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+        ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void prefetch_map(const CUtensorMap *map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, 8-bit integer operands, int32 accumulate.
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The barrier gets one arrival when every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void mma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// AND-reduction of a predicate over the 128 epilogue threads (named barrier 2): every thread gets
+// the same answer, so all of them leave the tile loop together.
+__device__ __forceinline__ bool epi_bar_all(bool pred)
+{
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 p, %1, 0;\n\t"
+        "barrier.cta.red.and.pred q, 2, 128, p;\n\t"
+        "selp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(out)
+        : "r"((uint32_t)pred)
+        : "memory");
+    return out != 0;
+}
+
+// Shared-memory matrix descriptor of a K-major operand tile whose rows are `bk` bytes
+// (bk = 128 / 64 / 32 selects the 128B / 64B / 32B swizzle both TMA and the MMA use); eight rows
+// form one swizzle atom, atoms follow each other every 8*bk bytes (the stride byte offset).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk)
+{
+    const uint64_t layout = bk == 128 ? 2ull : (bk == 64 ? 4ull : 6ull);
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);          // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                           // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)((8 * bk) >> 4) << 32;             // stride byte offset
+    d |= (uint64_t)1 << 46;                           // descriptor version of sm_100
+    d |= layout << 61;
+    return d;
+}
+
+// ---- shared memory layout (dynamic, base aligned to 1024) ---------------------------------------
+//   [stages x A tile (128 x bk)] [stages x B tile (bn x bk)] [output staging 128 x bn]
+//   [mult bn x 4][shift bn x 4] [barriers][tmem address][abort flag]
+struct SmemLayout {
+    uint32_t a, b, out, mult, shift, bars, tmem_slot, abort_flag, total;
+};
+__host__ __device__ inline SmemLayout smem_layout(int stages, int bk, int bn)
+{
+    SmemLayout L;
+    uint32_t o = 0;
+    L.a = o;
+    o += (uint32_t)stages * kTileM * bk;
+    L.b = o;
+    uint32_t b_tile = ((uint32_t)bn * bk + 1023u) & ~1023u;
+    o += (uint32_t)stages * b_tile;
+    L.out = o;
+    o += (uint32_t)kTileM * bn;
+    o = (o + 1023u) & ~1023u;
+    L.mult = o;
+    o += (uint32_t)bn * 4;
+    L.shift = o;
+    o += (uint32_t)bn * 4;
+    o = (o + 15u) & ~15u;
+    L.bars = o;
+    o += (2 * kMaxStages + 2 * kAccStages) * 8;
+    L.tmem_slot = o;
+    o += 8;
+    L.abort_flag = o;
+    o += 8;
+    L.total = o;
+    return L;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const IgemmArgs g)
+{
+    extern __shared__ uint8_t smem_raw[];
+    // the swizzle patterns are functions of the absolute shared address: align the base to 1024
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (base - raw_addr);
+    const SmemLayout L = smem_layout(g.stages, g.bk, g.bn);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t a_tile_bytes = (uint32_t)kTileM * g.bk;
+    const uint32_t b_tile_bytes = ((uint32_t)g.bn * g.bk + 1023u) & ~1023u;
+    const uint32_t bar0 = base + L.bars;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
+    auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * kMaxStages + s); };
+    auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * kMaxStages + kAccStages + s); };
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < g.stages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int s = 0; s < kAccStages; ++s) {
+            mbar_init(tfull_bar(s), 1);
+            mbar_init(tempty_bar(s), 4);   // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_map(&maps.a[0]);
+        prefetch_map(&maps.b);
+        prefetch_map(&maps.y);
+    }
+    if (warp == 1) {
+        tmem_alloc(base + L.tmem_slot, g.tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int m_tiles = g.tiles_w * g.tiles_h * g.tiles_n;
+    const int total_tiles = m_tiles * g.n_tiles_n;
+    const int cchunks = g.c / g.bk;
+    const int kblocks = g.r * g.s * cchunks;
+
+    if (warp == 0) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int nt = tile % g.n_tiles_n;
+                int mt = tile / g.n_tiles_n;
+                const int twi = mt % g.tiles_w;
+                mt /= g.tiles_w;
+                const int thi = mt % g.tiles_h;
+                const int tni = mt / g.tiles_h;
+                const int ow0 = twi * g.tw, oh0 = thi * g.th, n0 = tni * g.tn;
+                for (int rr = 0; rr < g.r && ok; ++rr) {
+                    // input row of output row oh for this tap: ih = oh*stride + rr - pad
+                    //   = stride * (oh + floor(d / stride)) + (d mod stride),  d = rr - pad
+                    const int dh = rr - g.pad_h;
+                    const int ph = ((dh % g.stride_h) + g.stride_h) % g.stride_h;
+                    const int qh = (dh - ph) / g.stride_h;
+                    for (int ss = 0; ss < g.s && ok; ++ss) {
+                        const int dw = ss - g.pad_w;
+                        const int pw = ((dw % g.stride_w) + g.stride_w) % g.stride_w;
+                        const int qw = (dw - pw) / g.stride_w;
+                        const CUtensorMap *amap = &maps.a[ph * 2 + pw];
+                        for (int cc = 0; cc < cchunks; ++cc) {
+                            if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                                atomicCAS(g.status, 0, kErrProducerWait);
+                                *abort_flag = 1;
+                                ok = false;
+                                break;
+                            }
+                            mbar_expect_tx(full_bar(stage), a_tile_bytes + (uint32_t)g.bn * g.bk);
+                            tma_load_4d(base + L.a + stage * a_tile_bytes, amap, full_bar(stage),
+                                        cc * g.bk, ow0 + qw, oh0 + qh, n0);
+                            tma_load_2d(base + L.b + stage * b_tile_bytes, &maps.b, full_bar(stage),
+                                        ((rr * g.s + ss) * cchunks + cc) * g.bk, nt * g.bn);
+                            if (++stage == g.stages) {
+                                stage = 0;
+                                phase ^= 1;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int as = 0;
+            uint32_t aphase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(as), aphase ^ 1, abort_flag)) {
+                    atomicCAS(g.status, 0, kErrMmaTmemWait);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(as * g.bn);
+                for (int kb = 0; kb < kblocks; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                        atomicCAS(g.status, 0, kErrMmaFullWait);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t adesc = make_smem_desc(base + L.a + stage * a_tile_bytes, g.bk);
+                    const uint64_t bdesc = make_smem_desc(base + L.b + stage * b_tile_bytes, g.bk);
+                    const int ksteps = g.bk / 32;
+                    for (int ks = 0; ks < ksteps; ++ks) {
+                        // advance 32 bytes of K inside the swizzle atom: +2 in 16-byte units
+                        mma_i8(d_tmem, adesc + 2ull * ks, bdesc + 2ull * ks, g.idesc, (kb | ks) != 0);
+                    }
+                    mma_commit(empty_bar(stage));   // frees the smem stage when these MMAs are done
+                    if (++stage == g.stages) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok)
+                    break;
+                mma_commit(tfull_bar(as));          // accumulator complete
+                if (++as == kAccStages) {
+                    as = 0;
+                    aphase ^= 1;
+                }
+            }
+        }
+    } else {
+        // ================= epilogue (warps 2..5) =================
+        const int et = threadIdx.x - 64;             // 0..127
+        const int quarter = warp & 3;                // TMEM lanes 32*quarter .. +31 belong to this warp
+        const int row = quarter * 32 + lane;         // accumulator row = pixel of the tile
+        uint32_t *s_mult = reinterpret_cast<uint32_t *>(smem + L.mult);
+        int32_t *s_shift = reinterpret_cast<int32_t *>(smem + L.shift);
+        uint8_t *s_out = smem + L.out;
+        const int n_sub = g.bn / g.ob;               // output sub-tiles of `ob` bytes per row
+        const int sw_shift = g.ob == 128 ? 0 : (g.ob == 64 ? 1 : 2);
+        const int sw_mask = g.ob == 128 ? 7 : (g.ob == 64 ? 3 : (g.ob == 32 ? 1 : 0));
+        int as = 0;
+        uint32_t aphase = 0;
+        int cur_nt = -1;
+        bool store_pending = false;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            const int nt = tile % g.n_tiles_n;
+            int mt = tile / g.n_tiles_n;
+            const int twi = mt % g.tiles_w;
+            mt /= g.tiles_w;
+            const int thi = mt % g.tiles_h;
+            const int tni = mt / g.tiles_h;
+            const int ow0 = twi * g.tw, oh0 = thi * g.th, n0 = tni * g.tn;
+            const int k0 = nt * g.bn;
+            // this thread's pixel
+            const int lw = row % g.tw, lh = (row / g.tw) % g.th, ln = row / (g.tw * g.th);
+            const int ow = ow0 + lw, oh = oh0 + lh, img = n0 + ln;
+            const bool pix_valid = ow < g.ow && oh < g.oh && img < g.n;
+            const int cls = (int)g.row_cls[min(oh, g.oh - 1)] * g.n_col_cls + (int)g.col_cls[min(ow, g.ow - 1)];
+            const int32_t *off_row = g.off + (size_t)cls * g.kpad + k0;
+
+            // the previous tile's store must have finished reading the staging buffer, and the
+            // per-channel tables change with the channel tile
+            if (store_pending && et == 0)
+                tma_store_wait_read();
+            epi_bar_sync();
+            if (nt != cur_nt) {
+                for (int j = et; j < g.bn; j += 128) {
+                    s_mult[j] = g.mult[k0 + j];
+                    s_shift[j] = g.shift[k0 + j];
+                }
+                cur_nt = nt;
+            }
+            epi_bar_sync();
+
+            if (!epi_bar_all(mbar_wait(tfull_bar(as), aphase, abort_flag))) {
+                if (et == 0) {
+                    atomicCAS(g.status, 0, kErrEpilogueWait);
+                    *abort_flag = 1;
+                }
+                break;
+            }
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * g.bn);
+            for (int c0 = 0; c0 < g.bn; c0 += 32) {
+                uint32_t v[32];
+                const int ncol = min(32, g.bn - c0);   // 32, or 16 for the last chunk of bn % 32 == 16
+                if (ncol == 32)
+                    tmem_ld32(t_row + c0, v);
+                else
+                    tmem_ld16(t_row + c0, v);
+                tmem_ld_wait();
+                uint32_t packed[8];
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) {
+                    if (q4 * 4 < ncol) {
+                        const int4 o4 = __ldg(reinterpret_cast<const int4 *>(off_row + c0 + q4 * 4));
+                        const int offs[4] = { o4.x, o4.y, o4.z, o4.w };
+                        int q[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int col = c0 + q4 * 4 + e;
+                            const int acc = (int)v[q4 * 4 + e] + offs[e];
+                            q[e] = sat_relu(requant_raw(acc, s_mult[col], s_shift[col], g.ozp), g.qmax, g.relu_lo);
+                        }
+                        packed[q4] = pack4(q[0], q[1], q[2], q[3]);
+                    }
+                }
+                // staging: sub-tile (c0 / ob), row-major rows of `ob` bytes, 16-byte chunks XOR-swizzled
+                // with the row index exactly as the TMA store's swizzle mode expects
+                const int sw = (row >> sw_shift) & sw_mask;
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    if (ch * 16 < ncol) {
+                        const int col = c0 + ch * 16;
+                        const int sub = col / g.ob;
+                        const int chunk = (col % g.ob) >> 4;
+                        uint8_t *srow = s_out + (size_t)sub * kTileM * g.ob + (size_t)row * g.ob;
+                        uint4 val = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+                        *reinterpret_cast<uint4 *>(srow + ((chunk ^ sw) << 4)) = val;
+                    }
+                }
+            }
+            // accumulator stage drained: hand it back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(tempty_bar(as));
+            if (++as == kAccStages) {
+                as = 0;
+                aphase ^= 1;
+            }
+
+            if (g.use_tma_store) {
+                fence_async_smem();
+                epi_bar_sync();
+                if (et == 0) {
+                    for (int sub = 0; sub < n_sub; ++sub) {
+                        if (k0 + sub * g.ob < g.cout)
+                            tma_store_4d(&maps.y, smem_u32(s_out + (size_t)sub * kTileM * g.ob), k0 + sub * g.ob, ow0, oh0, n0);
+                    }
+                    tma_store_commit();
+                }
+                store_pending = true;
+            } else {
+                // plain stores for channel counts the TMA store cannot address (Cout % 16 != 0)
+                epi_bar_sync();
+                const int sw = (row >> sw_shift) & sw_mask;
+                if (pix_valid) {
+                    uint8_t *dst = g.y + (((size_t)img * g.oh + oh) * g.ow + ow) * g.cout + k0;
+                    const int nvalid = min(g.bn, g.cout - k0);
+                    for (int j = 0; j < nvalid; ++j) {
+                        const int sub = j / g.ob, cin = j % g.ob;
+                        const int chunk = cin >> 4;
+                        dst[j] = s_out[(size_t)sub * kTileM * g.ob + (size_t)row * g.ob + ((chunk ^ sw) << 4) + (cin & 15)];
+                    }
+                }
+                store_pending = false;
+            }
+        }
+        if (store_pending && et == 0)
+            tma_store_wait_all();
+    }
+
+    // ---- common exit: every role gets here (all waits are bounded) ---------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, g.tmem_cols);
+    }
+}
+
+// ---- host side -------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(
+    CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess
+            && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+CUtensorMapSwizzle swizzle_for(int bytes)
+{
+    return bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+        : bytes == 64   ? CU_TENSOR_MAP_SWIZZLE_64B
+        : bytes == 32   ? CU_TENSOR_MAP_SWIZZLE_32B
+                        : CU_TENSOR_MAP_SWIZZLE_NONE;
+}
+
+int encode(CUtensorMap *m, void *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides_bytes,
+           const cuuint32_t *box, CUtensorMapSwizzle sw)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn)
+        return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint32_t estr[5] = { 1, 1, 1, 1, 1 };
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, base, dims, strides_bytes, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu %llu, box %u %u)",
+                    (int)r, rank, (unsigned long long)dims[0], (unsigned long long)dims[1], box[0], box[1]);
+    return B200_OK;
+}
+
+}  // namespace
+
+struct ConvIgemmPlan {
+    ConvGeom g;
+    int bk = 0, bn = 0, stages = 0, ob = 0, kpad = 0;
+    int n_row_cls = 0, n_col_cls = 0;
+    int8_t *w_dev = nullptr;        // [kpad][r][s][c]
+    int32_t *off_dev = nullptr;     // [n_cls][kpad]
+    uint32_t *mult_dev = nullptr;   // [kpad]
+    int32_t *shift_dev = nullptr;   // [kpad]
+    uint8_t *row_cls_dev = nullptr, *col_cls_dev = nullptr;
+    // tensor maps of the last (x, y, n) seen
+    const uint8_t *last_x = nullptr;
+    uint8_t *last_y = nullptr;
+    int last_n = -1;
+    IgemmMaps maps;
+    IgemmArgs args;
+    dim3 grid;
+    size_t smem = 0;
+    bool attr_set = false;
+};
+
+int conv_igemm_supported(const ConvGeom &g, char *why, size_t why_len)
+{
+    const char *msg = nullptr;
+    if (g.group != 1) msg = "group != 1";
+    else if (g.c % 32 != 0) msg = "input channels not a multiple of 32";
+    else if (g.k < 16) msg = "fewer than 16 output channels";
+    else if (g.stride_h > 2 || g.stride_w > 2) msg = "stride > 2";
+    else if (g.h < g.stride_h || g.w < g.stride_w) msg = "input smaller than the stride";
+    if (msg) {
+        snprintf(why, why_len, "%s", msg);
+        return 0;
+    }
+    return 1;
+}
+
+// Distinct sets of in-image taps along one axis: cls[o] = class of output coordinate o, and
+// valid[class] = bit mask of taps that fall inside the image.
+static void tap_classes(int out, int in, int kernel, int pad, int stride, std::vector<uint8_t> &cls,
+                        std::vector<std::vector<char>> &valid)
+{
+    cls.resize(out);
+    valid.clear();
+    for (int o = 0; o < out; ++o) {
+        std::vector<char> v(kernel);
+        for (int t = 0; t < kernel; ++t) {
+            int i = o * stride + t - pad;
+            v[t] = (i >= 0 && i < in) ? 1 : 0;
+        }
+        int id = -1;
+        for (size_t j = 0; j < valid.size(); ++j)
+            if (valid[j] == v) {
+                id = (int)j;
+                break;
+            }
+        if (id < 0) {
+            valid.push_back(v);
+            id = (int)valid.size() - 1;
+        }
+        cls[o] = (uint8_t)id;
+    }
+}
+
+int conv_igemm_create(
+    const ConvGeom &g, const std::vector<int8_t> &w_s8, const int32_t *bias, const uint32_t *mult,
+    const int32_t *shift, ConvIgemmPlan **out)
+{
+    ConvIgemmPlan *p = new ConvIgemmPlan();
+    p->g = g;
+    p->bk = g.c % 128 == 0 ? 128 : (g.c % 64 == 0 ? 64 : 32);
+    // output-channel tile: a multiple of 16 up to 256 that wastes little of Cout
+    {
+        const int k16 = (g.k + 15) / 16 * 16;
+        if (k16 <= 256) {
+            p->bn = k16;
+        } else {
+            int best = 256, best_waste = 1 << 30;
+            for (int bn = 256; bn >= 128; bn -= 16) {
+                int tiles = (g.k + bn - 1) / bn;
+                int waste = tiles * bn - g.k;
+                if (waste < best_waste) {
+                    best_waste = waste;
+                    best = bn;
+                }
+            }
+            p->bn = best;
+        }
+    }
+    // staging sub-tile width: the largest of 128/64/32/16 that divides bn
+    p->ob = p->bn % 128 == 0 ? 128 : (p->bn % 64 == 0 ? 64 : (p->bn % 32 == 0 ? 32 : 16));
+    const int n_tiles_n = (g.k + p->bn - 1) / p->bn;
+    p->kpad = n_tiles_n * p->bn;
+    // pipeline depth from the shared memory left after the staging buffer
+    {
+        int stages = kMaxStages;
+        while (stages > 2 && smem_layout(stages, p->bk, p->bn).total + 1024 > 227 * 1024)
+            --stages;
+        const int kblocks = g.r * g.s * (g.c / p->bk);
+        if (stages > kblocks + 1)
+            stages = kblocks + 1 < 2 ? 2 : kblocks + 1;
+        p->stages = stages;
+    }
+    if (smem_layout(p->stages, p->bk, p->bn).total + 1024 > 227 * 1024) {
+        delete p;
+        return fail(B200_ERR_UNSUPPORTED, "conv(igemm): tile does not fit shared memory");
+    }
+
+    const int taps = g.r * g.s;
+    // ---- weights [kpad][r][s][c] ---------------------------------------------------------------
+    std::vector<int8_t> wp((size_t)p->kpad * taps * g.c, 0);
+    for (int k = 0; k < g.k; ++k)
+        for (int c = 0; c < g.c; ++c)
+            for (int t = 0; t < taps; ++t)
+                wp[((size_t)k * taps + t) * g.c + c] = w_s8[((size_t)k * g.c + c) * taps + t];
+    // ---- border classes and offsets ---------------------------------------------------------------
+    std::vector<uint8_t> row_cls, col_cls;
+    std::vector<std::vector<char>> row_valid, col_valid;
+    tap_classes(g.oh, g.h, g.r, g.pad_h, g.stride_h, row_cls, row_valid);
+    tap_classes(g.ow, g.w, g.s, g.pad_w, g.stride_w, col_cls, col_valid);
+    p->n_row_cls = (int)row_valid.size();
+    p->n_col_cls = (int)col_valid.size();
+    if (p->n_row_cls > 255 || p->n_col_cls > 255) {
+        delete p;
+        return fail(B200_ERR_UNSUPPORTED, "conv(igemm): too many border classes");
+    }
+    std::vector<long long> wtap((size_t)g.k * taps, 0);   // sum over channels per (k, tap)
+    for (int k = 0; k < g.k; ++k)
+        for (int c = 0; c < g.c; ++c)
+            for (int t = 0; t < taps; ++t)
+                wtap[(size_t)k * taps + t] += w_s8[((size_t)k * g.c + c) * taps + t];
+    std::vector<int32_t> off((size_t)p->n_row_cls * p->n_col_cls * p->kpad, 0);
+    for (int rc = 0; rc < p->n_row_cls; ++rc)
+        for (int cc = 0; cc < p->n_col_cls; ++cc)
+            for (int k = 0; k < g.k; ++k) {
+                long long sum = 0;
+                for (int rr = 0; rr < g.r; ++rr)
+                    if (row_valid[rc][rr])
+                        for (int ss = 0; ss < g.s; ++ss)
+                            if (col_valid[cc][ss])
+                                sum += wtap[(size_t)k * taps + rr * g.s + ss];
+                long long v = (long long)(bias ? bias[k] : 0) - (long long)g.izp * sum;
+                off[((size_t)rc * p->n_col_cls + cc) * p->kpad + k] = (int32_t)(uint32_t)(unsigned long long)v;
+            }
+    std::vector<uint32_t> multp(p->kpad, 0);
+    std::vector<int32_t> shiftp(p->kpad, 33);
+    for (int k = 0; k < g.k; ++k) {
+        multp[k] = mult[k];
+        shiftp[k] = shift[k];
+    }
+    auto up = [](const void *src, size_t bytes, void **dst) -> int {
+        B200_CUDA_TRY(cudaMalloc(dst, bytes));
+        B200_CUDA_TRY(cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice));
+        return B200_OK;
+    };
+    int rc = up(wp.data(), wp.size(), (void **)&p->w_dev);
+    if (rc == B200_OK) rc = up(off.data(), off.size() * 4, (void **)&p->off_dev);
+    if (rc == B200_OK) rc = up(multp.data(), multp.size() * 4, (void **)&p->mult_dev);
+    if (rc == B200_OK) rc = up(shiftp.data(), shiftp.size() * 4, (void **)&p->shift_dev);
+    if (rc == B200_OK) rc = up(row_cls.data(), row_cls.size(), (void **)&p->row_cls_dev);
+    if (rc == B200_OK) rc = up(col_cls.data(), col_cls.size(), (void **)&p->col_cls_dev);
+    if (rc != B200_OK) {
+        conv_igemm_destroy(p);
+        return rc;
+    }
+    *out = p;
+    return B200_OK;
+}
+
+void conv_igemm_destroy(ConvIgemmPlan *p)
+{
+    if (!p)
+        return;
+    cudaFree(p->w_dev);
+    cudaFree(p->off_dev);
+    cudaFree(p->mult_dev);
+    cudaFree(p->shift_dev);
+    cudaFree(p->row_cls_dev);
+    cudaFree(p->col_cls_dev);
+    delete p;
+}
+
+// Chooses the M-tile box (tw, th, tn), powers of two with product 128, that covers the output with
+// the fewest tiles; ties go to the wider box.
+static void choose_tile(int ow, int oh, int n, int *tw, int *th, int *tn)
+{
+    long long best = -1;
+    for (int a = 0; a <= 7; ++a)
+        for (int b = 0; a + b <= 7; ++b) {
+            int w = 1 << a, h = 1 << b, nn = 1 << (7 - a - b);
+            long long tiles = (long long)((ow + w - 1) / w) * ((oh + h - 1) / h) * ((n + nn - 1) / nn);
+            if (best < 0 || tiles < best || (tiles == best && w > *tw)) {
+                best = tiles;
+                *tw = w;
+                *th = h;
+                *tn = nn;
+            }
+        }
+}
+
+static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y)
+{
+    const ConvGeom &g = p->g;
+    if ((((uintptr_t)x | (uintptr_t)y) & 15) != 0)
+        return fail(B200_ERR_INVALID, "conv(igemm): x and y must be 16-byte aligned");
+    IgemmArgs &a = p->args;
+    memset(&a, 0, sizeof(a));
+    a.n = n; a.oh = g.oh; a.ow = g.ow; a.cout = g.k;
+    a.r = g.r; a.s = g.s; a.pad_h = g.pad_h; a.pad_w = g.pad_w; a.stride_h = g.stride_h; a.stride_w = g.stride_w;
+    a.c = g.c;
+    choose_tile(g.ow, g.oh, n, &a.tw, &a.th, &a.tn);
+    a.tiles_w = (g.ow + a.tw - 1) / a.tw;
+    a.tiles_h = (g.oh + a.th - 1) / a.th;
+    a.tiles_n = (n + a.tn - 1) / a.tn;
+    a.n_tiles_n = p->kpad / p->bn;
+    a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.ob = p->ob;
+    // instruction descriptor: D = S32 (2 at bit 4), A = unsigned 8-bit (0 at bit 7), B = signed 8-bit
+    // (1 at bit 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
+    a.idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(p->bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+    uint32_t cols = 32;
+    while (cols < (uint32_t)(kAccStages * p->bn))
+        cols <<= 1;
+    a.tmem_cols = cols;
+    a.off = p->off_dev; a.mult = p->mult_dev; a.shift = p->shift_dev;
+    a.row_cls = p->row_cls_dev; a.col_cls = p->col_cls_dev;
+    a.n_col_cls = p->n_col_cls; a.kpad = p->kpad;
+    a.ozp = g.ozp; a.qmax = g.qmax; a.relu_lo = g.relu_lo;
+    a.use_tma_store = (g.k % 16 == 0) ? 1 : 0;
+    a.y = y;
+    B200_TRY(status_word_ptr(&a.status));
+
+    // ---- tensor maps -------------------------------------------------------------------------------
+    const CUtensorMapSwizzle sw_ab = swizzle_for(p->bk);
+    for (int ph = 0; ph < g.stride_h; ++ph)
+        for (int pw = 0; pw < g.stride_w; ++pw) {
+            // input pixels (ph + stride_h * i, pw + stride_w * j): a dense 4-D tensor (c, j, i, image)
+            if (ph >= g.h || pw >= g.w) {
+                p->maps.a[ph * 2 + pw] = p->maps.a[0];
+                continue;
+            }
+            cuuint64_t dims[4] = { (cuuint64_t)g.c, (cuuint64_t)((g.w - pw + g.stride_w - 1) / g.stride_w),
+                                   (cuuint64_t)((g.h - ph + g.stride_h - 1) / g.stride_h), (cuuint64_t)n };
+            cuuint64_t strides[3] = { (cuuint64_t)g.stride_w * g.c, (cuuint64_t)g.stride_h * g.w * g.c,
+                                      (cuuint64_t)g.h * g.w * g.c };
+            cuuint32_t box[4] = { (cuuint32_t)p->bk, (cuuint32_t)a.tw, (cuuint32_t)a.th, (cuuint32_t)a.tn };
+            void *base = (void *)(x + ((size_t)ph * g.w + pw) * g.c);
+            B200_TRY(encode(&p->maps.a[ph * 2 + pw], base, 4, dims, strides, box, sw_ab));
+        }
+    for (int i = 0; i < 4; ++i) {
+        int ph = i / 2, pw = i % 2;
+        if (ph >= g.stride_h || pw >= g.stride_w)
+            p->maps.a[i] = p->maps.a[0];
+    }
+    {
+        const int ktot = g.r * g.s * g.c;
+        cuuint64_t dims[2] = { (cuuint64_t)ktot, (cuuint64_t)p->kpad };
+        cuuint64_t strides[1] = { (cuuint64_t)ktot };
+        cuuint32_t box[2] = { (cuuint32_t)p->bk, (cuuint32_t)p->bn };
+        B200_TRY(encode(&p->maps.b, p->w_dev, 2, dims, strides, box, sw_ab));
+    }
+    if (a.use_tma_store) {
+        cuuint64_t dims[4] = { (cuuint64_t)g.k, (cuuint64_t)g.ow, (cuuint64_t)g.oh, (cuuint64_t)n };
+        cuuint64_t strides[3] = { (cuuint64_t)g.k, (cuuint64_t)g.ow * g.k, (cuuint64_t)g.oh * g.ow * g.k };
+        cuuint32_t box[4] = { (cuuint32_t)p->ob, (cuuint32_t)a.tw, (cuuint32_t)a.th, (cuuint32_t)a.tn };
+        B200_TRY(encode(&p->maps.y, y, 4, dims, strides, box, swizzle_for(p->ob)));
+    } else {
+        p->maps.y = p->maps.b;
+    }
+    const int total_tiles = a.tiles_w * a.tiles_h * a.tiles_n * a.n_tiles_n;
+    const int sms = sm_count();
+    p->grid = dim3((unsigned)(total_tiles < sms ? total_tiles : sms));
+    p->smem = smem_layout(p->stages, p->bk, p->bn).total + 1024;
+    if (!p->attr_set) {
+        B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        p->attr_set = true;
+    }
+    p->last_x = x;
+    p->last_y = y;
+    p->last_n = n;
+    return B200_OK;
+}
+
+int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cudaStream_t st)
+{
+    if (n == 0)
+        return B200_OK;
+    if (p->last_x != x || p->last_y != y || p->last_n != n)
+        B200_TRY(build_launch(p, x, n, y));
+    conv_igemm_i8_kernel<<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+}  // namespace b200
