@@ -1,0 +1,66 @@
+"""GPU parity of whole networks through the C-ABI case runner: every intermediate tensor and the
+final logits against the CPU restatement, bit for bit."""
+import numpy as np
+import pytest
+
+from gpu_util import assert_same
+
+pytestmark = pytest.mark.gpu
+
+
+def _check(spec, x, port, algo=0, max_batch=None):
+    from nart_b200 import nets
+    names = [op["out"] for op in spec["ops"]]
+    want_logits, want_q, kept = nets.run_cpu(spec, x, port, keep=set(names))
+    cs, ids = nets.to_case(spec, max_batch or x.shape[0], algo=algo, extra_outputs=names)
+    T = spec["tensors"]
+    shapes = [(np.float32, (T[spec["output"]]["c"], 1, 1))] + [
+        (np.uint8, (T[n]["c"], T[n]["h"], T[n]["w"])) for n in names]
+    outs = cs.run_host([x], shapes)
+    for n, got in zip(names, outs[1:]):
+        assert_same(got, kept[n], "%s tensor %s" % (spec["name"], n))
+    assert_same(outs[0].reshape(want_logits.shape).view(np.uint32), want_logits.view(np.uint32), "logits")
+    assert cs.launch_count() == len(spec["ops"]) + 1 + 1 + len(names)
+    cs.close()
+
+
+@pytest.mark.parametrize("spread", [True, False])
+def test_resnet18_small(port, spread):
+    from nart_b200 import nets
+    spec = nets.resnet(18, seed=5, hw=64, width_div=2, spread=spread, num_classes=40)
+    x = np.random.default_rng(1).integers(0, 256, (3, 3, 64, 64), dtype=np.uint8)
+    _check(spec, x, port)
+
+
+def test_resnet50_small(port):
+    from nart_b200 import nets
+    spec = nets.resnet(50, seed=6, hw=64, width_div=2, spread=True, num_classes=1000)
+    x = np.random.default_rng(2).integers(0, 256, (2, 3, 64, 64), dtype=np.uint8)
+    _check(spec, x, port, max_batch=4)
+
+
+def test_resnet18_direct_only(port):
+    from nart_b200 import nets, ops
+    spec = nets.resnet(18, seed=7, hw=32, width_div=4, spread=True, num_classes=16)
+    x = np.random.default_rng(3).integers(0, 256, (2, 3, 32, 32), dtype=np.uint8)
+    _check(spec, x, port, algo=ops.ALGO_DIRECT)
+
+
+def test_mobilenet_v2_small(port):
+    from nart_b200 import nets
+    spec = nets.mobilenet_v2(seed=8, hw=64, spread=True, num_classes=24)
+    x = np.random.default_rng(4).integers(0, 256, (2, 3, 64, 64), dtype=np.uint8)
+    _check(spec, x, port)
+
+
+def test_resnet50_full_size_one_image(port):
+    """The 224x224 network of the benchmark, batch 2, final logits only."""
+    from nart_b200 import nets
+    spec = nets.resnet(50, seed=2, spread=True)
+    x = np.random.default_rng(5).integers(0, 256, (2, 3, 224, 224), dtype=np.uint8)
+    want_logits, want_q, _ = nets.run_cpu(spec, x, port)
+    cs, ids = nets.to_case(spec, 2)
+    (got,) = cs.run_host([x], [(np.float32, (1000, 1, 1))])
+    assert_same(got.reshape(want_logits.shape).view(np.uint32), want_logits.view(np.uint32), "resnet50 logits")
+    assert len(np.unique(want_q)) > 16
+    cs.close()
