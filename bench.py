@@ -1,0 +1,339 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-convolution path on B200: int8 ResNet-50 (batch 256 per GPU,
+3x224x224 uint8 input, synthetic quantization), images per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One process per GPU (the driver launches torchrun for N > 1); the batch is sharded by replica, no
+collective is on the data path.  A step is one pass of the whole network over one batch.
+
+  value     whole-job images/s with the input batch already resident in HBM (CUDA events, max
+            over ranks).
+  e2e       the same through the host-buffer entry point b200_case_run_host: pinned host input
+            copied host->device and the logits copied device->host inside every step.
+  roofline  the tensor-core convolution kernel (all of its launches in a step): algorithmic bytes
+            and ops over the kernel's own time, measured with CUDA events around every launch.
+  cpu_baseline / --impl reference
+            the reference's CPU quant module (oracle/_ref, compiled unmodified from the reference
+            sources) on the host cores, one process per core, each running whole images.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH = 256
+WORKLOAD = "BASELINE configs[3]: ResNet-50 v1.5 int8, batch 256 per GPU, 3x224x224 uint8 input"
+SEED = 3
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm_gbs=float(d["hbm_gbs"]), bf16=float(d["bf16_tflops_sustained"]), src="measured")
+    return dict(hbm_gbs=6650.0, bf16=1400.0, src="fallback")
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks: sampled by nvidia-smi while the timed region runs
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["no samples"])
+        busy = sorted(sm)[len(sm) // 2:]   # the upper half: samples taken under load
+        return dict(sm_mhz=float(np.median(busy)), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arm: the reference quant module on the host cores
+# ---------------------------------------------------------------------------------------------
+def _cpu_worker(args):
+    kind, seed, n_images = args
+    os.environ["OMP_NUM_THREADS"] = "1"
+    import oracle
+    from nart_b200 import nets
+    spec = nets.resnet(50, seed=SEED)
+    be = oracle.ref() if kind == "reference" else oracle.port()
+    x = np.random.default_rng(seed).integers(0, 256, (n_images, 3, 224, 224), dtype=np.uint8)
+    t = time.perf_counter()
+    nets.run_cpu(spec, x, be, per_channel=(kind != "reference"))
+    return time.perf_counter() - t
+
+
+def cpu_images_per_sec(images_per_core: int = 1, procs: int | None = None):
+    """Runs `procs` processes, each pushing `images_per_core` images through the CPU module; returns
+    (images/s, kind, procs, seconds)."""
+    import multiprocessing as mp
+    import oracle
+    kind = "reference" if oracle.have_ref() else "port"
+    procs = procs or max(1, (os.cpu_count() or 1))
+    ctx = mp.get_context("spawn")
+    with ctx.Pool(procs) as pool:
+        t = time.perf_counter()
+        pool.map(_cpu_worker, [(kind, 100 + i, images_per_core) for i in range(procs)])
+        dt = time.perf_counter() - t
+    return procs * images_per_core / dt, kind, procs, dt
+
+
+def run_reference_arm(a):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    procs = max(1, min(os.cpu_count() or 1, 64))
+    import multiprocessing as mp
+    import oracle
+    kind = "reference" if oracle.have_ref() else "port"
+    ctx = mp.get_context("spawn")
+    times = []
+    with ctx.Pool(procs) as pool:
+        for step in range(a.warmup + a.steps):
+            t = time.perf_counter()
+            pool.map(_cpu_worker, [(kind, 100 + i, 1) for i in range(procs)])
+            dt = time.perf_counter() - t
+            if step >= a.warmup:
+                times.append(dt)
+    total = sum(times)
+    value = procs * len(times) / total
+    sample = "%d image(s) per step on each of %d host processes (one per core), whole ResNet-50 per image" % (1, procs)
+    line = dict(
+        impl="reference", metric="resnet50_int8_images_per_sec", value=value, unit="images/s", n_gpus=a.gpus,
+        steps=a.steps, warmup=a.warmup, ms_per_step=1e3 * total / len(times), higher_is_better=True, scaling="weak",
+        vs_baseline=None, dtype="u8", data="synthetic",
+        config=dict(workload=WORKLOAD, note="CPU arm: a step is %s; the reference reads one weight scale per layer" % sample),
+        cpu_baseline=dict(value=value, unit="images/s", cores=procs, kind=kind, sample=sample),
+        e2e=dict(value=value, unit="images/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+        gpu_launches=0)
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def conv_bytes_ops(spec, batch):
+    """Algorithmic bytes and ops of each conv op: every tensor once (1 B/element), weights and
+    bias once, 2*MACs; true dims."""
+    T = spec["tensors"]
+    out = []
+    for op in spec["ops"]:
+        if op["op"] not in ("conv", "ip"):
+            out.append(None)
+            continue
+        ti, to = T[op["ins"][0]], T[op["out"]]
+        if op["op"] == "conv":
+            k, cg, r, s = op["w"].shape
+        else:
+            k, cg, r, s = op["w"].shape[0], ti["c"], ti["h"], ti["w"]
+        ops = 2.0 * batch * to["h"] * to["w"] * k * cg * r * s
+        byts = batch * (ti["c"] * ti["h"] * ti["w"] + to["c"] * to["h"] * to["w"]) + k * cg * r * s + 4 * k
+        out.append((byts, ops))
+    return out
+
+
+def run_gpu_arm(a):
+    import torch
+    import torch.distributed as dist
+    from nart_b200 import nets
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    batch = a.batch
+    spec = nets.resnet(50, seed=SEED)
+    cs, ids = nets.to_case(spec, batch)
+    stream = torch.cuda.current_stream().cuda_stream
+    n_launch = cs.launch_count()
+
+    # host batch (pinned) and its resident copy in the case's input staging buffer
+    rng = np.random.default_rng(1000 + rank)
+    in_bytes = cs.io_bytes(False, 0) * batch
+    out_bytes = cs.io_bytes(True, 0) * batch
+    x_host = torch.from_numpy(rng.integers(0, 256, (batch, 3, 224, 224), dtype=np.uint8)).pin_memory()
+    y_host = torch.empty((batch, 1000), dtype=torch.float32).pin_memory()
+    from nart_b200._lib import check, lib
+    check(lib.b200_memcpy_h2d(cs.io_device_ptr(False, 0), x_host.data_ptr(), in_bytes, stream))
+    torch.cuda.synchronize()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput -----------------------------------------------------------
+    for _ in range(max(a.warmup, 3)):
+        cs.run_device(batch, stream)
+    torch.cuda.synchronize()
+    cs.set_profiling(True)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    per_kind = {}
+    igemm_ms = 0.0
+    igemm_launches = 0
+    igemm_bytes = igemm_ops = 0.0
+    cb = conv_bytes_ops(spec, batch)
+    e0.record()
+    for _ in range(a.steps):
+        cs.run_device(batch, stream)
+        # reading the events of this step waits for the step: the next step starts on an idle GPU,
+        # which does not change the per-step time (steps are milliseconds long, one stream)
+        prof = cs.profile()
+        for i, (ms, kind) in enumerate(prof):
+            per_kind[kind] = per_kind.get(kind, 0.0) + ms
+            if kind == 1:
+                igemm_ms += ms
+                igemm_launches += 1
+                byts, ops = cb[i - 1]   # launch 0 is the input layout kernel
+                igemm_bytes += byts
+                igemm_ops += ops
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    cs.set_profiling(False)
+    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    value = world * batch * a.steps / (ms_max / 1e3)
+
+    # ---- end to end through the host-buffer entry point ----------------------------------------
+    for _ in range(2):
+        cs.run_host_ptrs(batch, [x_host.data_ptr()], [y_host.data_ptr()], stream)
+    barrier()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    w0 = time.perf_counter()
+    for _ in range(a.steps):
+        cs.run_host_ptrs(batch, [x_host.data_ptr()], [y_host.data_ptr()], stream)
+    e3.record()
+    barrier()
+    wall_ms = (time.perf_counter() - w0) * 1e3
+    t = torch.tensor([max(e2.elapsed_time(e3), 0.0)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * batch * a.steps / (float(t.item()) / 1e3)
+    logits_checksum = float(y_host.double().abs().sum().item())
+
+    if rank == 0:
+        peaks = measured_peaks()
+        kind_names = {0: "input_layout", 1: "conv_igemm_tcgen05", 2: "conv_cuda_core", 3: "eltwise_add", 4: "relu",
+                      5: "pool", 6: "output_dequantize"}
+        tot = sum(per_kind.values())
+        breakdown = {kind_names[k]: round(v / a.steps, 4) for k, v in sorted(per_kind.items())}
+        sec = igemm_ms / 1e3
+        hbm_ach = igemm_bytes / sec / 1e9
+        tops_ach = igemm_ops / sec / 1e12
+        int8_peak = 2.0 * peaks["bf16"]
+        cpu_val, cpu_kind, cpu_procs, cpu_dt = (None, None, None, None)
+        cpu = None
+        if world == 1 and not a.no_cpu:
+            cpu_val, cpu_kind, cpu_procs, cpu_dt = cpu_images_per_sec(1)
+            cpu = dict(value=cpu_val, unit="images/s", cores=cpu_procs, kind=cpu_kind,
+                       sample="%d images in total, one whole ResNet-50 image per host process, %d processes, %.1f s"
+                              % (cpu_procs, cpu_procs, cpu_dt))
+        line = dict(
+            metric="resnet50_int8_images_per_sec", value=value, unit="images/s", n_gpus=world, steps=a.steps,
+            warmup=max(a.warmup, 3), ms_per_step=ms_max / a.steps, higher_is_better=True, scaling="weak",
+            vs_baseline=None, dtype="u8", data="synthetic",
+            config=dict(workload=WORKLOAD, batch_per_gpu=batch, parallelism="replicas x%d, batch-sharded, no collective" % world,
+                        l2="working set per step (5.6 GB of activations) is far larger than L2; no flush needed",
+                        conv_tops=igemm_ops / sec / 1e12, ms_per_step_by_kernel=breakdown,
+                        conv_gop_per_image=nets.conv_ops_per_image(spec) / 1e9, logits_checksum=logits_checksum),
+            roofline=dict(bound="hbm", achieved=hbm_ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=hbm_ach / peaks["hbm_gbs"],
+                          traffic=None, kernel="conv_igemm_i8_kernel", launches_per_step=igemm_launches // a.steps,
+                          peak_source=peaks["src"]),
+            roofline_tensor=dict(bound="tensor", achieved=tops_ach, peak=int8_peak / 1.0, unit="TOP/s",
+                                 frac=tops_ach / int8_peak,
+                                 peak_source="2 x bf16_tflops_sustained of %s (no int8 entry in MEASURED_PEAKS.json)" % peaks["src"]),
+            cpu_baseline=cpu,
+            e2e=dict(value=e2e_value, unit="images/s", h2d_bytes_per_step=in_bytes, d2h_bytes_per_step=out_bytes,
+                     wall_ms_per_step=wall_ms / a.steps),
+            gpu_launches=n_launch * a.steps,
+            clocks=clocks)
+        print(json.dumps(line))
+    cs.close()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        return run_reference_arm(a)
+    return run_gpu_arm(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -256,6 +256,16 @@ B200_API int b200_case_run_host(
     b200_stream_t stream);
 /* Number of kernels one b200_case_run_device launches. */
 B200_API int b200_case_launch_count(const b200_case_t *cs, int32_t *launches);
+/* Per-op device timing, the counterpart of the reference's per-op profiler pointcut around
+ * op->run_func (art/include/art/op.h:145-163) and its CUDA-event timer
+ * (art/modules/cuda_quant/src/cuda_timer.h).  When enabled, every launch of a run is bracketed by
+ * CUDA events on the run's stream; b200_case_profile then returns, for the last run, the
+ * milliseconds of each launch in launch order (inputs, ops, outputs) and its kind:
+ * 0 input layout/quantize, 1 conv (tensor-core path), 2 conv (CUDA-core path), 3 eltwise, 4 relu,
+ * 5 pool, 6 output layout/dequantize.  It synchronizes the stream of the last run. */
+B200_API int b200_case_set_profiling(b200_case_t *cs, int32_t enable);
+B200_API int b200_case_profile(
+    b200_case_t *cs, float *ms_per_launch, int32_t *kinds, int32_t capacity, int32_t *count);
 
 #ifdef __cplusplus
 }

@@ -120,6 +120,18 @@ class Case:
         check(lib.b200_case_launch_count(self._h, C.byref(v)))
         return v.value
 
+    def set_profiling(self, enable: bool):
+        check(lib.b200_case_set_profiling(self._h, int(enable)))
+
+    def profile(self):
+        """(ms, kind) per launch of the last profiled run, in launch order."""
+        cap = self.launch_count()
+        ms = (C.c_float * cap)()
+        kinds = (C.c_int32 * cap)()
+        n = C.c_int32()
+        check(lib.b200_case_profile(self._h, ms, kinds, cap, C.byref(n)))
+        return [(ms[i], kinds[i]) for i in range(n.value)]
+
     def run_device(self, batch: int, stream: int = 0):
         check(lib.b200_case_run_device(self._h, batch, stream))
 

@@ -64,6 +64,12 @@ struct b200_case {
     int max_batch = 0;
     bool prepared = false;
     int device = 0;
+    // per-launch timing (off by default)
+    bool profiling = false;
+    std::vector<cudaEvent_t> events;   // launches + 1
+    std::vector<int> kinds;            // kind of each launch of the last run
+    cudaStream_t last_stream = nullptr;
+    bool have_profile = false;
 };
 
 namespace {
@@ -120,6 +126,8 @@ int b200_case_destroy(b200_case_t *cs)
         cudaFree(io.staging);
     for (auto &io : cs->outputs)
         cudaFree(io.staging);
+    for (auto e : cs->events)
+        cudaEventDestroy(e);
     delete cs;
     return B200_OK;
 }
@@ -399,6 +407,20 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         return fail(B200_ERR_INVALID, "case_run: batch %d outside 0..%d", batch, cs->max_batch);
     if (batch == 0)
         return B200_OK;
+    const bool prof = cs->profiling;
+    size_t ev = 0;
+    cudaStream_t cst = as_stream(stream);
+    if (prof) {
+        cs->kinds.clear();
+        B200_CUDA_TRY(cudaEventRecord(cs->events[ev++], cst));
+    }
+    auto mark = [&](int kind) -> int {
+        if (prof) {
+            cs->kinds.push_back(kind);
+            B200_CUDA_TRY(cudaEventRecord(cs->events[ev++], cst));
+        }
+        return B200_OK;
+    };
     for (auto &io : cs->inputs) {
         CaseTensor &t = cs->tensors[io.tensor];
         if (io.is_f32)
@@ -407,13 +429,16 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         else
             B200_TRY(b200_nchw_to_nhwc_u8(
                 (const uint8_t *)io.staging, t.dev, batch, t.c, t.h, t.w, t.c_phys, 0, stream));
+        B200_TRY(mark(0));
     }
     for (auto &op : cs->ops) {
+        int kind = 0;
         CaseTensor &to = cs->tensors[op.out];
         const CaseTensor &ti = cs->tensors[op.ins[0]];
         switch (op.kind) {
         case OpKind::Conv:
             B200_TRY(b200_conv2d_run(op.conv, ti.dev, batch, to.dev, stream));
+            kind = b200_conv2d_algo(op.conv) == B200_CONV_ALGO_IGEMM ? 1 : 2;
             break;
         case OpKind::Eltwise: {
             const uint8_t *xs[4];
@@ -422,15 +447,19 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
             B200_TRY(b200_eltwise_sum_u8(
                 xs, (int)op.ins.size(), to.bytes_per_image() * batch, op.ialpha.data(), op.izp.data(),
                 op.has_coeff ? op.coeff.data() : nullptr, op.oalpha, op.ozp, op.obits, op.relu, to.dev, stream));
+            kind = 3;
             break;
         }
         case OpKind::Relu:
             B200_TRY(lut_u8_launch(ti.dev, to.dev, to.bytes_per_image() * batch, op.lut_dev, as_stream(stream)));
+            kind = 4;
             break;
         case OpKind::Pool:
             B200_TRY(pool_launch(ti.dev, to.dev, batch, ti.c_phys, op.method, op.pg, op.lut_dev, op.ptab, as_stream(stream)));
+            kind = 5;
             break;
         }
+        B200_TRY(mark(kind));
     }
     for (auto &io : cs->outputs) {
         const CaseTensor &t = cs->tensors[io.tensor];
@@ -438,6 +467,46 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
             B200_TRY(b200_dequantize_u8(t.dev, (float *)io.staging, batch, t.c, t.h, t.w, io.alpha, io.zp, 1, stream));
         else
             B200_TRY(b200_nhwc_to_nchw_u8(t.dev, (uint8_t *)io.staging, batch, t.c, t.h, t.w, t.c_phys, stream));
+        B200_TRY(mark(6));
+    }
+    if (prof) {
+        cs->last_stream = cst;
+        cs->have_profile = true;
+    }
+    return B200_OK;
+}
+
+int b200_case_set_profiling(b200_case_t *cs, int32_t enable)
+{
+    if (!cs || !cs->prepared)
+        return fail(B200_ERR_INVALID, "case_set_profiling: the case is not prepared");
+    if (enable && cs->events.empty()) {
+        size_t n = cs->inputs.size() + cs->ops.size() + cs->outputs.size() + 1;
+        for (size_t i = 0; i < n; ++i) {
+            cudaEvent_t e;
+            B200_CUDA_TRY(cudaEventCreate(&e));
+            cs->events.push_back(e);
+        }
+    }
+    cs->profiling = enable != 0;
+    cs->have_profile = false;
+    return B200_OK;
+}
+
+int b200_case_profile(b200_case_t *cs, float *ms_per_launch, int32_t *kinds, int32_t capacity, int32_t *count)
+{
+    if (!cs || !ms_per_launch || !kinds || !count)
+        return fail(B200_ERR_INVALID, "case_profile: NULL argument");
+    if (!cs->have_profile)
+        return fail(B200_ERR_INVALID, "case_profile: no profiled run yet");
+    B200_CUDA_TRY(cudaStreamSynchronize(cs->last_stream));
+    const int n = (int)cs->kinds.size();
+    *count = n;
+    if (capacity < n)
+        return fail(B200_ERR_INVALID, "case_profile: capacity %d < %d launches", capacity, n);
+    for (int i = 0; i < n; ++i) {
+        B200_CUDA_TRY(cudaEventElapsedTime(&ms_per_launch[i], cs->events[i], cs->events[i + 1]));
+        kinds[i] = cs->kinds[i];
     }
     return B200_OK;
 }
