@@ -193,6 +193,51 @@ __global__ void __launch_bounds__(256) conv_depthwise_kernel(
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Row lowering for the tensor-core path of 4-channel images (see kernels.h).  One thread builds
+// one 32-byte window: eight 4-byte pixels, two 16-byte stores.  Neighbouring threads read
+// overlapping windows, so the image is fetched from DRAM once.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) conv_lower_rows_kernel(
+    const uint32_t *__restrict__ x, uint4 *__restrict__ out, int n, int h, int w, int ow, int stride_w, int pad_w,
+    uint32_t izp4)
+{
+    const size_t total = (size_t)n * h * ow;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const int ox = (int)(idx % ow);
+        const size_t rowi = idx / ow;                       // n * h + ih
+        const uint32_t *xrow = x + rowi * w;
+        const int px0 = ox * stride_w - pad_w;
+        uint32_t v[kLowerWindow];
+#pragma unroll
+        for (int j = 0; j < kLowerWindow; ++j) {
+            const int px = px0 + j;
+            v[j] = (px >= 0 && px < w) ? __ldg(xrow + px) : izp4;
+        }
+        out[idx * 2] = make_uint4(v[0], v[1], v[2], v[3]);
+        out[idx * 2 + 1] = make_uint4(v[4], v[5], v[6], v[7]);
+    }
+}
+
+int conv_lower_rows_launch(const ConvGeom &g, const uint8_t *x, int n, uint8_t *out, cudaStream_t st)
+{
+    if (n == 0)
+        return B200_OK;
+    if (g.c != 4 || (((uintptr_t)x) & 3) != 0 || (((uintptr_t)out) & 15) != 0)
+        return fail(B200_ERR_INVALID, "conv(lower): needs a 4-channel, word-aligned input");
+    const size_t total = (size_t)n * g.h * g.ow;
+    size_t blocks = (total + 255) / 256;
+    const size_t cap = (size_t)sm_count() * 16;
+    if (blocks > cap)
+        blocks = cap;
+    conv_lower_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>(
+        reinterpret_cast<const uint32_t *>(x), reinterpret_cast<uint4 *>(out), n, g.h, g.w, g.ow, g.stride_w, g.pad_w,
+        (uint32_t)g.izp * 0x01010101u);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
 int conv_direct_launch(
     const ConvGeom &g, const ConvDirectPlan &p, const uint8_t *x, int n, uint8_t *y, int32_t *acc_out,
     cudaStream_t st)

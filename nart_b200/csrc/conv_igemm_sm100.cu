@@ -15,13 +15,16 @@
 // the reference pads with the real value 0, i.e. the byte izp.  With
 //   raw = sum_{valid taps} x * w      true = sum_{valid taps} (x - izp) * w = raw - izp * sum_{valid} w
 // the correction depends only on which taps are inside the image, i.e. on the output pixel's
-// border class.  The host builds off[class][k] = bias[k] - izp * sum_{taps valid in class} w[k] and
-// the epilogue adds the row of the pixel's class.
+// border class.  The host builds off[class][k] = bias[k] - izp * sum_{taps valid in class} w[k]; the
+// epilogue uses it folded with the requantize constants into one 64-bit addend per (class, k):
+//   rshift_rn((acc + off) * mult, shift) + ozp  ==  (acc * mult + off64) >> shift,
+//   off64 = off * mult + 2^(shift-1) + (ozp << shift).
 //
-// Warp roles (192 threads, one CTA per SM, persistent over tiles):
+// Warp roles (320 threads, one CTA per SM, persistent over tiles):
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      tensor-memory allocation, MMA issue (one elected lane)
-//   warps 2..5  epilogue: tcgen05.ld -> offsets -> requantize -> swizzled smem -> TMA store
+//   warps 2..9  epilogue (two warps per tensor-memory lane quarter, alternating 32-column chunks):
+//               tcgen05.ld -> requantize -> pack -> swizzled smem -> TMA store
 // Two accumulator stages in tensor memory let the epilogue of tile i overlap the mainloop of
 // tile i+1.  No cluster launch, no multicast.  Every wait is bounded: when one runs out the
 // kernel records a code in the status word, all roles leave their loops, tensor memory is freed
@@ -38,7 +41,9 @@ namespace b200 {
 
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;                  // two per TMEM lane quarter
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 8;
 constexpr int kAccStages = 2;
@@ -62,22 +67,24 @@ struct IgemmArgs {
     int r, s, pad_h, pad_w, stride_h, stride_w;
     int c;               // input channels
     // tiling
-    int tw, th, tn;      // M-tile box (ow, oh, image), tw*th*tn == 128
+    int tw, th, tn;      // M-tile box (ow, oh, image), tw*th*tn == 128, each a power of two
+    int tw_sh, th_sh;    // log2(tw), log2(th)
     int tiles_w, tiles_h, tiles_n, n_tiles_n;   // tile counts along ow, oh, image and Cout
     int bk;              // channels per k-block (32, 64, 128) == swizzle span of the operands
     int bn;              // output channels per tile (multiple of 16, <= 256)
     int stages;          // smem pipeline depth
-    int ob;              // bytes per row of an output staging sub-tile (<= 128, divides bn)
+    int ob, ob_sh;       // bytes per row of an output staging sub-tile (16..128, divides bn) and its log2
     uint32_t idesc;      // tcgen05 instruction descriptor
     uint32_t tmem_cols;  // columns to allocate (power of two >= 2*bn)
     // epilogue tables
-    const int32_t *off;      // [n_cls][kpad]
+    const long long *off;    // [n_cls][kpad]: off * mult + 2^(shift-1) + (ozp << shift)
     const uint32_t *mult;    // [kpad]
     const int32_t *shift;    // [kpad]
     const uint8_t *row_cls;  // [oh]
     const uint8_t *col_cls;  // [ow]
     int n_col_cls, kpad;
     int ozp, qmax, relu_lo;
+    int generic_requant;     // 1: some channel has shift < 33, use the 64-bit requantize everywhere
     int use_tma_store;       // 0: plain stores (Cout not a multiple of 16)
     uint8_t *y;
     int *status;
@@ -150,6 +157,8 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t sr
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all but the most recent store group have finished reading their shared-memory source
+__device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void prefetch_map(const CUtensorMap *map)
@@ -210,7 +219,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory"); }
 // AND-reduction of a predicate over the 128 epilogue threads (named barrier 2): every thread gets
 // the same answer, so all of them leave the tile loop together.
 __device__ __forceinline__ bool epi_bar_all(bool pred)
@@ -219,12 +228,22 @@ __device__ __forceinline__ bool epi_bar_all(bool pred)
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %1, 0;\n\t"
-        "barrier.cta.red.and.pred q, 2, 128, p;\n\t"
+        "barrier.cta.red.and.pred q, 2, %2, p;\n\t"
         "selp.u32 %0, 1, 0, q;\n\t}"
         : "=r"(out)
-        : "r"((uint32_t)pred)
+        : "r"((uint32_t)pred), "n"(kEpiThreads)
         : "memory");
     return out != 0;
+}
+
+// sat_u8 of four int32 values packed little-endian (byte 0 = a): cvt.pack.sat.u8.s32 converts two
+// values with saturation to 0..255 and merges them above the low half of a third operand.
+__device__ __forceinline__ uint32_t pack_sat_u8x4(int a, int b, int c, int d)
+{
+    uint32_t hi, out;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+    return out;
 }
 
 // Shared-memory matrix descriptor of a K-major operand tile whose rows are `bk` bytes
@@ -243,10 +262,10 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk)
 }
 
 // ---- shared memory layout (dynamic, base aligned to 1024) ---------------------------------------
-//   [stages x A tile (128 x bk)] [stages x B tile (bn x bk)] [output staging 128 x bn]
+//   [stages x A tile (128 x bk)] [stages x B tile (bn x bk)] [2 x output staging 128 x bn]
 //   [mult bn x 4][shift bn x 4] [barriers][tmem address][abort flag]
 struct SmemLayout {
-    uint32_t a, b, out, mult, shift, bars, tmem_slot, abort_flag, total;
+    uint32_t a, b, out, mult, shift, round, bars, tmem_slot, abort_flag, total;
 };
 __host__ __device__ inline SmemLayout smem_layout(int stages, int bk, int bn)
 {
@@ -258,11 +277,13 @@ __host__ __device__ inline SmemLayout smem_layout(int stages, int bk, int bn)
     uint32_t b_tile = ((uint32_t)bn * bk + 1023u) & ~1023u;
     o += (uint32_t)stages * b_tile;
     L.out = o;
-    o += (uint32_t)kTileM * bn;
+    o += 2u * (uint32_t)kTileM * bn;   // two output staging buffers, used alternately
     o = (o + 1023u) & ~1023u;
     L.mult = o;
     o += (uint32_t)bn * 4;
     L.shift = o;
+    o += (uint32_t)bn * 4;
+    L.round = o;
     o += (uint32_t)bn * 4;
     o = (o + 15u) & ~15u;
     L.bars = o;
@@ -303,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
         }
         for (int s = 0; s < kAccStages; ++s) {
             mbar_init(tfull_bar(s), 1);
-            mbar_init(tempty_bar(s), 4);   // one arrival per epilogue warp
+            mbar_init(tempty_bar(s), kEpiWarps);   // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -418,20 +439,78 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             }
         }
     } else {
-        // ================= epilogue (warps 2..5) =================
-        const int et = threadIdx.x - 64;             // 0..127
+        // ================= epilogue (warps 2..9) =================
+        const int et = threadIdx.x - 64;             // 0..kEpiThreads-1
         const int quarter = warp & 3;                // TMEM lanes 32*quarter .. +31 belong to this warp
+        const int half = (warp - 2) >> 2;            // which of the two warps of the quarter
         const int row = quarter * 32 + lane;         // accumulator row = pixel of the tile
-        uint32_t *s_mult = reinterpret_cast<uint32_t *>(smem + L.mult);
+        int32_t *s_mult = reinterpret_cast<int32_t *>(smem + L.mult);
         int32_t *s_shift = reinterpret_cast<int32_t *>(smem + L.shift);
-        uint8_t *s_out = smem + L.out;
-        const int n_sub = g.bn / g.ob;               // output sub-tiles of `ob` bytes per row
+        const int n_sub = g.bn >> g.ob_sh;           // output sub-tiles of `ob` bytes per row
         const int sw_shift = g.ob == 128 ? 0 : (g.ob == 64 ? 1 : 2);
         const int sw_mask = g.ob == 128 ? 7 : (g.ob == 64 ? 3 : (g.ob == 32 ? 1 : 0));
+        const int sw = (row >> sw_shift) & sw_mask;
+        const uint32_t out_bytes = (uint32_t)kTileM * g.bn;
+        // this thread's pixel inside a tile (tw, th are powers of two)
+        const int lw = row & (g.tw - 1), lh = (row >> g.tw_sh) & (g.th - 1), ln = row >> (g.tw_sh + g.th_sh);
         int as = 0;
         uint32_t aphase = 0;
         int cur_nt = -1;
+        int obuf = 0;                                // staging buffer of this tile (two alternate)
         bool store_pending = false;
+
+        // One 32-column chunk: requantize and write 2 x 16 bytes of this thread's row to staging.
+        // The host folded everything additive into one 64-bit constant per (border class, channel):
+        //   off64 = off * mult + 2^(shift-1) + (ozp << shift), so that
+        //   rshift_rn((acc + off) * mult, shift) + ozp == (acc * mult + off64) >> shift
+        // (one wide multiply-add; for shift >= 32 the shift acts on the high word only).
+        auto do_chunk = [&](const uint32_t (&v)[32], int c0, int ncol, const long long *off_row, uint8_t *s_out) {
+            uint32_t packed[8];
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) {
+                if (q4 * 4 < ncol) {
+                    const longlong2 oa = __ldg(reinterpret_cast<const longlong2 *>(off_row + c0 + q4 * 4));
+                    const longlong2 ob = __ldg(reinterpret_cast<const longlong2 *>(off_row + c0 + q4 * 4 + 2));
+                    const int4 m4 = *reinterpret_cast<const int4 *>(s_mult + c0 + q4 * 4);
+                    const int4 s4 = *reinterpret_cast<const int4 *>(s_shift + c0 + q4 * 4);
+                    const long long p0 = (long long)(int)v[q4 * 4 + 0] * m4.x + oa.x;
+                    const long long p1 = (long long)(int)v[q4 * 4 + 1] * m4.y + oa.y;
+                    const long long p2 = (long long)(int)v[q4 * 4 + 2] * m4.z + ob.x;
+                    const long long p3 = (long long)(int)v[q4 * 4 + 3] * m4.w + ob.y;
+                    int q0, q1, q2, q3;
+                    if (!g.generic_requant) {
+                        q0 = (int)(p0 >> 32) >> s4.x;
+                        q1 = (int)(p1 >> 32) >> s4.y;
+                        q2 = (int)(p2 >> 32) >> s4.z;
+                        q3 = (int)(p3 >> 32) >> s4.w;
+                    } else {
+                        q0 = (int)(p0 >> s4.x);
+                        q1 = (int)(p1 >> s4.y);
+                        q2 = (int)(p2 >> s4.z);
+                        q3 = (int)(p3 >> s4.w);
+                    }
+                    if (g.qmax != 255) {
+                        q0 = min(q0, g.qmax); q1 = min(q1, g.qmax); q2 = min(q2, g.qmax); q3 = min(q3, g.qmax);
+                    }
+                    // the pack saturates to 0..255; the ReLU floor is applied first
+                    packed[q4] = pack_sat_u8x4(max(q0, g.relu_lo), max(q1, g.relu_lo), max(q2, g.relu_lo), max(q3, g.relu_lo));
+                }
+            }
+            // staging: sub-tile (col / ob), row-major rows of `ob` bytes, 16-byte chunks XOR-swizzled
+            // with the row index exactly as the TMA store's swizzle mode expects
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+                if (ch * 16 < ncol) {
+                    const int col = c0 + ch * 16;
+                    const int sub = col >> g.ob_sh;
+                    const int chunk = (col & (g.ob - 1)) >> 4;
+                    uint8_t *srow = s_out + (((size_t)sub * kTileM + row) << g.ob_sh);
+                    *reinterpret_cast<uint4 *>(srow + ((chunk ^ sw) << 4))
+                        = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+                }
+            }
+        };
+
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             const int nt = tile % g.n_tiles_n;
             int mt = tile / g.n_tiles_n;
@@ -439,29 +518,30 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             mt /= g.tiles_w;
             const int thi = mt % g.tiles_h;
             const int tni = mt / g.tiles_h;
-            const int ow0 = twi * g.tw, oh0 = thi * g.th, n0 = tni * g.tn;
+            const int ow0 = twi << g.tw_sh, oh0 = thi << g.th_sh, n0 = tni * g.tn;
             const int k0 = nt * g.bn;
-            // this thread's pixel
-            const int lw = row % g.tw, lh = (row / g.tw) % g.th, ln = row / (g.tw * g.th);
             const int ow = ow0 + lw, oh = oh0 + lh, img = n0 + ln;
             const bool pix_valid = ow < g.ow && oh < g.oh && img < g.n;
             const int cls = (int)g.row_cls[min(oh, g.oh - 1)] * g.n_col_cls + (int)g.col_cls[min(ow, g.ow - 1)];
-            const int32_t *off_row = g.off + (size_t)cls * g.kpad + k0;
+            const long long *off_row = g.off + (size_t)cls * g.kpad + k0;
+            uint8_t *s_out = smem + L.out + (size_t)obuf * out_bytes;
 
-            // the previous tile's store must have finished reading the staging buffer, and the
-            // per-channel tables change with the channel tile
-            if (store_pending && et == 0)
-                tma_store_wait_read();
-            epi_bar_sync();
+            // per-channel tables change with the channel tile (all threads are past the previous
+            // tile's compute once they are through the barrier below)
             if (nt != cur_nt) {
-                for (int j = et; j < g.bn; j += 128) {
-                    s_mult[j] = g.mult[k0 + j];
-                    s_shift[j] = g.shift[k0 + j];
+                epi_bar_sync();
+                for (int j = et; j < g.bn; j += kEpiThreads) {
+                    const int sft = g.shift[k0 + j];
+                    s_mult[j] = (int)g.mult[k0 + j];
+                    s_shift[j] = g.generic_requant ? sft : sft - 32;
                 }
                 cur_nt = nt;
             }
-            epi_bar_sync();
-
+            // the store that last used this staging buffer (two tiles ago) must have read it
+            if (store_pending && et == 0)
+                tma_store_wait_read1();
+            // one barrier: makes the staging buffer and the tables safe, and makes the outcome of the
+            // bounded wait uniform over the epilogue threads
             if (!epi_bar_all(mbar_wait(tfull_bar(as), aphase, abort_flag))) {
                 if (et == 0) {
                     atomicCAS(g.status, 0, kErrEpilogueWait);
@@ -471,43 +551,31 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             }
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * g.bn);
-            for (int c0 = 0; c0 < g.bn; c0 += 32) {
-                uint32_t v[32];
-                const int ncol = min(32, g.bn - c0);   // 32, or 16 for the last chunk of bn % 32 == 16
-                if (ncol == 32)
-                    tmem_ld32(t_row + c0, v);
-                else
-                    tmem_ld16(t_row + c0, v);
-                tmem_ld_wait();
-                uint32_t packed[8];
-#pragma unroll
-                for (int q4 = 0; q4 < 8; ++q4) {
-                    if (q4 * 4 < ncol) {
-                        const int4 o4 = __ldg(reinterpret_cast<const int4 *>(off_row + c0 + q4 * 4));
-                        const int offs[4] = { o4.x, o4.y, o4.z, o4.w };
-                        int q[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int col = c0 + q4 * 4 + e;
-                            const int acc = (int)v[q4 * 4 + e] + offs[e];
-                            q[e] = sat_relu(requant_raw(acc, s_mult[col], s_shift[col], g.ozp), g.qmax, g.relu_lo);
-                        }
-                        packed[q4] = pack4(q[0], q[1], q[2], q[3]);
-                    }
+            // The two warps that share a lane quarter take alternate 32-column chunks.  Loads are
+            // issued one chunk ahead (two register buffers) so that the tensor-memory read of chunk
+            // i+1 overlaps the arithmetic of chunk i.
+            {
+                uint32_t va[32], vb[32];
+                int c0 = half * 32;
+                if (c0 < g.bn) {
+                    if (g.bn - c0 >= 32) tmem_ld32(t_row + c0, va); else tmem_ld16(t_row + c0, va);
                 }
-                // staging: sub-tile (c0 / ob), row-major rows of `ob` bytes, 16-byte chunks XOR-swizzled
-                // with the row index exactly as the TMA store's swizzle mode expects
-                const int sw = (row >> sw_shift) & sw_mask;
-#pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
-                    if (ch * 16 < ncol) {
-                        const int col = c0 + ch * 16;
-                        const int sub = col / g.ob;
-                        const int chunk = (col % g.ob) >> 4;
-                        uint8_t *srow = s_out + (size_t)sub * kTileM * g.ob + (size_t)row * g.ob;
-                        uint4 val = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
-                        *reinterpret_cast<uint4 *>(srow + ((chunk ^ sw) << 4)) = val;
+                while (c0 < g.bn) {
+                    const int c1 = c0 + 64;
+                    tmem_ld_wait();
+                    if (c1 < g.bn) {
+                        if (g.bn - c1 >= 32) tmem_ld32(t_row + c1, vb); else tmem_ld16(t_row + c1, vb);
                     }
+                    do_chunk(va, c0, min(32, g.bn - c0), off_row, s_out);
+                    if (c1 >= g.bn)
+                        break;
+                    const int c2 = c1 + 64;
+                    tmem_ld_wait();
+                    if (c2 < g.bn) {
+                        if (g.bn - c2 >= 32) tmem_ld32(t_row + c2, va); else tmem_ld16(t_row + c2, va);
+                    }
+                    do_chunk(vb, c1, min(32, g.bn - c1), off_row, s_out);
+                    c0 = c2;
                 }
             }
             // accumulator stage drained: hand it back to the MMA warp
@@ -525,8 +593,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 epi_bar_sync();
                 if (et == 0) {
                     for (int sub = 0; sub < n_sub; ++sub) {
-                        if (k0 + sub * g.ob < g.cout)
-                            tma_store_4d(&maps.y, smem_u32(s_out + (size_t)sub * kTileM * g.ob), k0 + sub * g.ob, ow0, oh0, n0);
+                        if (k0 + (sub << g.ob_sh) < g.cout)
+                            tma_store_4d(&maps.y, smem_u32(s_out + (((size_t)sub * kTileM) << g.ob_sh)), k0 + (sub << g.ob_sh), ow0, oh0, n0);
                     }
                     tma_store_commit();
                 }
@@ -534,18 +602,17 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             } else {
                 // plain stores for channel counts the TMA store cannot address (Cout % 16 != 0)
                 epi_bar_sync();
-                const int sw = (row >> sw_shift) & sw_mask;
-                if (pix_valid) {
+                if (pix_valid && half == 0) {
                     uint8_t *dst = g.y + (((size_t)img * g.oh + oh) * g.ow + ow) * g.cout + k0;
                     const int nvalid = min(g.bn, g.cout - k0);
                     for (int j = 0; j < nvalid; ++j) {
-                        const int sub = j / g.ob, cin = j % g.ob;
+                        const int sub = j >> g.ob_sh, cin = j & (g.ob - 1);
                         const int chunk = cin >> 4;
-                        dst[j] = s_out[(size_t)sub * kTileM * g.ob + (size_t)row * g.ob + ((chunk ^ sw) << 4) + (cin & 15)];
+                        dst[j] = s_out[(((size_t)sub * kTileM + row) << g.ob_sh) + ((chunk ^ sw) << 4) + (cin & 15)];
                     }
                 }
-                store_pending = false;
             }
+            obuf ^= 1;
         }
         if (store_pending && et == 0)
             tma_store_wait_all();
@@ -609,8 +676,9 @@ struct ConvIgemmPlan {
     ConvGeom g;
     int bk = 0, bn = 0, stages = 0, ob = 0, kpad = 0;
     int n_row_cls = 0, n_col_cls = 0;
+    int generic_requant = 0;
     int8_t *w_dev = nullptr;        // [kpad][r][s][c]
-    int32_t *off_dev = nullptr;     // [n_cls][kpad]
+    long long *off_dev = nullptr;   // [n_cls][kpad]
     uint32_t *mult_dev = nullptr;   // [kpad]
     int32_t *shift_dev = nullptr;   // [kpad]
     uint8_t *row_cls_dev = nullptr, *col_cls_dev = nullptr;
@@ -671,6 +739,21 @@ int conv_igemm_create(
     const ConvGeom &g, const std::vector<int8_t> &w_s8, const int32_t *bias, const uint32_t *mult,
     const int32_t *shift, ConvIgemmPlan **out)
 {
+    // The epilogue adds the accumulator offset in 64-bit arithmetic, where the reference's int32
+    // accumulator would wrap; and its folded addend needs shift <= 53 to stay inside int64.
+    {
+        long long max_bias = 0;
+        for (int k = 0; k < g.k && bias; ++k) {
+            long long b = bias[k] < 0 ? -(long long)bias[k] : (long long)bias[k];
+            if (b > max_bias)
+                max_bias = b;
+        }
+        if (max_bias + (long long)g.r * g.s * g.c * 255ll * 128ll >= (1ll << 31))
+            return fail(B200_ERR_UNSUPPORTED, "conv(igemm): the int32 accumulator could wrap");
+        for (int k = 0; k < g.k; ++k)
+            if (shift[k] > 53)
+                return fail(B200_ERR_UNSUPPORTED, "conv(igemm): shift %d of channel %d exceeds 53", shift[k], k);
+    }
     ConvIgemmPlan *p = new ConvIgemmPlan();
     p->g = g;
     p->bk = g.c % 128 == 0 ? 128 : (g.c % 64 == 0 ? 64 : 32);
@@ -701,9 +784,7 @@ int conv_igemm_create(
         int stages = kMaxStages;
         while (stages > 2 && smem_layout(stages, p->bk, p->bn).total + 1024 > 227 * 1024)
             --stages;
-        const int kblocks = g.r * g.s * (g.c / p->bk);
-        if (stages > kblocks + 1)
-            stages = kblocks + 1 < 2 ? 2 : kblocks + 1;
+        // a deep ring lets the producer run several tiles ahead when a tile has few k-blocks
         p->stages = stages;
     }
     if (smem_layout(p->stages, p->bk, p->bn).total + 1024 > 227 * 1024) {
@@ -734,7 +815,7 @@ int conv_igemm_create(
         for (int c = 0; c < g.c; ++c)
             for (int t = 0; t < taps; ++t)
                 wtap[(size_t)k * taps + t] += w_s8[((size_t)k * g.c + c) * taps + t];
-    std::vector<int32_t> off((size_t)p->n_row_cls * p->n_col_cls * p->kpad, 0);
+    std::vector<long long> off((size_t)p->n_row_cls * p->n_col_cls * p->kpad, 0);
     for (int rc = 0; rc < p->n_row_cls; ++rc)
         for (int cc = 0; cc < p->n_col_cls; ++cc)
             for (int k = 0; k < g.k; ++k) {
@@ -745,13 +826,19 @@ int conv_igemm_create(
                             if (col_valid[cc][ss])
                                 sum += wtap[(size_t)k * taps + rr * g.s + ss];
                 long long v = (long long)(bias ? bias[k] : 0) - (long long)g.izp * sum;
-                off[((size_t)rc * p->n_col_cls + cc) * p->kpad + k] = (int32_t)(uint32_t)(unsigned long long)v;
+                // the int32 accumulator offset, folded with the multiplier, the rounding term and the
+                // output zero point into the 64-bit addend of the epilogue's multiply-add
+                const long long off32 = (long long)(int32_t)(uint32_t)(unsigned long long)v;
+                off[((size_t)rc * p->n_col_cls + cc) * p->kpad + k]
+                    = off32 * (long long)mult[k] + (1ll << (shift[k] - 1)) + ((long long)g.ozp << shift[k]);
             }
     std::vector<uint32_t> multp(p->kpad, 0);
     std::vector<int32_t> shiftp(p->kpad, 33);
     for (int k = 0; k < g.k; ++k) {
         multp[k] = mult[k];
         shiftp[k] = shift[k];
+        if (shift[k] < 32)
+            p->generic_requant = 1;
     }
     auto up = [](const void *src, size_t bytes, void **dst) -> int {
         B200_CUDA_TRY(cudaMalloc(dst, bytes));
@@ -759,7 +846,7 @@ int conv_igemm_create(
         return B200_OK;
     };
     int rc = up(wp.data(), wp.size(), (void **)&p->w_dev);
-    if (rc == B200_OK) rc = up(off.data(), off.size() * 4, (void **)&p->off_dev);
+    if (rc == B200_OK) rc = up(off.data(), off.size() * 8, (void **)&p->off_dev);
     if (rc == B200_OK) rc = up(multp.data(), multp.size() * 4, (void **)&p->mult_dev);
     if (rc == B200_OK) rc = up(shiftp.data(), shiftp.size() * 4, (void **)&p->shift_dev);
     if (rc == B200_OK) rc = up(row_cls.data(), row_cls.size(), (void **)&p->row_cls_dev);
@@ -819,6 +906,9 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y)
     a.tiles_n = (n + a.tn - 1) / a.tn;
     a.n_tiles_n = p->kpad / p->bn;
     a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.ob = p->ob;
+    for (a.tw_sh = 0; (1 << a.tw_sh) < a.tw; ++a.tw_sh) {}
+    for (a.th_sh = 0; (1 << a.th_sh) < a.th; ++a.th_sh) {}
+    for (a.ob_sh = 0; (1 << a.ob_sh) < a.ob; ++a.ob_sh) {}
     // instruction descriptor: D = S32 (2 at bit 4), A = unsigned 8-bit (0 at bit 7), B = signed 8-bit
     // (1 at bit 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
     a.idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(p->bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
@@ -830,6 +920,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y)
     a.row_cls = p->row_cls_dev; a.col_cls = p->col_cls_dev;
     a.n_col_cls = p->n_col_cls; a.kpad = p->kpad;
     a.ozp = g.ozp; a.qmax = g.qmax; a.relu_lo = g.relu_lo;
+    a.generic_requant = p->generic_requant;
     a.use_tma_store = (g.k % 16 == 0) ? 1 : 0;
     a.y = y;
     B200_TRY(status_word_ptr(&a.status));

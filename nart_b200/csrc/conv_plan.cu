@@ -16,6 +16,12 @@ struct b200_conv {
     int device = 0;
     b200::ConvDirectPlan direct;
     b200::ConvIgemmPlan *igemm = nullptr;
+    // Row lowering of 4-channel inputs (the image stem): the igemm plan then runs on `g_low`, and
+    // its activation operand is a scratch tensor the lowering kernel fills on every run.
+    bool lowered = false;
+    b200::ConvGeom g_low;
+    uint8_t *scratch = nullptr;     // [n][h][ow][32]
+    size_t scratch_bytes = 0;
 };
 
 using namespace b200;
@@ -44,6 +50,7 @@ void destroy_conv(b200_conv *cv)
     cudaFree(cv->direct.shift_dev);
     if (cv->igemm)
         conv_igemm_destroy(cv->igemm);
+    cudaFree(cv->scratch);
     delete cv;
 }
 
@@ -152,17 +159,48 @@ int b200_conv2d_create(
     // ---- tensor-core plan ---------------------------------------------------------------------
     char why[256] = "";
     const bool ig_ok = conv_igemm_supported(g, why, sizeof(why)) != 0;
-    if (p->algo == B200_CONV_ALGO_IGEMM && !ig_ok) {
+    // A 4-channel image with a short kernel row is no contraction the tensor cores can take as it
+    // is (4 bytes per tap).  Gathering, for every input row and output column, the 8-pixel window
+    // the kernel row slides over gives a 32-channel tensor [n][h][ow][8 pixels x 4 channels] on
+    // which the same conv is an r x 1 kernel with stride (stride_h, 1): that is dense enough.
+    // Window cells outside the image hold the byte izp, whose contribution the epilogue's
+    // zero-point term removes exactly; cells past the kernel width get zero weights.
+    const bool low_ok = g.group == 1 && g.c == 4 && g.s <= kLowerWindow && g.k >= 16 && g.stride_h <= 2
+        && g.h >= g.stride_h;
+    if (!ig_ok && low_ok && p->algo != B200_CONV_ALGO_DIRECT) {
+        ConvGeom gl = g;
+        gl.c = kLowerWindow * 4;
+        gl.w = g.ow;
+        gl.s = 1;
+        gl.pad_w = 0;
+        gl.stride_w = 1;
+        std::vector<int8_t> w_low((size_t)g.k * gl.c * g.r, 0);   // [k][32][r][1]
+        for (int k = 0; k < g.k; ++k)
+            for (int c = 0; c < 4; ++c)
+                for (int rr = 0; rr < g.r; ++rr)
+                    for (int j = 0; j < g.s; ++j)
+                        w_low[((size_t)k * gl.c + j * 4 + c) * g.r + rr] = w_s8[(((size_t)k * 4 + c) * g.r + rr) * g.s + j];
+        rc = conv_igemm_create(gl, w_low, bias, mult.data(), shift.data(), &cv->igemm);
+        if (rc == B200_OK) {
+            cv->algo = B200_CONV_ALGO_IGEMM;
+            cv->lowered = true;
+            cv->g_low = gl;
+        } else if (rc != B200_ERR_UNSUPPORTED || p->algo == B200_CONV_ALGO_IGEMM) {
+            destroy_conv(cv);
+            return rc;
+        }
+    } else if (p->algo == B200_CONV_ALGO_IGEMM && !ig_ok) {
         destroy_conv(cv);
         return fail(B200_ERR_UNSUPPORTED, "conv: implicit-GEMM path declined: %s", why);
     }
     if (ig_ok && p->algo != B200_CONV_ALGO_DIRECT) {
         rc = conv_igemm_create(g, w_s8, bias, mult.data(), shift.data(), &cv->igemm);
-        if (rc != B200_OK) {
+        if (rc == B200_OK) {
+            cv->algo = B200_CONV_ALGO_IGEMM;
+        } else if (rc != B200_ERR_UNSUPPORTED || p->algo == B200_CONV_ALGO_IGEMM) {
             destroy_conv(cv);
             return rc;
-        }
-        cv->algo = B200_CONV_ALGO_IGEMM;
+        }   // declined under AUTO: the CUDA-core kernel runs it
     }
     *out = cv;
     return B200_OK;
@@ -201,6 +239,20 @@ int b200_conv2d_run(b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, 
         return fail(B200_ERR_INVALID, "conv: bad argument");
     if (n == 0)
         return B200_OK;
+    if (conv->lowered) {
+        const ConvGeom &g = conv->g;
+        const size_t need = (size_t)n * g.h * g.ow * (kLowerWindow * 4);
+        if (need > conv->scratch_bytes) {
+            // grow-only scratch; the first call at a given batch size allocates (and synchronizes)
+            B200_CUDA_TRY(cudaFree(conv->scratch));
+            conv->scratch = nullptr;
+            conv->scratch_bytes = 0;
+            B200_TRY(b200_malloc((void **)&conv->scratch, need));
+            conv->scratch_bytes = need;
+        }
+        B200_TRY(conv_lower_rows_launch(g, x, n, conv->scratch, as_stream(stream)));
+        return conv_igemm_launch(conv->igemm, conv->scratch, n, y, as_stream(stream));
+    }
     if (conv->algo == B200_CONV_ALGO_IGEMM)
         return conv_igemm_launch(conv->igemm, x, n, y, as_stream(stream));
     return conv_direct_launch(conv->g, conv->direct, x, n, y, nullptr, as_stream(stream));

@@ -60,6 +60,11 @@ int conv_direct_launch(
     const ConvGeom &g, const ConvDirectPlan &p, const uint8_t *x, int n, uint8_t *y, int32_t *acc_out,
     cudaStream_t st);
 
+// Row lowering of a 4-channel NHWC image: out[n][ih][ow][j*4 + c] = x[n][ih][ow*stride_w - pad_w + j][c]
+// for j < kLowerWindow, the byte izp where the pixel lies outside the image.
+constexpr int kLowerWindow = 8;
+int conv_lower_rows_launch(const ConvGeom &g, const uint8_t *x, int n, uint8_t *out, cudaStream_t st);
+
 // Implicit-GEMM (tcgen05) convolution plan; defined in conv_igemm_sm100.cu.
 struct ConvIgemmPlan;
 int conv_igemm_supported(const ConvGeom &g, char *why, size_t why_len);

@@ -214,3 +214,21 @@ def test_pool(ops, port):
     x = rng.integers(0, 256, (4, 2048, 7, 7), dtype=np.uint8)
     want = port.pool_u8(x, 1, (7, 7), (0, 0), (1, 1), 0, 0.05, 3, 0.02, 0)
     assert_same(to_host_nchw(ops.pool(to_dev_nhwc(x), 1, (7, 7), (0, 0), (1, 1), 0, 0.05, 3, 0.02, 0)), want, "resnet gap")
+
+
+@pytest.mark.parametrize("k,ks,st,pd,h,w", [(64, 7, 2, 3, 33, 35), (32, 3, 2, 1, 20, 22), (16, 3, 1, 1, 9, 8),
+                                             (48, 5, 1, 0, 12, 17), (64, 7, 2, 3, 224, 224)])
+def test_conv_four_channel_image_row_lowering(ops, port, k, ks, st, pd, h, w):
+    """4-channel (padded RGB) inputs take the tensor-core path through the row-lowering kernel."""
+    x, wt, bias, walpha = conv_inputs(k + ks + h, 2, 4, h, w, k, ks, ks)
+    wt[:, 3] = 128            # the padding channel carries zero weights
+    q = dict(ialpha=0.02, izp=97, wzp=128, oalpha=0.05 * np.sqrt(3 * ks * ks) / 2, ozp=13)
+    want = port.conv2d_u8(x, wt, bias, (st, st), (pd, pd), 1, walpha=walpha, relu=True, **q)
+    conv = ops.Conv2d(wt, bias, in_hw=(h, w), stride=(st, st), pad=(pd, pd), walpha=walpha, relu=True, **q)
+    assert conv.algo == ops.ALGO_IGEMM
+    got = to_host_nchw(conv(to_dev_nhwc(x)))
+    assert ops.device_status() == 0
+    assert_same(got, want, "row lowering k=%d ks=%d" % (k, ks))
+    # a second call at a smaller batch reuses the scratch tensor
+    got1 = to_host_nchw(conv(to_dev_nhwc(x[:1])))
+    assert_same(got1, want[:1], "row lowering, smaller batch")
