@@ -20,10 +20,10 @@
 //   rshift_rn((acc + off) * mult, shift) + ozp  ==  (acc * mult + off64) >> shift,
 //   off64 = off * mult + 2^(shift-1) + (ozp << shift).
 //
-// Warp roles (320 threads, one CTA per SM, persistent over tiles):
+// Warp roles (576 threads, one CTA per SM, persistent over tiles):
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      tensor-memory allocation, MMA issue (one elected lane)
-//   warps 2..9  epilogue (two warps per tensor-memory lane quarter, alternating 32-column chunks):
+//   warps 2..17 epilogue (four warps per tensor-memory lane quarter, 32-column chunks round-robin):
 //               tcgen05.ld -> requantize -> pack -> swizzled smem -> TMA store
 // Two accumulator stages in tensor memory let the epilogue of tile i overlap the mainloop of
 // tile i+1.  No cluster launch, no multicast.  Every wait is bounded: when one runs out the
@@ -41,7 +41,8 @@ namespace b200 {
 
 namespace {
 
-constexpr int kEpiWarps = 8;                  // two per TMEM lane quarter
+constexpr int kWarpsPerQuarter = 4;           // epilogue warps per tensor-memory lane quarter
+constexpr int kEpiWarps = 4 * kWarpsPerQuarter;
 constexpr int kEpiThreads = kEpiWarps * 32;
 constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kTileM = 128;
@@ -70,6 +71,7 @@ struct IgemmArgs {
     int tw, th, tn;      // M-tile box (ow, oh, image), tw*th*tn == 128, each a power of two
     int tw_sh, th_sh;    // log2(tw), log2(th)
     int tiles_w, tiles_h, tiles_n, n_tiles_n;   // tile counts along ow, oh, image and Cout
+    int step_nt, step_w, step_h, step_n;        // mixed-radix digits of the grid size (see TileWalker)
     int bk;              // channels per k-block (32, 64, 128) == swizzle span of the operands
     int bn;              // output channels per tile (multiple of 16, <= 256)
     int stages;          // smem pipeline depth
@@ -88,6 +90,35 @@ struct IgemmArgs {
     int use_tma_store;       // 0: plain stores (Cout not a multiple of 16)
     uint8_t *y;
     int *status;
+};
+
+// Tile index -> (Cout tile, ow tile, oh tile, image tile), Cout tile fastest.  A persistent CTA
+// visits tiles blockIdx.x, blockIdx.x + gridDim.x, ...: the digits advance by the mixed-radix
+// digits of gridDim.x (computed on the host) with carries, so no role divides inside its loop.
+struct TileWalker {
+    int nt, twi, thi, tni;
+    __device__ __forceinline__ void init(const IgemmArgs &g, int tile)
+    {
+        nt = tile % g.n_tiles_n;
+        int mt = tile / g.n_tiles_n;
+        twi = mt % g.tiles_w;
+        mt /= g.tiles_w;
+        thi = mt % g.tiles_h;
+        tni = mt / g.tiles_h;
+    }
+    __device__ __forceinline__ void advance(const IgemmArgs &g)
+    {
+        nt += g.step_nt;
+        int carry = 0;
+        if (nt >= g.n_tiles_n) { nt -= g.n_tiles_n; carry = 1; }
+        twi += g.step_w + carry;
+        carry = 0;
+        if (twi >= g.tiles_w) { twi -= g.tiles_w; carry = 1; }
+        thi += g.step_h + carry;
+        carry = 0;
+        if (thi >= g.tiles_h) { thi -= g.tiles_h; carry = 1; }
+        tni += g.step_n + carry;
+    }
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -348,41 +379,42 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
 
     if (warp == 0) {
         // ================= TMA producer =================
+        // One thread: every instruction here is on the critical path of the pipeline, so the
+        // loop carries its coordinates incrementally (no divisions).
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int nt = tile % g.n_tiles_n;
-                int mt = tile / g.n_tiles_n;
-                const int twi = mt % g.tiles_w;
-                mt /= g.tiles_w;
-                const int thi = mt % g.tiles_h;
-                const int tni = mt / g.tiles_h;
-                const int ow0 = twi * g.tw, oh0 = thi * g.th, n0 = tni * g.tn;
+            TileWalker tw;
+            tw.init(g, blockIdx.x);
+            const uint32_t tx_bytes = a_tile_bytes + (uint32_t)g.bn * g.bk;
+            const int sh_h = g.stride_h - 1, sh_w = g.stride_w - 1;   // strides are 1 or 2
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, tw.advance(g)) {
+                const int ow0 = tw.twi << g.tw_sh, oh0 = tw.thi << g.th_sh, n0 = tw.tni * g.tn;
+                const int bn0 = tw.nt * g.bn;
+                int kcoord = 0;
                 for (int rr = 0; rr < g.r && ok; ++rr) {
-                    // input row of output row oh for this tap: ih = oh*stride + rr - pad
-                    //   = stride * (oh + floor(d / stride)) + (d mod stride),  d = rr - pad
+                    // input row of output row oh for this tap: ih = oh*stride + d, d = rr - pad
+                    //   = stride * (oh + (d - p) / stride) + p with p = d mod stride (0 <= p < stride)
                     const int dh = rr - g.pad_h;
-                    const int ph = ((dh % g.stride_h) + g.stride_h) % g.stride_h;
-                    const int qh = (dh - ph) / g.stride_h;
+                    const int ph = dh & sh_h;
+                    const int yh = oh0 + ((dh - ph) >> sh_h);
                     for (int ss = 0; ss < g.s && ok; ++ss) {
                         const int dw = ss - g.pad_w;
-                        const int pw = ((dw % g.stride_w) + g.stride_w) % g.stride_w;
-                        const int qw = (dw - pw) / g.stride_w;
+                        const int pw = dw & sh_w;
+                        const int xw = ow0 + ((dw - pw) >> sh_w);
                         const CUtensorMap *amap = &maps.a[ph * 2 + pw];
-                        for (int cc = 0; cc < cchunks; ++cc) {
+                        for (int cc = 0; cc < g.c; cc += g.bk, kcoord += g.bk) {
                             if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
                                 atomicCAS(g.status, 0, kErrProducerWait);
                                 *abort_flag = 1;
                                 ok = false;
                                 break;
                             }
-                            mbar_expect_tx(full_bar(stage), a_tile_bytes + (uint32_t)g.bn * g.bk);
-                            tma_load_4d(base + L.a + stage * a_tile_bytes, amap, full_bar(stage),
-                                        cc * g.bk, ow0 + qw, oh0 + qh, n0);
-                            tma_load_2d(base + L.b + stage * b_tile_bytes, &maps.b, full_bar(stage),
-                                        ((rr * g.s + ss) * cchunks + cc) * g.bk, nt * g.bn);
+                            const uint32_t fb = full_bar(stage);
+                            mbar_expect_tx(fb, tx_bytes);
+                            tma_load_4d(base + L.a + stage * a_tile_bytes, amap, fb, cc, xw, yh, n0);
+                            tma_load_2d(base + L.b + stage * b_tile_bytes, &maps.b, fb, kcoord, bn0);
                             if (++stage == g.stages) {
                                 stage = 0;
                                 phase ^= 1;
@@ -400,6 +432,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             int as = 0;
             uint32_t aphase = 0;
             bool ok = true;
+            const uint64_t adesc0 = make_smem_desc(base + L.a, g.bk);
+            const uint64_t bdesc0 = make_smem_desc(base + L.b, g.bk);
+            const uint32_t a_step = a_tile_bytes >> 4, b_step = b_tile_bytes >> 4;   // descriptor address units
+            const int ksteps = g.bk / 32;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 if (!mbar_wait(tempty_bar(as), aphase ^ 1, abort_flag)) {
                     atomicCAS(g.status, 0, kErrMmaTmemWait);
@@ -416,9 +452,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                         break;
                     }
                     tc_fence_after();
-                    const uint64_t adesc = make_smem_desc(base + L.a + stage * a_tile_bytes, g.bk);
-                    const uint64_t bdesc = make_smem_desc(base + L.b + stage * b_tile_bytes, g.bk);
-                    const int ksteps = g.bk / 32;
+                    const uint64_t adesc = adesc0 + (uint64_t)(stage * a_step);
+                    const uint64_t bdesc = bdesc0 + (uint64_t)(stage * b_step);
                     for (int ks = 0; ks < ksteps; ++ks) {
                         // advance 32 bytes of K inside the swizzle atom: +2 in 16-byte units
                         mma_i8(d_tmem, adesc + 2ull * ks, bdesc + 2ull * ks, g.idesc, (kb | ks) != 0);
@@ -439,10 +474,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             }
         }
     } else {
-        // ================= epilogue (warps 2..9) =================
+        // ================= epilogue (warps 2..17) =================
         const int et = threadIdx.x - 64;             // 0..kEpiThreads-1
         const int quarter = warp & 3;                // TMEM lanes 32*quarter .. +31 belong to this warp
-        const int half = (warp - 2) >> 2;            // which of the two warps of the quarter
+        const int sub_warp = (warp - 2) >> 2;        // which of the warps of the quarter
         const int row = quarter * 32 + lane;         // accumulator row = pixel of the tile
         int32_t *s_mult = reinterpret_cast<int32_t *>(smem + L.mult);
         int32_t *s_shift = reinterpret_cast<int32_t *>(smem + L.shift);
@@ -511,14 +546,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             }
         };
 
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-            const int nt = tile % g.n_tiles_n;
-            int mt = tile / g.n_tiles_n;
-            const int twi = mt % g.tiles_w;
-            mt /= g.tiles_w;
-            const int thi = mt % g.tiles_h;
-            const int tni = mt / g.tiles_h;
-            const int ow0 = twi << g.tw_sh, oh0 = thi << g.th_sh, n0 = tni * g.tn;
+        TileWalker tw;
+        tw.init(g, blockIdx.x);
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tw.advance(g)) {
+            const int nt = tw.nt;
+            const int ow0 = tw.twi << g.tw_sh, oh0 = tw.thi << g.th_sh, n0 = tw.tni * g.tn;
             const int k0 = nt * g.bn;
             const int ow = ow0 + lw, oh = oh0 + lh, img = n0 + ln;
             const bool pix_valid = ow < g.ow && oh < g.oh && img < g.n;
@@ -551,32 +583,17 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             }
             tc_fence_after();
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * g.bn);
-            // The two warps that share a lane quarter take alternate 32-column chunks.  Loads are
-            // issued one chunk ahead (two register buffers) so that the tensor-memory read of chunk
-            // i+1 overlaps the arithmetic of chunk i.
-            {
-                uint32_t va[32], vb[32];
-                int c0 = half * 32;
-                if (c0 < g.bn) {
-                    if (g.bn - c0 >= 32) tmem_ld32(t_row + c0, va); else tmem_ld16(t_row + c0, va);
-                }
-                while (c0 < g.bn) {
-                    const int c1 = c0 + 64;
-                    tmem_ld_wait();
-                    if (c1 < g.bn) {
-                        if (g.bn - c1 >= 32) tmem_ld32(t_row + c1, vb); else tmem_ld16(t_row + c1, vb);
-                    }
-                    do_chunk(va, c0, min(32, g.bn - c0), off_row, s_out);
-                    if (c1 >= g.bn)
-                        break;
-                    const int c2 = c1 + 64;
-                    tmem_ld_wait();
-                    if (c2 < g.bn) {
-                        if (g.bn - c2 >= 32) tmem_ld32(t_row + c2, va); else tmem_ld16(t_row + c2, va);
-                    }
-                    do_chunk(vb, c1, min(32, g.bn - c1), off_row, s_out);
-                    c0 = c2;
-                }
+            // The warps that share a lane quarter take 32-column chunks round-robin; with four warps
+            // per scheduler the tensor-memory read of one warp overlaps the arithmetic of the others.
+            for (int c0 = sub_warp * 32; c0 < g.bn; c0 += kWarpsPerQuarter * 32) {
+                uint32_t v[32];
+                const int ncol = min(32, g.bn - c0);   // 32, or 16 for the last chunk of bn % 32 == 16
+                if (ncol == 32)
+                    tmem_ld32(t_row + c0, v);
+                else
+                    tmem_ld16(t_row + c0, v);
+                tmem_ld_wait();
+                do_chunk(v, c0, ncol, off_row, s_out);
             }
             // accumulator stage drained: hand it back to the MMA warp
             tc_fence_before();
@@ -602,7 +619,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             } else {
                 // plain stores for channel counts the TMA store cannot address (Cout % 16 != 0)
                 epi_bar_sync();
-                if (pix_valid && half == 0) {
+                if (pix_valid && sub_warp == 0) {
                     uint8_t *dst = g.y + (((size_t)img * g.oh + oh) * g.ow + ow) * g.cout + k0;
                     const int nvalid = min(g.bn, g.cout - k0);
                     for (int j = 0; j < nvalid; ++j) {
@@ -965,6 +982,15 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y)
     const int total_tiles = a.tiles_w * a.tiles_h * a.tiles_n * a.n_tiles_n;
     const int sms = sm_count();
     p->grid = dim3((unsigned)(total_tiles < sms ? total_tiles : sms));
+    {
+        int gsz = (int)p->grid.x;
+        a.step_nt = gsz % a.n_tiles_n;
+        gsz /= a.n_tiles_n;
+        a.step_w = gsz % a.tiles_w;
+        gsz /= a.tiles_w;
+        a.step_h = gsz % a.tiles_h;
+        a.step_n = gsz / a.tiles_h;
+    }
     p->smem = smem_layout(p->stages, p->bk, p->bn).total + 1024;
     if (!p->attr_set) {
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
