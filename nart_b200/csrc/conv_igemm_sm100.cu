@@ -23,10 +23,10 @@
 // Warp roles (576 threads, one CTA per SM, persistent over tiles):
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      tensor-memory allocation, MMA issue (one elected lane)
-//   warps 2..17 epilogue (four warps per tensor-memory lane quarter, 32-column chunks round-robin):
-//               tcgen05.ld -> requantize -> pack -> swizzled smem -> TMA store
+//   warps 2..17 epilogue, two groups of 8 warps (two per tensor-memory lane quarter); group i
+//               owns accumulator stage i: tcgen05.ld -> requantize -> pack -> swizzled smem -> TMA store
 // Two accumulator stages in tensor memory let the epilogue of tile i overlap the mainloop of
-// tile i+1.  No cluster launch, no multicast.  Every wait is bounded: when one runs out the
+// tile i+1 and the epilogue of tile i+1 (the other group).  No cluster launch, no multicast.  Every wait is bounded: when one runs out the
 // kernel records a code in the status word, all roles leave their loops, tensor memory is freed
 // and the kernel returns.
 #include <cuda.h>
@@ -41,13 +41,14 @@ namespace b200 {
 
 namespace {
 
-constexpr int kWarpsPerQuarter = 4;           // epilogue warps per tensor-memory lane quarter
-constexpr int kEpiWarps = 4 * kWarpsPerQuarter;
-constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kThreads = 64 + kEpiThreads;
+constexpr int kAccStages = 2;                 // accumulator stages in tensor memory = epilogue groups
+constexpr int kWarpsPerQuarter = 2;           // warps of one epilogue group per tensor-memory lane quarter
+constexpr int kGroupWarps = 4 * kWarpsPerQuarter;
+constexpr int kGroupThreads = kGroupWarps * 32;
+constexpr int kEpiWarps = kAccStages * kGroupWarps;
+constexpr int kThreads = 64 + kEpiWarps * 32;
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 8;
-constexpr int kAccStages = 2;
 constexpr long long kWaitCycles = 4000000000ll;   // ~2 s at 1.9 GHz
 
 // device status codes (which wait gave up)
@@ -84,7 +85,7 @@ struct IgemmArgs {
     const int32_t *shift;    // [kpad]
     const uint8_t *row_cls;  // [oh]
     const uint8_t *col_cls;  // [ow]
-    int n_col_cls, kpad;
+    int n_col_cls, n_cls, kpad;
     int ozp, qmax, relu_lo;
     int generic_requant;     // 1: some channel has shift < 33, use the 64-bit requantize everywhere
     int use_tma_store;       // 0: plain stores (Cout not a multiple of 16)
@@ -250,19 +251,23 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory"); }
-// AND-reduction of a predicate over the 128 epilogue threads (named barrier 2): every thread gets
+// Named barriers of one epilogue group (ids 1, 2 for group 0 and 3, 4 for group 1).
+__device__ __forceinline__ void epi_bar_sync(int group)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + 2 * group), "n"(kGroupThreads) : "memory");
+}
+// AND-reduction of a predicate over the threads of one epilogue group: every thread gets
 // the same answer, so all of them leave the tile loop together.
-__device__ __forceinline__ bool epi_bar_all(bool pred)
+__device__ __forceinline__ bool epi_bar_all(int group, bool pred)
 {
     uint32_t out;
     asm volatile(
         "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %1, 0;\n\t"
-        "barrier.cta.red.and.pred q, 2, %2, p;\n\t"
+        "barrier.cta.red.and.pred q, %3, %2, p;\n\t"
         "selp.u32 %0, 1, 0, q;\n\t}"
         : "=r"(out)
-        : "r"((uint32_t)pred), "n"(kEpiThreads)
+        : "r"((uint32_t)pred), "n"(kGroupThreads), "r"(2 + 2 * group)
         : "memory");
     return out != 0;
 }
@@ -294,9 +299,9 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk)
 
 // ---- shared memory layout (dynamic, base aligned to 1024) ---------------------------------------
 //   [stages x A tile (128 x bk)] [stages x B tile (bn x bk)] [2 x output staging 128 x bn]
-//   [mult bn x 4][shift bn x 4] [barriers][tmem address][abort flag]
+//   [2 x (mult bn x 4, shift bn x 4, offsets bn x 8)] [barriers][tmem address][abort flag]
 struct SmemLayout {
-    uint32_t a, b, out, mult, shift, round, bars, tmem_slot, abort_flag, total;
+    uint32_t a, b, out, tables, bars, tmem_slot, abort_flag, total;
 };
 __host__ __device__ inline SmemLayout smem_layout(int stages, int bk, int bn)
 {
@@ -310,12 +315,8 @@ __host__ __device__ inline SmemLayout smem_layout(int stages, int bk, int bn)
     L.out = o;
     o += 2u * (uint32_t)kTileM * bn;   // two output staging buffers, used alternately
     o = (o + 1023u) & ~1023u;
-    L.mult = o;
-    o += (uint32_t)bn * 4;
-    L.shift = o;
-    o += (uint32_t)bn * 4;
-    L.round = o;
-    o += (uint32_t)bn * 4;
+    L.tables = o;                      // per epilogue group: mult[bn], shift[bn] (int32), off[bn] (int64)
+    o += (uint32_t)kAccStages * bn * 16;
     o = (o + 15u) & ~15u;
     L.bars = o;
     o += (2 * kMaxStages + 2 * kAccStages) * 8;
@@ -355,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
         }
         for (int s = 0; s < kAccStages; ++s) {
             mbar_init(tfull_bar(s), 1);
-            mbar_init(tempty_bar(s), kEpiWarps);   // one arrival per epilogue warp
+            mbar_init(tempty_bar(s), kGroupWarps);   // one arrival per warp of the stage's epilogue group
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -475,12 +476,20 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
         }
     } else {
         // ================= epilogue (warps 2..17) =================
-        const int et = threadIdx.x - 64;             // 0..kEpiThreads-1
+        // Two independent groups of 8 warps; group i owns accumulator stage i, i.e. every second
+        // tile of this CTA, with its own staging buffer, tables and named barriers, so that one
+        // group's waits and barriers overlap the other group's arithmetic.
+        const int group = (warp - 2) / kGroupWarps;
+        const int gw = (warp - 2) % kGroupWarps;     // warp inside the group
+        const int et = gw * 32 + lane;               // thread inside the group, 0..kGroupThreads-1
         const int quarter = warp & 3;                // TMEM lanes 32*quarter .. +31 belong to this warp
-        const int sub_warp = (warp - 2) >> 2;        // which of the warps of the quarter
+        const int sub_warp = gw >> 2;                // which of the group's warps of that quarter
         const int row = quarter * 32 + lane;         // accumulator row = pixel of the tile
-        int32_t *s_mult = reinterpret_cast<int32_t *>(smem + L.mult);
-        int32_t *s_shift = reinterpret_cast<int32_t *>(smem + L.shift);
+        uint8_t *tables = smem + L.tables + (size_t)group * g.bn * 16;
+        int32_t *s_mult = reinterpret_cast<int32_t *>(tables);
+        int32_t *s_shift = s_mult + g.bn;
+        long long *s_off = reinterpret_cast<long long *>(tables + (size_t)g.bn * 8);
+        const bool single_class = g.n_cls == 1;      // 1x1 / unpadded convs: one offset row for all pixels
         const int n_sub = g.bn >> g.ob_sh;           // output sub-tiles of `ob` bytes per row
         const int sw_shift = g.ob == 128 ? 0 : (g.ob == 64 ? 1 : 2);
         const int sw_mask = g.ob == 128 ? 7 : (g.ob == 64 ? 3 : (g.ob == 32 ? 1 : 0));
@@ -488,24 +497,30 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
         const uint32_t out_bytes = (uint32_t)kTileM * g.bn;
         // this thread's pixel inside a tile (tw, th are powers of two)
         const int lw = row & (g.tw - 1), lh = (row >> g.tw_sh) & (g.th - 1), ln = row >> (g.tw_sh + g.th_sh);
-        int as = 0;
+        const int as = group;                        // accumulator stage of this group
         uint32_t aphase = 0;
         int cur_nt = -1;
-        int obuf = 0;                                // staging buffer of this tile (two alternate)
         bool store_pending = false;
+        uint8_t *s_out = smem + L.out + (size_t)group * out_bytes;
 
         // One 32-column chunk: requantize and write 2 x 16 bytes of this thread's row to staging.
         // The host folded everything additive into one 64-bit constant per (border class, channel):
         //   off64 = off * mult + 2^(shift-1) + (ozp << shift), so that
         //   rshift_rn((acc + off) * mult, shift) + ozp == (acc * mult + off64) >> shift
         // (one wide multiply-add; for shift >= 32 the shift acts on the high word only).
-        auto do_chunk = [&](const uint32_t (&v)[32], int c0, int ncol, const long long *off_row, uint8_t *s_out) {
+        auto do_chunk = [&](const uint32_t (&v)[32], int c0, int ncol, const long long *off_row) {
             uint32_t packed[8];
 #pragma unroll
             for (int q4 = 0; q4 < 8; ++q4) {
                 if (q4 * 4 < ncol) {
-                    const longlong2 oa = __ldg(reinterpret_cast<const longlong2 *>(off_row + c0 + q4 * 4));
-                    const longlong2 ob = __ldg(reinterpret_cast<const longlong2 *>(off_row + c0 + q4 * 4 + 2));
+                    longlong2 oa, ob;
+                    if (single_class) {   // offsets of the only border class, staged in shared memory
+                        oa = *reinterpret_cast<const longlong2 *>(s_off + c0 + q4 * 4);
+                        ob = *reinterpret_cast<const longlong2 *>(s_off + c0 + q4 * 4 + 2);
+                    } else {
+                        oa = __ldg(reinterpret_cast<const longlong2 *>(off_row + c0 + q4 * 4));
+                        ob = __ldg(reinterpret_cast<const longlong2 *>(off_row + c0 + q4 * 4 + 2));
+                    }
                     const int4 m4 = *reinterpret_cast<const int4 *>(s_mult + c0 + q4 * 4);
                     const int4 s4 = *reinterpret_cast<const int4 *>(s_shift + c0 + q4 * 4);
                     const long long p0 = (long long)(int)v[q4 * 4 + 0] * m4.x + oa.x;
@@ -548,33 +563,37 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
 
         TileWalker tw;
         tw.init(g, blockIdx.x);
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, tw.advance(g)) {
+        if (group == 1)
+            tw.advance(g);
+        for (int tile = blockIdx.x + group * gridDim.x; tile < total_tiles; tile += 2 * gridDim.x, tw.advance(g), tw.advance(g)) {
             const int nt = tw.nt;
             const int ow0 = tw.twi << g.tw_sh, oh0 = tw.thi << g.th_sh, n0 = tw.tni * g.tn;
             const int k0 = nt * g.bn;
             const int ow = ow0 + lw, oh = oh0 + lh, img = n0 + ln;
             const bool pix_valid = ow < g.ow && oh < g.oh && img < g.n;
-            const int cls = (int)g.row_cls[min(oh, g.oh - 1)] * g.n_col_cls + (int)g.col_cls[min(ow, g.ow - 1)];
-            const long long *off_row = g.off + (size_t)cls * g.kpad + k0;
-            uint8_t *s_out = smem + L.out + (size_t)obuf * out_bytes;
+            const long long *off_row = g.off + k0;
+            if (!single_class)
+                off_row += (size_t)((int)g.row_cls[min(oh, g.oh - 1)] * g.n_col_cls + (int)g.col_cls[min(ow, g.ow - 1)]) * g.kpad;
 
             // per-channel tables change with the channel tile (all threads are past the previous
             // tile's compute once they are through the barrier below)
             if (nt != cur_nt) {
-                epi_bar_sync();
-                for (int j = et; j < g.bn; j += kEpiThreads) {
+                epi_bar_sync(group);
+                for (int j = et; j < g.bn; j += kGroupThreads) {
                     const int sft = g.shift[k0 + j];
                     s_mult[j] = (int)g.mult[k0 + j];
                     s_shift[j] = g.generic_requant ? sft : sft - 32;
+                    if (single_class)
+                        s_off[j] = g.off[k0 + j];
                 }
                 cur_nt = nt;
             }
-            // the store that last used this staging buffer (two tiles ago) must have read it
+            // the group's previous store must have finished reading the staging buffer
             if (store_pending && et == 0)
-                tma_store_wait_read1();
+                tma_store_wait_read();
             // one barrier: makes the staging buffer and the tables safe, and makes the outcome of the
             // bounded wait uniform over the epilogue threads
-            if (!epi_bar_all(mbar_wait(tfull_bar(as), aphase, abort_flag))) {
+            if (!epi_bar_all(group, mbar_wait(tfull_bar(as), aphase, abort_flag))) {
                 if (et == 0) {
                     atomicCAS(g.status, 0, kErrEpilogueWait);
                     *abort_flag = 1;
@@ -593,21 +612,18 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 else
                     tmem_ld16(t_row + c0, v);
                 tmem_ld_wait();
-                do_chunk(v, c0, ncol, off_row, s_out);
+                do_chunk(v, c0, ncol, off_row);
             }
             // accumulator stage drained: hand it back to the MMA warp
             tc_fence_before();
             __syncwarp();
             if (lane == 0)
                 mbar_arrive(tempty_bar(as));
-            if (++as == kAccStages) {
-                as = 0;
-                aphase ^= 1;
-            }
+            aphase ^= 1;
 
             if (g.use_tma_store) {
                 fence_async_smem();
-                epi_bar_sync();
+                epi_bar_sync(group);
                 if (et == 0) {
                     for (int sub = 0; sub < n_sub; ++sub) {
                         if (k0 + (sub << g.ob_sh) < g.cout)
@@ -618,7 +634,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 store_pending = true;
             } else {
                 // plain stores for channel counts the TMA store cannot address (Cout % 16 != 0)
-                epi_bar_sync();
+                epi_bar_sync(group);
                 if (pix_valid && sub_warp == 0) {
                     uint8_t *dst = g.y + (((size_t)img * g.oh + oh) * g.ow + ow) * g.cout + k0;
                     const int nvalid = min(g.bn, g.cout - k0);
@@ -629,7 +645,6 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                     }
                 }
             }
-            obuf ^= 1;
         }
         if (store_pending && et == 0)
             tma_store_wait_all();
@@ -935,7 +950,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y)
     a.tmem_cols = cols;
     a.off = p->off_dev; a.mult = p->mult_dev; a.shift = p->shift_dev;
     a.row_cls = p->row_cls_dev; a.col_cls = p->col_cls_dev;
-    a.n_col_cls = p->n_col_cls; a.kpad = p->kpad;
+    a.n_col_cls = p->n_col_cls; a.n_cls = p->n_row_cls * p->n_col_cls; a.kpad = p->kpad;
     a.ozp = g.ozp; a.qmax = g.qmax; a.relu_lo = g.relu_lo;
     a.generic_requant = p->generic_requant;
     a.use_tma_store = (g.k % 16 == 0) ? 1 : 0;
