@@ -192,7 +192,27 @@ class Ref(_Common):
     per_channel = False
 
     def __init__(self):
+        # RTLD_GLOBAL: an art plugin loaded afterwards resolves the runtime's symbols against it,
+        # the way a plugin dlopen'ed by the reference's drivers resolves them against libart
+        if not os.path.exists(REF_SO):
+            raise FileNotFoundError(REF_SO)
+        C.CDLL(REF_SO, mode=C.RTLD_GLOBAL)
         super().__init__(REF_SO)
+        self._plugins = {}
+
+    def use_module(self, plugin_path=None, symbol=None, whole_batch=False, conv_relu=False):
+        """Routes every op of this object through another art module (``plugin_path`` exporting
+        the ``module_t`` named ``symbol``), or back to the reference quant module when called
+        without arguments."""
+        ptr = None
+        if plugin_path is not None:
+            if plugin_path not in self._plugins:
+                self._plugins[plugin_path] = C.CDLL(plugin_path, mode=C.RTLD_GLOBAL)
+            ptr = C.c_void_p.in_dll(self._plugins[plugin_path], symbol)
+            ptr = C.addressof(ptr)
+        self.lib.ref_use_module.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        self.lib.ref_use_module.restype = None
+        self.lib.ref_use_module(ptr, int(whole_batch), int(conv_relu))
 
     def conv2d_u8(self, x, w, bias, stride, pad, group, ialpha, izp, walpha, wzp, oalpha, ozp,
                   obits=8):

@@ -41,17 +41,35 @@
 #define REF_API __attribute__((visibility("default")))
 
 static workspace_t *g_ws = NULL;
+static const module_t *g_module = &quant_module_tp;
+static int g_whole_batch = 0;   /* run conv on the whole batch at once (the reference itself cannot) */
+static int g_conv_relu = 0;     /* set SETTING_CONV_2D_RELU_FLAG (the reference quant module ignores it) */
+
+/* Drives another art module through the very same calls: the tests point this at the b200
+ * plugin's `b200_module_tp`, which makes every function below a test of the plugin boundary. */
+REF_API void ref_use_module(const module_t *module, int whole_batch, int conv_relu)
+{
+    if (g_ws) {
+        workspace_delete(g_ws);
+        g_ws = NULL;
+    }
+    g_module = module ? module : &quant_module_tp;
+    g_whole_batch = whole_batch;
+    g_conv_relu = conv_relu;
+}
 
 static workspace_t *ws(void)
 {
     if (!g_ws)
-        g_ws = workspace_new(&quant_module_tp, NULL);
+        g_ws = workspace_new(g_module, NULL);
     return g_ws;
 }
 
 static tensor_t *new_tensor(uint32_t dtype, int dim_size, const int *dims)
 {
-    tensor_t *t = tensor_new(cpu_mem_tp, dtype);
+    /* tensors live in the workspace's own mem type, as the reference's drivers create them
+     * (tools/promark.cpp:179) */
+    tensor_t *t = tensor_new(workspace_memtype(ws()), dtype);
     int i;
     t->shape.dim_size = dim_size;
     for (i = 0; i < dim_size; ++i)
@@ -111,18 +129,29 @@ REF_API int ref_conv2d_u8(
     int r, int s, int pad_h, int pad_w, int stride_h, int stride_w, int group, float ialpha,
     uint8_t izp, float walpha, uint8_t wzp, float oalpha, uint8_t ozp, uint8_t obits, uint8_t *y)
 {
-    int xd[4] = { 1, c, h, w }, wd[4] = { k, c / group, r, s }, bd[1] = { k };
+    int per_run = g_whole_batch ? n : 1;
+    int xd[4] = { per_run, c, h, w }, wd[4] = { k, c / group, r, s }, bd[1] = { k };
     tensor_t *tx = new_tensor(dtUINT8, 4, xd);
     tensor_t *tw = new_tensor(dtUINT8, 4, wd);
     tensor_t *tb = new_tensor(dtINT32, 1, bd);
     tensor_t *in[3] = { tx, tw, tb };
     float ia[3] = { ialpha, walpha, 1.f };
     uint8_t iz[3] = { izp, wzp, 0 }, ib[3] = { 8, 8, 32 };
-    size_t xsz = (size_t)c * h * w, ysz;
+    size_t xsz = (size_t)per_run * c * h * w, ysz;
     int i;
-    op_t *op = workspace_new_op(ws(), OP_CONV_2D, 3, in);
+    op_t *op;
+    /* weights and bias are in place before prepare, as after deserialization
+     * (art/src/serialize_v2.c:211-280): a module may repack them there */
+    memcpy(mem_cpu_data(tw->mem), wt, (size_t)k * (c / group) * r * s);
+    if (bias)
+        memcpy(mem_cpu_data(tb->mem), bias, sizeof(int32_t) * k);
+    else
+        memset(mem_cpu_data(tb->mem), 0, sizeof(int32_t) * k);
+    op = workspace_new_op(ws(), OP_CONV_2D, 3, in);
     if (!op)
         return -1;
+    if (g_conv_relu)
+        CHECK(op_setting_single_set(op, SETTING_CONV_2D_RELU_FLAG, dtBOOL, 1));
     CHECK(op_setting_single_set(op, SETTING_CONV_2D_NUM_OUTPUT, dtUINT32, (uint32_t)k));
     CHECK(op_setting_single_set(op, SETTING_CONV_2D_KERNEL_H, dtUINT32, (uint32_t)r));
     CHECK(op_setting_single_set(op, SETTING_CONV_2D_KERNEL_W, dtUINT32, (uint32_t)s));
@@ -136,20 +165,15 @@ REF_API int ref_conv2d_u8(
     set_out_quant(op, oalpha, ozp, obits);
     CHECK(op_config(op));
     op_prepare(op);
-    {
+    if (g_module == &quant_module_tp) {
         op_conv_2d_t *conv_op = (op_conv_2d_t *)op;
         memset(mem_cpu_data(conv_op->temp_data), 0, mem_sizeof(conv_op->temp_data));
     }
-    memcpy(mem_cpu_data(tw->mem), wt, (size_t)k * (c / group) * r * s);
-    if (bias)
-        memcpy(mem_cpu_data(tb->mem), bias, sizeof(int32_t) * k);
-    else
-        memset(mem_cpu_data(tb->mem), 0, sizeof(int32_t) * k);
     ysz = shape_count(&op->output_tensors[0].shape);
-    for (i = 0; i < n; ++i) {
-        memcpy(mem_cpu_data(tx->mem), x + xsz * i, xsz);
+    for (i = 0; i < n; i += per_run) {
+        memcpy(mem_cpu_data(tx->mem), x + xsz * (i / per_run), xsz);
         op_run(op);
-        memcpy(y + ysz * i, mem_cpu_data(op->output_tensors[0].mem), ysz);
+        memcpy(y + ysz * (i / per_run), mem_cpu_data(op->output_tensors[0].mem), ysz);
     }
     op_delete(op);
     tensor_delete(tx);
@@ -179,13 +203,13 @@ REF_API int ref_ip_u8(
     set_w_quant(op, walpha, wzp, 8);
     set_out_quant(op, oalpha, ozp, obits);
     CHECK(op_config(op));
-    op_prepare(op);
-    memcpy(mem_cpu_data(tx->mem), x, (size_t)n * chw);
     memcpy(mem_cpu_data(tw->mem), wt, (size_t)k * chw);
     if (bias)
         memcpy(mem_cpu_data(tb->mem), bias, sizeof(int32_t) * k);
     else
         memset(mem_cpu_data(tb->mem), 0, sizeof(int32_t) * k);
+    op_prepare(op);
+    memcpy(mem_cpu_data(tx->mem), x, (size_t)n * chw);
     op_run(op);
     memcpy(y, mem_cpu_data(op->output_tensors[0].mem), (size_t)n * k);
     op_delete(op);

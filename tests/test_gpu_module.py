@@ -1,0 +1,75 @@
+"""GPU: the art plugin (libart_module_b200.so) driven through the reference's own op API --
+workspace_new_op / op_setting_*_set / op_config / op_prepare / op_run on `b200_module_tp`, by the
+same shim that drives the reference quant module -- gives the reference module's bytes.  The art
+core it runs under is the reference's, compiled unmodified into oracle/_ref."""
+import os
+
+import numpy as np
+import pytest
+
+from cases import EDGE_SHAPES, conv_inputs
+from gpu_util import assert_same
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PLUGIN = os.path.join(ROOT, "nart_b200", "libart_module_b200.so")
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "quant_ref.npz"))
+
+
+@pytest.fixture()
+def plugin(ref):
+    if not os.path.exists(PLUGIN):
+        pytest.skip("libart_module_b200.so was not built (the art headers were not available)")
+    ref.use_module(PLUGIN, "b200_module_tp", whole_batch=True)
+    yield ref
+    ref.use_module()
+
+
+def test_plugin_conv_config0(plugin):
+    n, c, h, w, k, r, s, st, pd, g = EDGE_SHAPES[0]
+    x, wt, bias, walpha = conv_inputs(0, n, c, h, w, k, r, s, g)
+    y = plugin.conv2d_u8(x, wt, bias, (st, st), (pd, pd), g, 0.02, 128, float(walpha[0]), 128, 0.05, 0)
+    assert_same(y, GOLD["c0_scalar"], "plugin conv config 0")
+
+
+@pytest.mark.parametrize("i", range(1, len(EDGE_SHAPES)))
+def test_plugin_conv_edge_shapes(plugin, i):
+    n, c, h, w, k, r, s, st, pd, g = EDGE_SHAPES[i]
+    x, wt, bias, walpha = conv_inputs(100 + i, n, c, h, w, k, r, s, g)
+    y = plugin.conv2d_u8(x, wt, bias, (st, st), (pd, pd), g, 0.037, (37 * i) % 256, float(walpha[0]), 128,
+                         0.05 * np.sqrt(c // g * r * s) / 4, (11 * i) % 200)
+    assert_same(y, GOLD["edge%d" % i], "plugin edge%d" % i)
+
+
+def test_plugin_fused_relu_flag(ref):
+    if not os.path.exists(PLUGIN):
+        pytest.skip("plugin not built")
+    n, c, h, w, k, r, s, st, pd, g = EDGE_SHAPES[0]
+    x, wt, bias, walpha = conv_inputs(0, n, c, h, w, k, r, s, g)
+    ref.use_module(PLUGIN, "b200_module_tp", whole_batch=True, conv_relu=True)
+    try:
+        y = ref.conv2d_u8(x, wt, bias, (st, st), (pd, pd), g, 0.02, 117, float(walpha[0]), 128, 0.4, 77)
+    finally:
+        ref.use_module()
+    assert_same(y, GOLD["c0_zp_relu"], "plugin conv + relu flag")
+
+
+def test_plugin_other_ops(plugin):
+    rng = np.random.default_rng(7)
+    a = rng.integers(0, 256, (2, 32, 14, 14), dtype=np.uint8)
+    b = rng.integers(0, 256, (2, 32, 14, 14), dtype=np.uint8)
+    f = (rng.standard_normal((2, 3, 20, 20)) * 3).astype(np.float32)
+    xi = rng.integers(0, 256, (4, 512), dtype=np.uint8)
+    wi = (rng.integers(-127, 128, (100, 512)) + 128).astype(np.uint8)
+    bi = rng.integers(-4096, 4097, 100).astype(np.int32)
+    ia, iz = [0.037, 0.081], [117, 9]
+    assert_same(plugin.eltwise_sum_u8([a, b], ia, iz, 0.093, 31), GOLD["eltwise"], "eltwise")
+    assert_same(plugin.eltwise_sum_u8([a, b], ia, iz, 0.093, 31, use_add=True), GOLD["add"], "add")
+    assert_same(plugin.relu_u8(a, 0.037, 117, 0.037, 117), GOLD["relu_same"], "relu")
+    assert_same(plugin.relu_u8(a, 0.037, 117, 0.05, 20), GOLD["relu_rescale"], "relu rescale")
+    for name, m, cm in (("pool_max", 0, 0), ("pool_max_ceil", 0, 1), ("pool_ave", 1, 0), ("pool_ave_ceil", 1, 1)):
+        assert_same(plugin.pool_u8(a, m, (3, 3), (1, 1), (2, 2), cm, 0.037, 117, 0.093, 31), GOLD[name], name)
+    assert_same(plugin.pool_u8(a, 1, (14, 14), (0, 0), (1, 1), 0, 0.037, 117, 0.093, 31), GOLD["pool_gap"], "gap")
+    assert_same(plugin.quantize_u8(f, 0.037, 117), GOLD["quantize"], "quantize")
+    assert_same(plugin.dequantize_u8(a, 0.037, 117).view(np.uint32), GOLD["dequantize"].view(np.uint32), "dequantize")
+    assert_same(plugin.ip_u8(xi, wi, bi, 0.02, 100, 0.005, 128, 0.1, 50), GOLD["ip"], "ip")
