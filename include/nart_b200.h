@@ -135,6 +135,23 @@ B200_API int b200_conv2d_run_acc(
     b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, int32_t *acc,
     b200_stream_t stream);
 B200_API int b200_conv2d_destroy(b200_conv_t *conv);
+/* No counterpart in the reference.  b200_conv2d_run for callers that must not allocate: a serving
+ * loop that cannot afford the device-wide synchronization of cudaMalloc / cudaFree, or a host
+ * application that has already given all device memory to its own pool, where an allocation made
+ * from inside a plugin fails.  It applies to plans that use a scratch tensor -- the row-lowered
+ * convs of 4-channel images (c == 4, group == 1, kernel width <= 8, k >= 16; any other plan is
+ * refused with B200_ERR_INVALID) -- and keeps that tensor in a fixed 32 MiB device array inside
+ * the library instead of growing one with cudaMalloc.  The call fails with B200_ERR_UNSUPPORTED
+ * when n * h * ow * 32 bytes exceed 32 MiB (41 images of a 224x224 stride-2 stem).  It makes no
+ * cudaMalloc / cudaFree and calls no allocating routine.
+ * - The first call on a device looks up the array's device address; make that call outside any
+ *   stream capture.  Every GPU the library is used on holds the 32 MiB until the process exits.
+ * - All calls on a device share the one array: two calls whose kernels overlap on the GPU (different
+ *   streams, no dependency between them) race on it.  Calls on one stream are safe.
+ * - A bounded device-side wait that runs out is recorded in the array's own status word, which each
+ *   call clears first; b200_device_status does not report it. */
+B200_API int b200_conv2d_run_static_scratch(
+    b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, b200_stream_t stream);
 
 /* ---- ip (fully connected) -------------------------------------------------------------------
  * op_quant_ip_u8xu8_run (art/modules/quant/src/op/ip.cpp:133-209): a conv whose kernel covers

@@ -57,6 +57,7 @@ SIGNATURES = {
     "b200_conv2d_run": (C.c_int, [vp, vp, i32, vp, vp]),
     "b200_conv2d_run_acc": (C.c_int, [vp, vp, i32, vp, vp, vp]),
     "b200_conv2d_destroy": (C.c_int, [vp]),
+    "b200_conv2d_run_static_scratch": (C.c_int, [vp, vp, i32, vp, vp]),
     "b200_ip_create": (C.c_int, [i32, i32, i32, i32, f32, u8, C.POINTER(f32), i32, u8, f32, u8, u8,
                                  vp, vp, C.POINTER(vp)]),
     "b200_quantize_u8": (C.c_int, [vp, vp, i32, i32, i32, i32, f32, u8, u8, i32, vp]),

@@ -718,6 +718,7 @@ struct ConvIgemmPlan {
     const uint8_t *last_x = nullptr;
     uint8_t *last_y = nullptr;
     int last_n = -1;
+    int *last_status = nullptr;
     IgemmMaps maps;
     IgemmArgs args;
     dim3 grid;
@@ -922,7 +923,7 @@ static void choose_tile(int ow, int oh, int n, int *tw, int *th, int *tn)
         }
 }
 
-static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y)
+static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, int *status_word)
 {
     const ConvGeom &g = p->g;
     if ((((uintptr_t)x | (uintptr_t)y) & 15) != 0)
@@ -955,7 +956,10 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y)
     a.generic_requant = p->generic_requant;
     a.use_tma_store = (g.k % 16 == 0) ? 1 : 0;
     a.y = y;
-    B200_TRY(status_word_ptr(&a.status));
+    if (status_word)
+        a.status = status_word;       // caller-provided word (the allocation-free entry point)
+    else
+        B200_TRY(status_word_ptr(&a.status));
 
     // ---- tensor maps -------------------------------------------------------------------------------
     const CUtensorMapSwizzle sw_ab = swizzle_for(p->bk);
@@ -1014,15 +1018,16 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y)
     p->last_x = x;
     p->last_y = y;
     p->last_n = n;
+    p->last_status = status_word;
     return B200_OK;
 }
 
-int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cudaStream_t st)
+int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cudaStream_t st, int *status_word)
 {
     if (n == 0)
         return B200_OK;
-    if (p->last_x != x || p->last_y != y || p->last_n != n)
-        B200_TRY(build_launch(p, x, n, y));
+    if (p->last_x != x || p->last_y != y || p->last_n != n || p->last_status != status_word)
+        B200_TRY(build_launch(p, x, n, y, status_word));
     conv_igemm_i8_kernel<<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;

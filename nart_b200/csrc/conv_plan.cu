@@ -10,20 +10,6 @@
 #include "common.cuh"
 #include "kernels.h"
 
-struct b200_conv {
-    b200::ConvGeom g;
-    int algo = B200_CONV_ALGO_DIRECT;
-    int device = 0;
-    b200::ConvDirectPlan direct;
-    b200::ConvIgemmPlan *igemm = nullptr;
-    // Row lowering of 4-channel inputs (the image stem): the igemm plan then runs on `g_low`, and
-    // its activation operand is a scratch tensor the lowering kernel fills on every run.
-    bool lowered = false;
-    b200::ConvGeom g_low;
-    uint8_t *scratch = nullptr;     // [n][h][ow][32]
-    size_t scratch_bytes = 0;
-};
-
 using namespace b200;
 
 namespace {

@@ -71,7 +71,25 @@ int conv_igemm_supported(const ConvGeom &g, char *why, size_t why_len);
 int conv_igemm_create(
     const ConvGeom &g, const std::vector<int8_t> &w_s8 /* [k][c][r][s] */, const int32_t *bias,
     const uint32_t *mult, const int32_t *shift, ConvIgemmPlan **plan);
-int conv_igemm_launch(ConvIgemmPlan *plan, const uint8_t *x, int n, uint8_t *y, cudaStream_t st);
+// status_word: device int that a bounded wait writes its code into; nullptr = the per-device word
+// that b200_device_status reads.
+int conv_igemm_launch(ConvIgemmPlan *plan, const uint8_t *x, int n, uint8_t *y, cudaStream_t st,
+                      int *status_word = nullptr);
 void conv_igemm_destroy(ConvIgemmPlan *plan);
 
 }  // namespace b200
+
+// A prepared convolution (the handle of the C-ABI).
+struct b200_conv {
+    b200::ConvGeom g;
+    int algo = B200_CONV_ALGO_DIRECT;
+    int device = 0;
+    b200::ConvDirectPlan direct;
+    b200::ConvIgemmPlan *igemm = nullptr;
+    // Row lowering of 4-channel inputs (the image stem): the igemm plan then runs on `g_low`, and
+    // its activation operand is a scratch tensor the lowering kernel fills on every run.
+    bool lowered = false;
+    b200::ConvGeom g_low;
+    uint8_t *scratch = nullptr;     // [n][h][ow][32]
+    size_t scratch_bytes = 0;
+};
