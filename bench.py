@@ -189,14 +189,11 @@ def conv_bytes_ops(spec, batch):
 def run_gpu_arm(a):
     import torch
     import torch.distributed as dist
-    from nart_b200 import nets
+    from nart_b200 import nets, replicas
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    rank, world, local = replicas.env_rank_world()
     torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    replicas.init("nccl", torch.device("cuda", local))
 
     batch = a.batch
     spec = nets.resnet(50, seed=SEED)
@@ -215,8 +212,7 @@ def run_gpu_arm(a):
     torch.cuda.synchronize()
 
     def barrier():
-        if world > 1:
-            dist.barrier()
+        replicas.barrier()
         torch.cuda.synchronize()
 
     # ---- device-resident throughput -----------------------------------------------------------
@@ -254,11 +250,8 @@ def run_gpu_arm(a):
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
     cs.set_profiling(False)
-    t = torch.tensor([ms_total], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_max = float(t.item())
-    value = world * batch * a.steps / (ms_max / 1e3)
+    ms_max = replicas.max_over_ranks(ms_total, "cuda")
+    value = replicas.images_per_sec(batch, a.steps, ms_total, "cuda")
 
     # ---- end to end through the host-buffer entry point ----------------------------------------
     for _ in range(2):
@@ -272,10 +265,7 @@ def run_gpu_arm(a):
     e3.record()
     barrier()
     wall_ms = (time.perf_counter() - w0) * 1e3
-    t = torch.tensor([max(e2.elapsed_time(e3), 0.0)], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_value = world * batch * a.steps / (float(t.item()) / 1e3)
+    e2e_value = replicas.images_per_sec(batch, a.steps, e2.elapsed_time(e3), "cuda")
     logits_checksum = float(y_host.double().abs().sum().item())
 
     if rank == 0:
