@@ -103,16 +103,27 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------
 # CPU arm: the reference quant module on the host cores
 # ---------------------------------------------------------------------------------------------
-def _cpu_worker(args):
-    kind, seed, n_images = args
+_CPU_STATE = {}
+
+
+def _cpu_init(kind):
+    """Per worker process, outside any timed step: the network spec and the CPU module."""
     os.environ["OMP_NUM_THREADS"] = "1"
     import oracle
     from nart_b200 import nets
-    spec = nets.resnet(50, seed=SEED)
-    be = oracle.ref() if kind == "reference" else oracle.port()
+    _CPU_STATE["spec"] = nets.resnet(50, seed=SEED)
+    _CPU_STATE["be"] = oracle.ref() if kind == "reference" else oracle.port()
+    _CPU_STATE["kind"] = kind
+
+
+def _cpu_worker(args):
+    seed, n_images = args
+    from nart_b200 import nets
+    if n_images == 0:          # warm-up call: the worker exists and is initialised
+        return 0.0
     x = np.random.default_rng(seed).integers(0, 256, (n_images, 3, 224, 224), dtype=np.uint8)
     t = time.perf_counter()
-    nets.run_cpu(spec, x, be, per_channel=(kind != "reference"))
+    nets.run_cpu(_CPU_STATE["spec"], x, _CPU_STATE["be"], per_channel=(_CPU_STATE["kind"] != "reference"))
     return time.perf_counter() - t
 
 
@@ -124,9 +135,10 @@ def cpu_images_per_sec(images_per_core: int = 1, procs: int | None = None):
     kind = "reference" if oracle.have_ref() else "port"
     procs = procs or max(1, (os.cpu_count() or 1))
     ctx = mp.get_context("spawn")
-    with ctx.Pool(procs) as pool:
+    with ctx.Pool(procs, initializer=_cpu_init, initargs=(kind,)) as pool:
+        pool.map(_cpu_worker, [(1, 0)] * procs)          # every worker is up and initialised
         t = time.perf_counter()
-        pool.map(_cpu_worker, [(kind, 100 + i, images_per_core) for i in range(procs)])
+        pool.map(_cpu_worker, [(100 + i, images_per_core) for i in range(procs)], chunksize=1)
         dt = time.perf_counter() - t
     return procs * images_per_core / dt, kind, procs, dt
 
@@ -141,10 +153,11 @@ def run_reference_arm(a):
     kind = "reference" if oracle.have_ref() else "port"
     ctx = mp.get_context("spawn")
     times = []
-    with ctx.Pool(procs) as pool:
+    with ctx.Pool(procs, initializer=_cpu_init, initargs=(kind,)) as pool:
+        pool.map(_cpu_worker, [(1, 0)] * procs)
         for step in range(a.warmup + a.steps):
             t = time.perf_counter()
-            pool.map(_cpu_worker, [(kind, 100 + i, 1) for i in range(procs)])
+            pool.map(_cpu_worker, [(100 + i, 1) for i in range(procs)], chunksize=1)
             dt = time.perf_counter() - t
             if step >= a.warmup:
                 times.append(dt)
