@@ -297,6 +297,74 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk)
     return d;
 }
 
+// ---- epilogue arithmetic ------------------------------------------------------------------------
+struct EpiConsts {
+    const int32_t *s_mult;     // shared: per-channel multiplier of the current channel tile
+    const int32_t *s_shift;    // shared: shift - 32 (fast form) or shift (generic form)
+    const long long *s_off;    // shared: folded 64-bit addends when the layer has one border class
+    uint8_t *s_out;            // staging buffer of this epilogue group
+    int ob, ob_sh, sw, row;
+    int qmax, relu_lo;
+};
+
+// One chunk of NCOL (32 or 16) accumulator columns of this thread's row: requantize, pack, write to
+// the swizzled staging tile.  The host folded everything additive into one 64-bit constant per
+// (border class, channel):  off64 = off * mult + 2^(shift-1) + (ozp << shift), so that
+//   rshift_rn((acc + off) * mult, shift) + ozp == (acc * mult + off64) >> shift
+// -- one wide multiply-add, then a shift (of the high word alone when every shift is >= 32: FAST).
+// FAST also assumes obits == 8, where the pack's saturation to 0..255 is the whole clamp.
+// SMEM_OFF reads the addends from shared memory (layers with a single border class) instead of
+// the per-class rows in global memory.  All flags are compile-time so that the body is one
+// straight-line block of independent chains.
+template <bool FAST, bool SMEM_OFF, int NCOL>
+__device__ __forceinline__ void epi_chunk(const uint32_t (&v)[32], int c0, const long long *off_row, const EpiConsts &ec)
+{
+    uint32_t packed[NCOL / 4];
+#pragma unroll
+    for (int q4 = 0; q4 < NCOL / 4; ++q4) {
+        longlong2 oa, ob;
+        if (SMEM_OFF) {
+            oa = *reinterpret_cast<const longlong2 *>(ec.s_off + c0 + q4 * 4);
+            ob = *reinterpret_cast<const longlong2 *>(ec.s_off + c0 + q4 * 4 + 2);
+        } else {
+            oa = __ldg(reinterpret_cast<const longlong2 *>(off_row + c0 + q4 * 4));
+            ob = __ldg(reinterpret_cast<const longlong2 *>(off_row + c0 + q4 * 4 + 2));
+        }
+        const int4 m4 = *reinterpret_cast<const int4 *>(ec.s_mult + c0 + q4 * 4);
+        const int4 s4 = *reinterpret_cast<const int4 *>(ec.s_shift + c0 + q4 * 4);
+        const long long p0 = (long long)(int)v[q4 * 4 + 0] * m4.x + oa.x;
+        const long long p1 = (long long)(int)v[q4 * 4 + 1] * m4.y + oa.y;
+        const long long p2 = (long long)(int)v[q4 * 4 + 2] * m4.z + ob.x;
+        const long long p3 = (long long)(int)v[q4 * 4 + 3] * m4.w + ob.y;
+        int q0, q1, q2, q3;
+        if (FAST) {
+            q0 = (int)(p0 >> 32) >> s4.x;
+            q1 = (int)(p1 >> 32) >> s4.y;
+            q2 = (int)(p2 >> 32) >> s4.z;
+            q3 = (int)(p3 >> 32) >> s4.w;
+        } else {
+            // generic: full 64-bit shift, narrowed to int32 as the reference narrows before saturating
+            q0 = min((int)(p0 >> s4.x), ec.qmax);
+            q1 = min((int)(p1 >> s4.y), ec.qmax);
+            q2 = min((int)(p2 >> s4.z), ec.qmax);
+            q3 = min((int)(p3 >> s4.w), ec.qmax);
+        }
+        // the pack saturates to 0..255; the ReLU floor is applied first
+        packed[q4] = pack_sat_u8x4(max(q0, ec.relu_lo), max(q1, ec.relu_lo), max(q2, ec.relu_lo), max(q3, ec.relu_lo));
+    }
+    // staging: sub-tile (col / ob), row-major rows of `ob` bytes, 16-byte chunks XOR-swizzled with the
+    // row index exactly as the TMA store's swizzle mode expects
+#pragma unroll
+    for (int ch = 0; ch < NCOL / 16; ++ch) {
+        const int col = c0 + ch * 16;
+        const int sub = col >> ec.ob_sh;
+        const int chunk = (col & (ec.ob - 1)) >> 4;
+        uint8_t *srow = ec.s_out + (((size_t)sub * kTileM + ec.row) << ec.ob_sh);
+        *reinterpret_cast<uint4 *>(srow + ((chunk ^ ec.sw) << 4))
+            = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
+    }
+}
+
 // ---- shared memory layout (dynamic, base aligned to 1024) ---------------------------------------
 //   [stages x A tile (128 x bk)] [stages x B tile (bn x bk)] [2 x output staging 128 x bn]
 //   [2 x (mult bn x 4, shift bn x 4, offsets bn x 8)] [barriers][tmem address][abort flag]
@@ -503,63 +571,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
         bool store_pending = false;
         uint8_t *s_out = smem + L.out + (size_t)group * out_bytes;
 
-        // One 32-column chunk: requantize and write 2 x 16 bytes of this thread's row to staging.
-        // The host folded everything additive into one 64-bit constant per (border class, channel):
-        //   off64 = off * mult + 2^(shift-1) + (ozp << shift), so that
-        //   rshift_rn((acc + off) * mult, shift) + ozp == (acc * mult + off64) >> shift
-        // (one wide multiply-add; for shift >= 32 the shift acts on the high word only).
-        auto do_chunk = [&](const uint32_t (&v)[32], int c0, int ncol, const long long *off_row) {
-            uint32_t packed[8];
-#pragma unroll
-            for (int q4 = 0; q4 < 8; ++q4) {
-                if (q4 * 4 < ncol) {
-                    longlong2 oa, ob;
-                    if (single_class) {   // offsets of the only border class, staged in shared memory
-                        oa = *reinterpret_cast<const longlong2 *>(s_off + c0 + q4 * 4);
-                        ob = *reinterpret_cast<const longlong2 *>(s_off + c0 + q4 * 4 + 2);
-                    } else {
-                        oa = __ldg(reinterpret_cast<const longlong2 *>(off_row + c0 + q4 * 4));
-                        ob = __ldg(reinterpret_cast<const longlong2 *>(off_row + c0 + q4 * 4 + 2));
-                    }
-                    const int4 m4 = *reinterpret_cast<const int4 *>(s_mult + c0 + q4 * 4);
-                    const int4 s4 = *reinterpret_cast<const int4 *>(s_shift + c0 + q4 * 4);
-                    const long long p0 = (long long)(int)v[q4 * 4 + 0] * m4.x + oa.x;
-                    const long long p1 = (long long)(int)v[q4 * 4 + 1] * m4.y + oa.y;
-                    const long long p2 = (long long)(int)v[q4 * 4 + 2] * m4.z + ob.x;
-                    const long long p3 = (long long)(int)v[q4 * 4 + 3] * m4.w + ob.y;
-                    int q0, q1, q2, q3;
-                    if (!g.generic_requant) {
-                        q0 = (int)(p0 >> 32) >> s4.x;
-                        q1 = (int)(p1 >> 32) >> s4.y;
-                        q2 = (int)(p2 >> 32) >> s4.z;
-                        q3 = (int)(p3 >> 32) >> s4.w;
-                    } else {
-                        q0 = (int)(p0 >> s4.x);
-                        q1 = (int)(p1 >> s4.y);
-                        q2 = (int)(p2 >> s4.z);
-                        q3 = (int)(p3 >> s4.w);
-                    }
-                    if (g.qmax != 255) {
-                        q0 = min(q0, g.qmax); q1 = min(q1, g.qmax); q2 = min(q2, g.qmax); q3 = min(q3, g.qmax);
-                    }
-                    // the pack saturates to 0..255; the ReLU floor is applied first
-                    packed[q4] = pack_sat_u8x4(max(q0, g.relu_lo), max(q1, g.relu_lo), max(q2, g.relu_lo), max(q3, g.relu_lo));
-                }
-            }
-            // staging: sub-tile (col / ob), row-major rows of `ob` bytes, 16-byte chunks XOR-swizzled
-            // with the row index exactly as the TMA store's swizzle mode expects
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                if (ch * 16 < ncol) {
-                    const int col = c0 + ch * 16;
-                    const int sub = col >> g.ob_sh;
-                    const int chunk = (col & (g.ob - 1)) >> 4;
-                    uint8_t *srow = s_out + (((size_t)sub * kTileM + row) << g.ob_sh);
-                    *reinterpret_cast<uint4 *>(srow + ((chunk ^ sw) << 4))
-                        = make_uint4(packed[ch * 4], packed[ch * 4 + 1], packed[ch * 4 + 2], packed[ch * 4 + 3]);
-                }
-            }
-        };
+        const EpiConsts ec = { s_mult, s_shift, s_off, s_out, g.ob, g.ob_sh, sw, row, g.qmax, g.relu_lo };
+        const bool fast_epi = !g.generic_requant && g.qmax == 255;
 
         TileWalker tw;
         tw.init(g, blockIdx.x);
@@ -582,7 +595,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 for (int j = et; j < g.bn; j += kGroupThreads) {
                     const int sft = g.shift[k0 + j];
                     s_mult[j] = (int)g.mult[k0 + j];
-                    s_shift[j] = g.generic_requant ? sft : sft - 32;
+                    s_shift[j] = fast_epi ? sft - 32 : sft;   // the fast form shifts the high word only
                     if (single_class)
                         s_off[j] = g.off[k0 + j];
                 }
@@ -612,7 +625,19 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 else
                     tmem_ld16(t_row + c0, v);
                 tmem_ld_wait();
-                do_chunk(v, c0, ncol, off_row);
+                // the common case is one straight-line block of 32 independent chains
+                if (fast_epi && ncol == 32) {
+                    if (single_class)
+                        epi_chunk<true, true, 32>(v, c0, off_row, ec);
+                    else
+                        epi_chunk<true, false, 32>(v, c0, off_row, ec);
+                } else if (fast_epi) {
+                    epi_chunk<true, false, 16>(v, c0, off_row, ec);
+                } else if (ncol == 32) {
+                    epi_chunk<false, false, 32>(v, c0, off_row, ec);
+                } else {
+                    epi_chunk<false, false, 16>(v, c0, off_row, ec);
+                }
             }
             // accumulator stage drained: hand it back to the MMA warp
             tc_fence_before();

@@ -232,3 +232,17 @@ def test_conv_four_channel_image_row_lowering(ops, port, k, ks, st, pd, h, w):
     # a second call at a smaller batch reuses the scratch tensor
     got1 = to_host_nchw(conv(to_dev_nhwc(x[:1])))
     assert_same(got1, want[:1], "row lowering, smaller batch")
+
+
+@pytest.mark.parametrize("k", [32, 48, 16])
+def test_conv_requantize_variants_on_both_paths(ops, port, k):
+    """Epilogue variants of the tensor-core path: shifts below 32 (large scales), output widths
+    below 8 bits, channel tiles of 16 and of 48 (a 32-column chunk plus a 16-column tail)."""
+    x, wt, bias, walpha = conv_inputs(40 + k, 3, 32, 9, 10, k, 3, 3)
+    for oalpha, obits, ozp in ((0.3, 8, 11), (1e-4, 8, 100), (3e-6, 8, 7), (0.3, 7, 40), (0.5, 4, 5), (2e-5, 6, 20)):
+        q = dict(ialpha=0.02, izp=101, wzp=128, oalpha=oalpha, ozp=ozp, obits=obits)
+        for relu in (False, True):
+            want = port.conv2d_u8(x, wt, bias, (1, 1), (1, 1), 1, walpha=walpha, relu=relu, **q)
+            for algo in (ops.ALGO_DIRECT, ops.ALGO_IGEMM):
+                got = run_conv(ops, x, wt, bias, 1, 1, 1, algo, walpha=walpha, relu=relu, **q)
+                assert_same(got, want, "k=%d oalpha=%g obits=%d relu=%s algo=%d" % (k, oalpha, obits, relu, algo))
