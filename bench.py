@@ -211,7 +211,9 @@ def run_gpu_arm(a):
     batch = a.batch
     spec = nets.resnet(50, seed=SEED)
     cs, ids = nets.to_case(spec, batch)
-    stream = torch.cuda.current_stream().cuda_stream
+    side = torch.cuda.Stream()   # a stream of its own: the default stream cannot be captured into a graph
+    torch.cuda.set_stream(side)
+    stream = side.cuda_stream
     n_launch = cs.launch_count()
 
     # host batch (pinned) and its resident copy in the case's input staging buffer
@@ -229,26 +231,36 @@ def run_gpu_arm(a):
         torch.cuda.synchronize()
 
     # ---- device-resident throughput -----------------------------------------------------------
+    # The case replays its launches as one CUDA graph (eager first run, captured second run).
+    cs.use_graph(not a.no_graph)
     for _ in range(max(a.warmup, 3)):
         cs.run_device(batch, stream)
     torch.cuda.synchronize()
-    cs.set_profiling(True)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        cs.run_device(batch, stream)
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    ms_max = replicas.max_over_ranks(ms_total, "cuda")
+    value = replicas.images_per_sec(batch, a.steps, ms_total, "cuda")
+
+    # ---- the same K steps again with a CUDA-event pair around every launch: kernel times ---------
+    # (op-by-op launches on the same stream and data; the graph is bypassed while profiling is on)
+    cs.set_profiling(True)
     per_kind = {}
     igemm_ms = 0.0
     igemm_launches = 0
     igemm_bytes = igemm_ops = 0.0
     cb = conv_bytes_ops(spec, batch)
-    e0.record()
     for _ in range(a.steps):
         cs.run_device(batch, stream)
-        # reading the events of this step waits for the step: the next step starts on an idle GPU,
-        # which does not change the per-step time (steps are milliseconds long, one stream)
         prof = cs.profile()
         for i, (ms, kind) in enumerate(prof):
             per_kind[kind] = per_kind.get(kind, 0.0) + ms
@@ -258,13 +270,7 @@ def run_gpu_arm(a):
                 byts, ops = cb[i - 1]   # launch 0 is the input layout kernel
                 igemm_bytes += byts
                 igemm_ops += ops
-    e1.record()
-    barrier()
-    ms_total = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
     cs.set_profiling(False)
-    ms_max = replicas.max_over_ranks(ms_total, "cuda")
-    value = replicas.images_per_sec(batch, a.steps, ms_total, "cuda")
 
     # ---- end to end through the host-buffer entry point ----------------------------------------
     for _ in range(2):
@@ -278,6 +284,7 @@ def run_gpu_arm(a):
     e3.record()
     barrier()
     wall_ms = (time.perf_counter() - w0) * 1e3
+    clocks = sampler.stop() if rank == 0 else None
     e2e_value = replicas.images_per_sec(batch, a.steps, e2.elapsed_time(e3), "cuda")
     logits_checksum = float(y_host.double().abs().sum().item())
 
@@ -304,6 +311,8 @@ def run_gpu_arm(a):
             vs_baseline=None, dtype="u8", data="synthetic",
             config=dict(workload=WORKLOAD, batch_per_gpu=batch, parallelism="replicas x%d, batch-sharded, no collective" % world,
                         l2="working set per step (5.6 GB of activations) is far larger than L2; no flush needed",
+                        launch="one CUDA graph per step" if not a.no_graph else "op by op",
+                        kernel_times="CUDA events around every launch, a second pass of the same K steps",
                         conv_tops=igemm_ops / sec / 1e12, ms_per_step_by_kernel=breakdown,
                         conv_gop_per_image=nets.conv_ops_per_image(spec) / 1e9, logits_checksum=logits_checksum),
             roofline=dict(bound="hbm", achieved=hbm_ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=hbm_ach / peaks["hbm_gbs"],
@@ -332,6 +341,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="launch op by op instead of replaying a CUDA graph")
     a = ap.parse_args()
     if a.impl == "reference":
         return run_reference_arm(a)

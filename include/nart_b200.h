@@ -273,6 +273,12 @@ B200_API int b200_case_run_host(
     b200_stream_t stream);
 /* Number of kernels one b200_case_run_device launches. */
 B200_API int b200_case_launch_count(const b200_case_t *cs, int32_t *launches);
+/* Replays b200_case_run_device as one CUDA graph per (batch, stream) instead of launching op by op
+ * (the reference's parade_run loop, art/src/parade.c:184-197, launches one op at a time): the first
+ * run at a batch size is eager, the second is captured, later ones replay.  Off by default; ignored
+ * while profiling is on and on the default (NULL) stream, which cannot be captured.  The buffers of a
+ * case never move, so a captured graph stays valid. */
+B200_API int b200_case_use_graph(b200_case_t *cs, int32_t enable);
 /* Per-op device timing, the counterpart of the reference's per-op profiler pointcut around
  * op->run_func (art/include/art/op.h:145-163) and its CUDA-event timer
  * (art/modules/cuda_quant/src/cuda_timer.h).  When enabled, every launch of a run is bracketed by

@@ -120,6 +120,10 @@ class Case:
         check(lib.b200_case_launch_count(self._h, C.byref(v)))
         return v.value
 
+    def use_graph(self, enable: bool = True):
+        """Replay run_device as one CUDA graph per batch size (see b200_case_use_graph)."""
+        check(lib.b200_case_use_graph(self._h, int(enable)))
+
     def set_profiling(self, enable: bool):
         check(lib.b200_case_set_profiling(self._h, int(enable)))
 

@@ -70,6 +70,15 @@ struct b200_case {
     std::vector<int> kinds;            // kind of each launch of the last run
     cudaStream_t last_stream = nullptr;
     bool have_profile = false;
+    // CUDA graph of one run, per (batch, stream); off by default
+    bool use_graph = false;
+    struct Graph {
+        int batch;
+        cudaStream_t stream;
+        int runs_seen;           // eager runs at this batch before capturing (the first one allocates)
+        cudaGraphExec_t exec;
+    };
+    std::vector<Graph> graphs;
 };
 
 namespace {
@@ -128,6 +137,9 @@ int b200_case_destroy(b200_case_t *cs)
         cudaFree(io.staging);
     for (auto e : cs->events)
         cudaEventDestroy(e);
+    for (auto &gr : cs->graphs)
+        if (gr.exec)
+            cudaGraphExecDestroy(gr.exec);
     delete cs;
     return B200_OK;
 }
@@ -399,6 +411,8 @@ int b200_case_tensor_device_ptr(const b200_case_t *cs, int32_t tensor, void **de
     return B200_OK;
 }
 
+static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream);
+
 int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
 {
     if (!cs || !cs->prepared)
@@ -407,6 +421,53 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         return fail(B200_ERR_INVALID, "case_run: batch %d outside 0..%d", batch, cs->max_batch);
     if (batch == 0)
         return B200_OK;
+    // the legacy default stream cannot be captured: graph mode needs a stream of its own
+    if (!cs->use_graph || cs->profiling || stream == nullptr)
+        return run_eager(cs, batch, stream);
+    // Graph mode: the first run at a batch size is eager (plans build their tensor maps and scratch
+    // then), the second is captured, later ones replay the captured launches back to back.
+    cudaStream_t cst = as_stream(stream);
+    b200_case::Graph *gr = nullptr;
+    for (auto &g0 : cs->graphs)
+        if (g0.batch == batch && g0.stream == cst)
+            gr = &g0;
+    if (!gr) {
+        cs->graphs.push_back({ batch, cst, 0, nullptr });
+        gr = &cs->graphs.back();
+    }
+    if (gr->exec) {
+        B200_CUDA_TRY(cudaGraphLaunch(gr->exec, cst));
+        return B200_OK;
+    }
+    if (gr->runs_seen++ == 0)
+        return run_eager(cs, batch, stream);
+    cudaGraph_t graph = nullptr;
+    B200_CUDA_TRY(cudaStreamBeginCapture(cst, cudaStreamCaptureModeThreadLocal));
+    int rc = run_eager(cs, batch, stream);
+    cudaError_t ce = cudaStreamEndCapture(cst, &graph);
+    if (rc != B200_OK || ce != cudaSuccess || !graph) {
+        if (graph)
+            cudaGraphDestroy(graph);
+        cudaGetLastError();
+        cs->use_graph = false;   // something on the path cannot be captured: stay eager
+        if (rc != B200_OK)
+            return rc;
+        return run_eager(cs, batch, stream);
+    }
+    ce = cudaGraphInstantiate(&gr->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ce != cudaSuccess) {
+        gr->exec = nullptr;
+        cudaGetLastError();
+        cs->use_graph = false;
+        return run_eager(cs, batch, stream);
+    }
+    B200_CUDA_TRY(cudaGraphLaunch(gr->exec, cst));
+    return B200_OK;
+}
+
+static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream)
+{
     const bool prof = cs->profiling;
     size_t ev = 0;
     cudaStream_t cst = as_stream(stream);
@@ -476,6 +537,14 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
     return B200_OK;
 }
 
+int b200_case_use_graph(b200_case_t *cs, int32_t enable)
+{
+    if (!cs)
+        return fail(B200_ERR_INVALID, "case_use_graph: NULL argument");
+    cs->use_graph = enable != 0;
+    return B200_OK;
+}
+
 int b200_case_set_profiling(b200_case_t *cs, int32_t enable)
 {
     if (!cs || !cs->prepared)
@@ -538,7 +607,11 @@ int b200_case_launch_count(const b200_case_t *cs, int32_t *launches)
 {
     if (!cs || !launches)
         return fail(B200_ERR_INVALID, "case_launch_count: NULL argument");
-    *launches = (int)(cs->inputs.size() + cs->ops.size() + cs->outputs.size());
+    int n = (int)(cs->inputs.size() + cs->ops.size() + cs->outputs.size());
+    for (const auto &op : cs->ops)
+        if (op.conv && op.conv->lowered)
+            ++n;   // the row-lowering kernel runs ahead of the convolution kernel
+    *launches = n;
     return B200_OK;
 }
 

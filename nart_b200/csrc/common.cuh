@@ -18,10 +18,12 @@ int fail(int status, const char *fmt, ...);
 #define B200_CUDA_TRY(expr)                                                                    \
     do {                                                                                       \
         cudaError_t _e = (expr);                                                               \
-        if (_e != cudaSuccess)                                                                 \
+        if (_e != cudaSuccess) {                                                               \
+            cudaGetLastError(); /* a non-sticky error must not surface at a later, unrelated call */ \
             return ::b200::fail(                                                               \
                 B200_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, \
                 __LINE__);                                                                     \
+        }                                                                                      \
     } while (0)
 
 #define B200_TRY(expr)           \
@@ -76,6 +78,16 @@ __device__ __forceinline__ int sat_relu(int v, int qmax, int relu_lo)
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d)
 {
     return (uint32_t)a | ((uint32_t)b << 8) | ((uint32_t)c << 16) | ((uint32_t)d << 24);
+}
+
+// sat_u8 of four int32 values packed little-endian (byte 0 = a): cvt.pack.sat.u8.s32 converts two
+// values with saturation to 0..255 and merges them above the low half of a third operand.
+__device__ __forceinline__ uint32_t pack_sat_u8x4(int a, int b, int c, int d)
+{
+    uint32_t hi, out;
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+    asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+    return out;
 }
 
 // 32-bit rounded shift for operands known to satisfy |x| + 2^(b-1) < 2^31, 1 <= b <= 30.

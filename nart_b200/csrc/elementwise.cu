@@ -185,44 +185,54 @@ __device__ __forceinline__ int elt_finish(int t, const EltwiseArgs &a)
     return sat_relu(v, a.qmax, a.relu_lo);
 }
 
-template <int N_IN>
+// FAST: obits == 8 and the final rounding term 2^(s0-1) << b[0] fits into add[0] (folded there by
+// the host, exact because it is a multiple of 2^b[0]); then y = sat_u8(max((t >> s0) + ozp, relu_lo))
+// and the saturation comes with the pack.  32 bytes per input per thread and iteration.
+template <int N_IN, bool FAST>
 __global__ void __launch_bounds__(256) eltwise_sum_kernel(EltwiseArgs a, uint8_t *__restrict__ y, size_t count)
 {
+    constexpr int VPT = 2;   // 16-byte vectors per input per thread
     const size_t nvec = count / 16;
+    const size_t nchunk = nvec / VPT;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t v = (size_t)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += stride) {
-        uint32_t xin[N_IN][4];
+    for (size_t ck = (size_t)blockIdx.x * blockDim.x + threadIdx.x; ck < nchunk; ck += stride) {
+        uint32_t xin[N_IN][4 * VPT];
 #pragma unroll
-        for (int i = 0; i < N_IN; ++i) {
-            uint4 q = __ldg(reinterpret_cast<const uint4 *>(a.x[i]) + v);
-            xin[i][0] = q.x; xin[i][1] = q.y; xin[i][2] = q.z; xin[i][3] = q.w;
-        }
-        uint32_t o[4];
+        for (int i = 0; i < N_IN; ++i)
 #pragma unroll
-        for (int wd = 0; wd < 4; ++wd) {
+            for (int u = 0; u < VPT; ++u) {
+                uint4 q = __ldg(reinterpret_cast<const uint4 *>(a.x[i]) + ck * VPT + u);
+                xin[i][4 * u + 0] = q.x; xin[i][4 * u + 1] = q.y; xin[i][4 * u + 2] = q.z; xin[i][4 * u + 3] = q.w;
+            }
+        uint32_t o[4 * VPT];
+#pragma unroll
+        for (int wd = 0; wd < 4 * VPT; ++wd) {
             int r[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 int t = 0;
 #pragma unroll
                 for (int i = 0; i < N_IN; ++i) {
-                    int xv = (int)((xin[i][wd] >> (8 * e)) & 0xffu);
+                    const int xv = (int)__byte_perm(xin[i][wd], 0, 0x4440 | e);   // byte e, zero-extended
                     t += (xv * a.m[i] + a.add[i]) >> a.b[i];
                 }
-                r[e] = elt_finish(t, a);
+                r[e] = FAST ? max((t >> a.s0) + a.ozp, a.relu_lo) : elt_finish(t, a);
             }
-            o[wd] = pack4(r[0], r[1], r[2], r[3]);
+            o[wd] = FAST ? pack_sat_u8x4(r[0], r[1], r[2], r[3]) : pack4(r[0], r[1], r[2], r[3]);
         }
-        reinterpret_cast<uint4 *>(y)[v] = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+        for (int u = 0; u < VPT; ++u)
+            reinterpret_cast<uint4 *>(y)[ck * VPT + u] = make_uint4(o[4 * u], o[4 * u + 1], o[4 * u + 2], o[4 * u + 3]);
     }
-    // tail (count not a multiple of 16)
+    // tail (what is left after whole 32-byte chunks)
     if (blockIdx.x == 0) {
-        for (size_t e = nvec * 16 + threadIdx.x; e < count; e += blockDim.x) {
+        for (size_t e = nchunk * VPT * 16 + threadIdx.x; e < count; e += blockDim.x) {
             int t = 0;
 #pragma unroll
             for (int i = 0; i < N_IN; ++i)
                 t += ((int)a.x[i][e] * a.m[i] + a.add[i]) >> a.b[i];
-            y[e] = (uint8_t)elt_finish(t, a);
+            int v = FAST ? min(max((t >> a.s0) + a.ozp, 0), 255) : elt_finish(t, a);
+            y[e] = (uint8_t)(FAST ? max(v, a.relu_lo) : v);
         }
     }
 }
@@ -443,13 +453,33 @@ int b200_eltwise_sum_u8(
     a.relu_lo = relu ? ozp : 0;
     if (count == 0)
         return B200_OK;
-    int grid = grid_for(count / 16 + 1, 256, 8);
+    // fold the final rounding term into the first input's addend when that stays inside int32
+    bool fast = a.qmax == 255;
+    {
+        long long folded = (long long)a.add[0] + ((long long)a.round0 << a.b[0]);
+        long long worst = folded < 0 ? -folded : folded;
+        worst += 255ll * a.m[0];
+        if (fast && worst < (1ll << 31))
+            a.add[0] = (int)folded;
+        else
+            fast = false;
+    }
+    int grid = grid_for(count / 32 + 1, 256, 8);
     cudaStream_t st = as_stream(stream);
-    switch (n_in) {
-    case 1: eltwise_sum_kernel<1><<<grid, 256, 0, st>>>(a, y, count); break;
-    case 2: eltwise_sum_kernel<2><<<grid, 256, 0, st>>>(a, y, count); break;
-    case 3: eltwise_sum_kernel<3><<<grid, 256, 0, st>>>(a, y, count); break;
-    default: eltwise_sum_kernel<4><<<grid, 256, 0, st>>>(a, y, count); break;
+    if (fast) {
+        switch (n_in) {
+        case 1: eltwise_sum_kernel<1, true><<<grid, 256, 0, st>>>(a, y, count); break;
+        case 2: eltwise_sum_kernel<2, true><<<grid, 256, 0, st>>>(a, y, count); break;
+        case 3: eltwise_sum_kernel<3, true><<<grid, 256, 0, st>>>(a, y, count); break;
+        default: eltwise_sum_kernel<4, true><<<grid, 256, 0, st>>>(a, y, count); break;
+        }
+    } else {
+        switch (n_in) {
+        case 1: eltwise_sum_kernel<1, false><<<grid, 256, 0, st>>>(a, y, count); break;
+        case 2: eltwise_sum_kernel<2, false><<<grid, 256, 0, st>>>(a, y, count); break;
+        case 3: eltwise_sum_kernel<3, false><<<grid, 256, 0, st>>>(a, y, count); break;
+        default: eltwise_sum_kernel<4, false><<<grid, 256, 0, st>>>(a, y, count); break;
+        }
     }
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
