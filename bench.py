@@ -272,20 +272,34 @@ def run_gpu_arm(a):
                 igemm_ops += ops
     cs.set_profiling(False)
 
-    # ---- end to end through the host-buffer entry point ----------------------------------------
-    for _ in range(2):
-        cs.run_host_ptrs(batch, [x_host.data_ptr()], [y_host.data_ptr()], stream)
+    # ---- end to end through the host-buffer entry points ------------------------------------------
+    # Every step copies its 256 images host->device and its logits device->host inside the timed
+    # region.  b200_case_submit_host queues a step and returns, so the copy of step i+1 overlaps the
+    # kernels of step i; two pinned input/output buffer pairs alternate.
+    x_hosts = [x_host, x_host.clone().pin_memory()]
+    y_hosts = [y_host, torch.empty_like(y_host).pin_memory()]
+    for i in range(3):
+        cs.submit_host_ptrs(batch, [x_hosts[i % 2].data_ptr()], [y_hosts[i % 2].data_ptr()])
+    cs.wait()
     barrier()
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2.record()
+    w0 = time.perf_counter()
+    e2.record()                                        # device timestamps on the (idle) bench stream ...
+    for i in range(a.steps):
+        cs.submit_host_ptrs(batch, [x_hosts[i % 2].data_ptr()], [y_hosts[i % 2].data_ptr()])
+    cs.wait()                                          # ... around submit...wait, which drains the case's streams
+    e3.record()
+    e3.synchronize()
+    e2e_wall_ms = (time.perf_counter() - w0) * 1e3
+    e2e_ms = e2.elapsed_time(e3)
+    barrier()
+    e2e_value = replicas.images_per_sec(batch, a.steps, e2e_ms, "cuda")
+    # the blocking single-call form, for comparison
     w0 = time.perf_counter()
     for _ in range(a.steps):
         cs.run_host_ptrs(batch, [x_host.data_ptr()], [y_host.data_ptr()], stream)
-    e3.record()
-    barrier()
     wall_ms = (time.perf_counter() - w0) * 1e3
     clocks = sampler.stop() if rank == 0 else None
-    e2e_value = replicas.images_per_sec(batch, a.steps, e2.elapsed_time(e3), "cuda")
     logits_checksum = float(y_host.double().abs().sum().item())
 
     if rank == 0:
@@ -323,7 +337,9 @@ def run_gpu_arm(a):
                                  peak_source="2 x bf16_tflops_sustained of %s (no int8 entry in MEASURED_PEAKS.json)" % peaks["src"]),
             cpu_baseline=cpu,
             e2e=dict(value=e2e_value, unit="images/s", h2d_bytes_per_step=in_bytes, d2h_bytes_per_step=out_bytes,
-                     wall_ms_per_step=wall_ms / a.steps),
+                     api="b200_case_submit_host + b200_case_wait (copy of step i+1 overlaps the kernels of step i)",
+                     ms_per_step=e2e_ms / a.steps, host_clock_ms_per_step=e2e_wall_ms / a.steps,
+                     blocking_run_host_ms_per_step=wall_ms / a.steps),
             gpu_launches=n_launch * a.steps,
             clocks=clocks)
         print(json.dumps(line))

@@ -271,6 +271,15 @@ B200_API int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t 
 B200_API int b200_case_run_host(
     b200_case_t *cs, int32_t batch, const void *const *inputs, void *const *outputs,
     b200_stream_t stream);
+/* Pipelined form of b200_case_run_host for back-to-back batches: returns as soon as the work is
+ * queued on the case's own copy and compute streams, so that the host->device copy of the next
+ * batch overlaps the kernels of this one (the reference's drivers run parade_run and the copies
+ * strictly one after the other, tools/promark.cpp:457-492).  The host buffers must be pinned and
+ * stay valid -- and the outputs unread -- until b200_case_wait returns.  A later submit may reuse
+ * the same host buffers only after a wait.  b200_case_wait also returns the bounded-wait status. */
+B200_API int b200_case_submit_host(
+    b200_case_t *cs, int32_t batch, const void *const *inputs, void *const *outputs);
+B200_API int b200_case_wait(b200_case_t *cs);
 /* Number of kernels one b200_case_run_device launches. */
 B200_API int b200_case_launch_count(const b200_case_t *cs, int32_t *launches);
 /* Replays b200_case_run_device as one CUDA graph per (batch, stream) instead of launching op by op

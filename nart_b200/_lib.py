@@ -91,6 +91,8 @@ SIGNATURES = {
     "b200_case_tensor_device_ptr": (C.c_int, [vp, i32, C.POINTER(vp)]),
     "b200_case_run_device": (C.c_int, [vp, i32, vp]),
     "b200_case_run_host": (C.c_int, [vp, i32, C.POINTER(vp), C.POINTER(vp), vp]),
+    "b200_case_submit_host": (C.c_int, [vp, i32, C.POINTER(vp), C.POINTER(vp)]),
+    "b200_case_wait": (C.c_int, [vp]),
     "b200_case_launch_count": (C.c_int, [vp, pi32]),
     "b200_case_use_graph": (C.c_int, [vp, i32]),
     "b200_case_set_profiling": (C.c_int, [vp, i32]),

@@ -145,6 +145,15 @@ class Case:
         outs = (C.c_void_p * len(out_ptrs))(*out_ptrs)
         check(lib.b200_case_run_host(self._h, batch, ins, outs, stream))
 
+    def submit_host_ptrs(self, batch: int, in_ptrs, out_ptrs):
+        """Queues one batch (pinned host pointers) and returns; see b200_case_submit_host."""
+        ins = (C.c_void_p * len(in_ptrs))(*in_ptrs)
+        outs = (C.c_void_p * len(out_ptrs))(*out_ptrs)
+        check(lib.b200_case_submit_host(self._h, batch, ins, outs))
+
+    def wait(self):
+        check(lib.b200_case_wait(self._h))
+
     def run_host(self, inputs, out_dtypes_shapes, stream: int = 0):
         """numpy in, numpy out.  ``out_dtypes_shapes``: list of (dtype, per-image shape)."""
         batch = inputs[0].shape[0]

@@ -79,6 +79,11 @@ struct b200_case {
         cudaGraphExec_t exec;
     };
     std::vector<Graph> graphs;
+    // pipelined host runs (b200_case_submit_host): a copy stream, a compute stream, and the events
+    // that order them
+    cudaStream_t copy_stream = nullptr, comp_stream = nullptr;
+    cudaEvent_t h2d_done = nullptr, after_inputs = nullptr;
+    bool submitted = false;
 };
 
 namespace {
@@ -140,6 +145,10 @@ int b200_case_destroy(b200_case_t *cs)
     for (auto &gr : cs->graphs)
         if (gr.exec)
             cudaGraphExecDestroy(gr.exec);
+    if (cs->h2d_done) cudaEventDestroy(cs->h2d_done);
+    if (cs->after_inputs) cudaEventDestroy(cs->after_inputs);
+    if (cs->copy_stream) cudaStreamDestroy(cs->copy_stream);
+    if (cs->comp_stream) cudaStreamDestroy(cs->comp_stream);
     delete cs;
     return B200_OK;
 }
@@ -411,7 +420,8 @@ int b200_case_tensor_device_ptr(const b200_case_t *cs, int32_t tensor, void **de
     return B200_OK;
 }
 
-static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream);
+// phase: 0 = whole run, 1 = input layout kernels only, 2 = ops and outputs only
+static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream, int phase = 0);
 
 int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
 {
@@ -422,8 +432,13 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
     if (batch == 0)
         return B200_OK;
     // the legacy default stream cannot be captured: graph mode needs a stream of its own
-    if (!cs->use_graph || cs->profiling || stream == nullptr)
-        return run_eager(cs, batch, stream);
+    if (!cs->use_graph || cs->profiling || stream == nullptr) {
+        if (cs->profiling || !cs->after_inputs)
+            return run_eager(cs, batch, stream);
+        B200_TRY(run_eager(cs, batch, stream, 1));
+        B200_CUDA_TRY(cudaEventRecord(cs->after_inputs, as_stream(stream)));
+        return run_eager(cs, batch, stream, 2);
+    }
     // Graph mode: the first run at a batch size is eager (plans build their tensor maps and scratch
     // then), the second is captured, later ones replay the captured launches back to back.
     cudaStream_t cst = as_stream(stream);
@@ -435,15 +450,27 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         cs->graphs.push_back({ batch, cst, 0, nullptr });
         gr = &cs->graphs.back();
     }
+    // the input layout kernels stay outside the graph: a pipelined caller refills the input staging
+    // buffer as soon as they are done (b200_case_submit_host)
     if (gr->exec) {
+        B200_TRY(run_eager(cs, batch, stream, 1));
+        if (cs->after_inputs)
+            B200_CUDA_TRY(cudaEventRecord(cs->after_inputs, cst));
         B200_CUDA_TRY(cudaGraphLaunch(gr->exec, cst));
         return B200_OK;
     }
-    if (gr->runs_seen++ == 0)
-        return run_eager(cs, batch, stream);
+    if (gr->runs_seen++ == 0) {
+        B200_TRY(run_eager(cs, batch, stream, 1));
+        if (cs->after_inputs)
+            B200_CUDA_TRY(cudaEventRecord(cs->after_inputs, cst));
+        return run_eager(cs, batch, stream, 2);
+    }
+    B200_TRY(run_eager(cs, batch, stream, 1));
+    if (cs->after_inputs)
+        B200_CUDA_TRY(cudaEventRecord(cs->after_inputs, cst));
     cudaGraph_t graph = nullptr;
     B200_CUDA_TRY(cudaStreamBeginCapture(cst, cudaStreamCaptureModeThreadLocal));
-    int rc = run_eager(cs, batch, stream);
+    int rc = run_eager(cs, batch, stream, 2);
     cudaError_t ce = cudaStreamEndCapture(cst, &graph);
     if (rc != B200_OK || ce != cudaSuccess || !graph) {
         if (graph)
@@ -452,7 +479,7 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         cs->use_graph = false;   // something on the path cannot be captured: stay eager
         if (rc != B200_OK)
             return rc;
-        return run_eager(cs, batch, stream);
+        return run_eager(cs, batch, stream, 2);
     }
     ce = cudaGraphInstantiate(&gr->exec, graph, 0);
     cudaGraphDestroy(graph);
@@ -460,15 +487,15 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         gr->exec = nullptr;
         cudaGetLastError();
         cs->use_graph = false;
-        return run_eager(cs, batch, stream);
+        return run_eager(cs, batch, stream, 2);
     }
     B200_CUDA_TRY(cudaGraphLaunch(gr->exec, cst));
     return B200_OK;
 }
 
-static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream)
+static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream, int phase)
 {
-    const bool prof = cs->profiling;
+    const bool prof = cs->profiling && phase == 0;
     size_t ev = 0;
     cudaStream_t cst = as_stream(stream);
     if (prof) {
@@ -483,6 +510,8 @@ static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         return B200_OK;
     };
     for (auto &io : cs->inputs) {
+        if (phase == 2)
+            break;
         CaseTensor &t = cs->tensors[io.tensor];
         if (io.is_f32)
             B200_TRY(b200_quantize_u8(
@@ -492,6 +521,8 @@ static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream)
                 (const uint8_t *)io.staging, t.dev, batch, t.c, t.h, t.w, t.c_phys, 0, stream));
         B200_TRY(mark(0));
     }
+    if (phase == 1)
+        return B200_OK;
     for (auto &op : cs->ops) {
         int kind = 0;
         CaseTensor &to = cs->tensors[op.out];
@@ -600,6 +631,51 @@ int b200_case_run_host(
     B200_TRY(b200_device_status(stream, &word));
     if (word != 0)
         return fail(B200_ERR_DEVICE_WAIT, "case_run_host: a device-side wait ran out (code 0x%x)", word);
+    return B200_OK;
+}
+
+int b200_case_submit_host(b200_case_t *cs, int32_t batch, const void *const *inputs, void *const *outputs)
+{
+    if (!cs || !cs->prepared)
+        return fail(B200_ERR_INVALID, "case_submit_host: the case is not prepared");
+    if (!inputs || !outputs)
+        return fail(B200_ERR_INVALID, "case_submit_host: NULL argument");
+    if (batch < 0 || batch > cs->max_batch)
+        return fail(B200_ERR_INVALID, "case_submit_host: batch %d outside 0..%d", batch, cs->max_batch);
+    if (!cs->copy_stream) {
+        B200_CUDA_TRY(cudaStreamCreateWithFlags(&cs->copy_stream, cudaStreamNonBlocking));
+        B200_CUDA_TRY(cudaStreamCreateWithFlags(&cs->comp_stream, cudaStreamNonBlocking));
+        B200_CUDA_TRY(cudaEventCreateWithFlags(&cs->h2d_done, cudaEventDisableTiming));
+        B200_CUDA_TRY(cudaEventCreateWithFlags(&cs->after_inputs, cudaEventDisableTiming));
+    }
+    // the input staging buffer is free again once the previous run's layout kernels have read it
+    if (cs->submitted)
+        B200_CUDA_TRY(cudaStreamWaitEvent(cs->copy_stream, cs->after_inputs, 0));
+    for (size_t i = 0; i < cs->inputs.size(); ++i)
+        B200_CUDA_TRY(cudaMemcpyAsync(
+            cs->inputs[i].staging, inputs[i], cs->inputs[i].bytes_per_image * batch, cudaMemcpyHostToDevice, cs->copy_stream));
+    B200_CUDA_TRY(cudaEventRecord(cs->h2d_done, cs->copy_stream));
+    B200_CUDA_TRY(cudaStreamWaitEvent(cs->comp_stream, cs->h2d_done, 0));
+    B200_TRY(b200_case_run_device(cs, batch, reinterpret_cast<b200_stream_t>(cs->comp_stream)));
+    for (size_t i = 0; i < cs->outputs.size(); ++i)
+        B200_CUDA_TRY(cudaMemcpyAsync(
+            outputs[i], cs->outputs[i].staging, cs->outputs[i].bytes_per_image * batch, cudaMemcpyDeviceToHost, cs->comp_stream));
+    cs->submitted = true;
+    return B200_OK;
+}
+
+int b200_case_wait(b200_case_t *cs)
+{
+    if (!cs)
+        return fail(B200_ERR_INVALID, "case_wait: NULL argument");
+    if (!cs->comp_stream)
+        return B200_OK;
+    B200_CUDA_TRY(cudaStreamSynchronize(cs->copy_stream));
+    B200_CUDA_TRY(cudaStreamSynchronize(cs->comp_stream));
+    int word = 0;
+    B200_TRY(b200_device_status(reinterpret_cast<b200_stream_t>(cs->comp_stream), &word));
+    if (word != 0)
+        return fail(B200_ERR_DEVICE_WAIT, "case_wait: a device-side wait ran out (code 0x%x)", word);
     return B200_OK;
 }
 

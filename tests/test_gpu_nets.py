@@ -89,3 +89,23 @@ def test_graph_replay_matches_eager(port):
         (got,) = cs.run_host([x], [(np.float32, (64, 1, 1))], stream)
         assert_same(got.reshape(ref_logits.shape).view(np.uint32), ref_logits.view(np.uint32), "graph batch 2 run %d" % it)
     cs.close()
+
+
+def test_pipelined_submit_matches_reference(port):
+    """b200_case_submit_host / b200_case_wait: three batches in flight back to back."""
+    import torch
+    from nart_b200 import nets
+    spec = nets.resnet(18, seed=12, hw=64, width_div=2, spread=True, num_classes=32)
+    rng = np.random.default_rng(8)
+    cs, ids = nets.to_case(spec, 4)
+    cs.use_graph(True)
+    for rnd in range(2):
+        xs = [torch.from_numpy(rng.integers(0, 256, (4, 3, 64, 64), dtype=np.uint8)).pin_memory() for _ in range(3)]
+        ys = [torch.zeros((4, 32), dtype=torch.float32).pin_memory() for _ in range(3)]
+        for x, y in zip(xs, ys):
+            cs.submit_host_ptrs(4, [x.data_ptr()], [y.data_ptr()])
+        cs.wait()
+        for i, (x, y) in enumerate(zip(xs, ys)):
+            want, _, _ = nets.run_cpu(spec, x.numpy(), port)
+            assert_same(y.numpy().reshape(want.shape).view(np.uint32), want.view(np.uint32), "round %d batch %d" % (rnd, i))
+    cs.close()
