@@ -76,6 +76,7 @@ struct IgemmArgs {
     int bk;              // channels per k-block (32, 64, 128) == swizzle span of the operands
     int bn;              // output channels per tile (multiple of 16, <= 256)
     int stages;          // smem pipeline depth
+    int b_resident;      // 1: all k-blocks of B stay in shared memory (one channel tile, weights fit)
     int ob, ob_sh;       // bytes per row of an output staging sub-tile (16..128, divides bn) and its log2
     uint32_t idesc;      // tcgen05 instruction descriptor
     uint32_t tmem_cols;  // columns to allocate (power of two >= 2*bn)
@@ -361,7 +362,9 @@ __device__ __forceinline__ void epi_chunk(const uint32_t (&v)[32], int c0, const
 struct SmemLayout {
     uint32_t a, b, out, tables, bars, tmem_slot, abort_flag, total;
 };
-__host__ __device__ inline SmemLayout smem_layout(int stages, int bk, int bn)
+// b_slots: B tiles held in shared memory -- one per pipeline stage, or every k-block of the layer
+// when the weights stay resident.
+__host__ __device__ inline SmemLayout smem_layout(int stages, int b_slots, int bk, int bn)
 {
     SmemLayout L;
     uint32_t o = 0;
@@ -369,7 +372,7 @@ __host__ __device__ inline SmemLayout smem_layout(int stages, int bk, int bn)
     o += (uint32_t)stages * kTileM * bk;
     L.b = o;
     uint32_t b_tile = ((uint32_t)bn * bk + 1023u) & ~1023u;
-    o += (uint32_t)stages * b_tile;
+    o += (uint32_t)b_slots * b_tile;
     L.out = o;
     o += 2u * (uint32_t)kTileM * bn;   // two output staging buffers, used alternately
     o = (o + 1023u) & ~1023u;
@@ -377,7 +380,7 @@ __host__ __device__ inline SmemLayout smem_layout(int stages, int bk, int bn)
     o += (uint32_t)kAccStages * bn * 16;
     o = (o + 15u) & ~15u;
     L.bars = o;
-    o += (2 * kMaxStages + 2 * kAccStages) * 8;
+    o += (2 * kMaxStages + 2 * kAccStages + 1) * 8;
     L.tmem_slot = o;
     o += 8;
     L.abort_flag = o;
@@ -393,7 +396,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
     const uint32_t raw_addr = smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (base - raw_addr);
-    const SmemLayout L = smem_layout(g.stages, g.bk, g.bn);
+    const int kblocks_all = g.r * g.s * (g.c / g.bk);
+    const SmemLayout L = smem_layout(g.stages, g.b_resident ? kblocks_all : g.stages, g.bk, g.bn);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -404,6 +408,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
     auto empty_bar = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
     auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * kMaxStages + s); };
     auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * kMaxStages + kAccStages + s); };
+    const uint32_t bres_bar = bar0 + 8u * (2 * kMaxStages + 2 * kAccStages);   // resident weights have landed
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
 
@@ -412,6 +417,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
+        mbar_init(bres_bar, 1);
         for (int s = 0; s < kAccStages; ++s) {
             mbar_init(tfull_bar(s), 1);
             mbar_init(tempty_bar(s), kGroupWarps);   // one arrival per warp of the stage's epilogue group
@@ -446,7 +452,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             bool ok = true;
             TileWalker tw;
             tw.init(g, blockIdx.x);
-            const uint32_t tx_bytes = a_tile_bytes + (uint32_t)g.bn * g.bk;
+            const uint32_t tx_bytes = a_tile_bytes + (g.b_resident ? 0u : (uint32_t)g.bn * g.bk);
+            if (g.b_resident && blockIdx.x < total_tiles) {
+                // one channel tile and weights that fit: every k-block of B is loaded once and stays
+                mbar_expect_tx(bres_bar, (uint32_t)kblocks * g.bn * g.bk);
+                for (int kb = 0; kb < kblocks; ++kb)
+                    tma_load_2d(base + L.b + kb * b_tile_bytes, &maps.b, bres_bar, kb * g.bk, 0);
+            }
             const int sh_h = g.stride_h - 1, sh_w = g.stride_w - 1;   // strides are 1 or 2
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, tw.advance(g)) {
                 const int ow0 = tw.twi << g.tw_sh, oh0 = tw.thi << g.th_sh, n0 = tw.tni * g.tn;
@@ -473,7 +485,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                             const uint32_t fb = full_bar(stage);
                             mbar_expect_tx(fb, tx_bytes);
                             tma_load_4d(base + L.a + stage * a_tile_bytes, amap, fb, cc, xw, yh, n0);
-                            tma_load_2d(base + L.b + stage * b_tile_bytes, &maps.b, fb, kcoord, bn0);
+                            if (!g.b_resident)
+                                tma_load_2d(base + L.b + stage * b_tile_bytes, &maps.b, fb, kcoord, bn0);
                             if (++stage == g.stages) {
                                 stage = 0;
                                 phase ^= 1;
@@ -495,6 +508,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             const uint64_t bdesc0 = make_smem_desc(base + L.b, g.bk);
             const uint32_t a_step = a_tile_bytes >> 4, b_step = b_tile_bytes >> 4;   // descriptor address units
             const int ksteps = g.bk / 32;
+            if (g.b_resident && blockIdx.x < total_tiles && !mbar_wait(bres_bar, 0, abort_flag)) {
+                atomicCAS(g.status, 0, kErrMmaFullWait);
+                *abort_flag = 1;
+                ok = false;
+            }
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 if (!mbar_wait(tempty_bar(as), aphase ^ 1, abort_flag)) {
                     atomicCAS(g.status, 0, kErrMmaTmemWait);
@@ -512,7 +530,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                     }
                     tc_fence_after();
                     const uint64_t adesc = adesc0 + (uint64_t)(stage * a_step);
-                    const uint64_t bdesc = bdesc0 + (uint64_t)(stage * b_step);
+                    const uint64_t bdesc = bdesc0 + (uint64_t)((g.b_resident ? kb : stage) * b_step);
                     for (int ks = 0; ks < ksteps; ++ks) {
                         // advance 32 bytes of K inside the swizzle atom: +2 in 16-byte units
                         mma_i8(d_tmem, adesc + 2ull * ks, bdesc + 2ull * ks, g.idesc, (kb | ks) != 0);
@@ -721,7 +739,7 @@ int encode(CUtensorMap *m, void *base, int rank, const cuuint64_t *dims, const c
 
 struct ConvIgemmPlan {
     ConvGeom g;
-    int bk = 0, bn = 0, stages = 0, ob = 0, kpad = 0;
+    int bk = 0, bn = 0, stages = 0, ob = 0, kpad = 0, b_resident = 0;
     int n_row_cls = 0, n_col_cls = 0;
     int generic_requant = 0;
     int8_t *w_dev = nullptr;        // [kpad][r][s][c]
@@ -841,13 +859,16 @@ int conv_igemm_create(
     p->kpad = n_tiles_n * p->bn;
     // pipeline depth from the shared memory left after the staging buffer
     {
+        const int kblocks = g.r * g.s * (g.c / p->bk);
+        // weights resident when there is one channel tile and they leave room for >= 3 A stages
+        p->b_resident = n_tiles_n == 1 && smem_layout(3, kblocks, p->bk, p->bn).total + 1024 <= 227 * 1024;
         int stages = kMaxStages;
-        while (stages > 2 && smem_layout(stages, p->bk, p->bn).total + 1024 > 227 * 1024)
+        while (stages > 2 && smem_layout(stages, p->b_resident ? kblocks : stages, p->bk, p->bn).total + 1024 > 227 * 1024)
             --stages;
         // a deep ring lets the producer run several tiles ahead when a tile has few k-blocks
         p->stages = stages;
     }
-    if (smem_layout(p->stages, p->bk, p->bn).total + 1024 > 227 * 1024) {
+    if (smem_layout(p->stages, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages, p->bk, p->bn).total + 1024 > 227 * 1024) {
         delete p;
         return fail(B200_ERR_UNSUPPORTED, "conv(igemm): tile does not fit shared memory");
     }
@@ -965,7 +986,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.tiles_h = (g.oh + a.th - 1) / a.th;
     a.tiles_n = (n + a.tn - 1) / a.tn;
     a.n_tiles_n = p->kpad / p->bn;
-    a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.ob = p->ob;
+    a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.ob = p->ob; a.b_resident = p->b_resident;
     for (a.tw_sh = 0; (1 << a.tw_sh) < a.tw; ++a.tw_sh) {}
     for (a.th_sh = 0; (1 << a.th_sh) < a.th; ++a.th_sh) {}
     for (a.ob_sh = 0; (1 << a.ob_sh) < a.ob; ++a.ob_sh) {}
@@ -1037,7 +1058,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
         a.step_h = gsz % a.tiles_h;
         a.step_n = gsz / a.tiles_h;
     }
-    p->smem = smem_layout(p->stages, p->bk, p->bn).total + 1024;
+    p->smem = smem_layout(p->stages, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages, p->bk, p->bn).total + 1024;
     if (!p->attr_set) {
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         p->attr_set = true;
