@@ -215,8 +215,10 @@ __global__ void __launch_bounds__(256) conv_lower_rows_kernel(
             const int px = px0 + j;
             v[j] = (px >= 0 && px < w) ? __ldg(xrow + px) : izp4;
         }
-        out[idx * 2] = make_uint4(v[0], v[1], v[2], v[3]);
-        out[idx * 2 + 1] = make_uint4(v[4], v[5], v[6], v[7]);
+        // halves swapped where bit 2 of ox is set: the 32-byte swizzle, applied here in global memory
+        const int sw = (ox >> 2) & 1;
+        out[idx * 2 + sw] = make_uint4(v[0], v[1], v[2], v[3]);
+        out[idx * 2 + (sw ^ 1)] = make_uint4(v[4], v[5], v[6], v[7]);
     }
 }
 

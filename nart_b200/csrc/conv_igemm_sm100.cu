@@ -21,7 +21,7 @@
 //   off64 = off * mult + 2^(shift-1) + (ozp << shift).
 //
 // Warp roles (576 threads, one CTA per SM, persistent over tiles):
-//   warp 0      TMA producer (one elected lane)
+//   warp 0      TMA producer (one lane per pipeline slot)
 //   warp 1      tensor-memory allocation, MMA issue (one elected lane)
 //   warps 2..17 epilogue, two groups of 8 warps (two per tensor-memory lane quarter); group i
 //               owns accumulator stage i: tcgen05.ld -> requantize -> pack -> swizzled smem -> TMA store
@@ -30,6 +30,7 @@
 // kernel records a code in the status word, all roles leave their loops, tensor memory is freed
 // and the kernel returns.
 #include <cuda.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
@@ -49,6 +50,8 @@ constexpr int kEpiWarps = kAccStages * kGroupWarps;
 constexpr int kThreads = 64 + kEpiWarps * 32;
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 8;
+constexpr int kGroupBytes = 32 * 1024;        // target size of one pipeline stage (a group of k-blocks)
+constexpr int kMaxGroup = 10;                 // three stages of a group must fit the producer's 32 lanes
 constexpr long long kWaitCycles = 4000000000ll;   // ~2 s at 1.9 GHz
 
 // device status codes (which wait gave up)
@@ -76,7 +79,10 @@ struct IgemmArgs {
     int bk;              // channels per k-block (32, 64, 128) == swizzle span of the operands
     int bn;              // output channels per tile (multiple of 16, <= 256)
     int stages;          // smem pipeline depth
+    int kgroup;          // k-blocks per pipeline stage (divides the k-blocks of a tile): one barrier round trip per group
+    uint32_t rcp_cchunks, rcp_s;   // ceil(2^30 / (c / bk)), ceil(2^30 / s): k-block index -> tap, tap -> row
     int b_resident;      // 1: all k-blocks of B stay in shared memory (one channel tile, weights fit)
+    int a_wide;          // 1: 32-channel rows stored pre-swizzled; A is fetched as whole rows of pixels
     int ob, ob_sh;       // bytes per row of an output staging sub-tile (16..128, divides bn) and its log2
     uint32_t idesc;      // tcgen05 instruction descriptor
     uint32_t tmem_cols;  // columns to allocate (power of two >= 2*bn)
@@ -174,6 +180,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1)
 {
     asm volatile(
@@ -213,20 +226,30 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols)
 {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
-// D[tmem] (+)= A[smem] * B[smem]^T, 8-bit integer operands, int32 accumulate.
-__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+// D[tmem] (+)= A[smem] * B[smem]^T, 8-bit integer operands, int32 accumulate.  The descriptors
+// come as low words plus the high word both share; `issue` predicates the instruction.
+__device__ __forceinline__ void mma_i8(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                       uint32_t accumulate, uint32_t issue)
 {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(issue)
         : "memory");
 }
 // The barrier gets one arrival when every MMA issued so far by this thread has completed.
-__device__ __forceinline__ void mma_commit(uint32_t bar)
+__device__ __forceinline__ void mma_commit(uint32_t bar, uint32_t issue)
 {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar), "r"(issue)
+        : "memory");
 }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32])
 {
@@ -364,12 +387,12 @@ struct SmemLayout {
 };
 // b_slots: B tiles held in shared memory -- one per pipeline stage, or every k-block of the layer
 // when the weights stay resident.
-__host__ __device__ inline SmemLayout smem_layout(int stages, int b_slots, int bk, int bn)
+__host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int bk, int bn)
 {
     SmemLayout L;
     uint32_t o = 0;
     L.a = o;
-    o += (uint32_t)stages * kTileM * bk;
+    o += (uint32_t)a_slots * kTileM * bk;
     L.b = o;
     uint32_t b_tile = ((uint32_t)bn * bk + 1023u) & ~1023u;
     o += (uint32_t)b_slots * b_tile;
@@ -397,7 +420,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t *smem = smem_raw + (base - raw_addr);
     const int kblocks_all = g.r * g.s * (g.c / g.bk);
-    const SmemLayout L = smem_layout(g.stages, g.b_resident ? kblocks_all : g.stages, g.bk, g.bn);
+    const int slots = g.stages * g.kgroup;
+    const SmemLayout L = smem_layout(slots, g.b_resident ? kblocks_all : slots, g.bk, g.bn);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -444,61 +468,99 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
 
     if (warp == 0) {
         // ================= TMA producer =================
-        // One thread: every instruction here is on the critical path of the pipeline, so the
-        // loop carries its coordinates incrementally (no divisions).
-        if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            TileWalker tw;
-            tw.init(g, blockIdx.x);
-            const uint32_t tx_bytes = a_tile_bytes + (g.b_resident ? 0u : (uint32_t)g.bn * g.bk);
-            if (g.b_resident && blockIdx.x < total_tiles) {
+        // The pipeline's k-blocks form one sequence over this CTA's tiles; slot l = q mod slots
+        // (slots = stages * kgroup <= 32) holds k-block q.  Lane l owns slot l for the whole kernel and
+        // issues the loads of k-blocks l, l + slots, ...: the lanes work side by side, so the latency
+        // of one lane's bookkeeping (decode the k-block, wait for the stage, issue) is shared by
+        // `slots` k-blocks.  The first lane of a group posts the group's byte count; a load of another
+        // lane may complete before that (the transaction count is signed), the phase cannot, because
+        // the arrival is still pending.
+        const int slots = g.stages * g.kgroup;
+        if (lane < slots && blockIdx.x < total_tiles) {
+            const int stage = lane / g.kgroup;
+            const bool first = lane == stage * g.kgroup;
+            const uint32_t fb = full_bar(stage), eb = empty_bar(stage);
+            const uint32_t a_dst = base + L.a + lane * a_tile_bytes, b_dst = base + L.b + lane * b_tile_bytes;
+            const uint32_t tx_bytes = (a_tile_bytes + (g.b_resident ? 0u : (uint32_t)g.bn * g.bk)) * (uint32_t)g.kgroup;
+            if (g.b_resident && lane == 0) {
                 // one channel tile and weights that fit: every k-block of B is loaded once and stays
                 mbar_expect_tx(bres_bar, (uint32_t)kblocks * g.bn * g.bk);
                 for (int kb = 0; kb < kblocks; ++kb)
                     tma_load_2d(base + L.b + kb * b_tile_bytes, &maps.b, bres_bar, kb * g.bk, 0);
             }
             const int sh_h = g.stride_h - 1, sh_w = g.stride_w - 1;   // strides are 1 or 2
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, tw.advance(g)) {
-                const int ow0 = tw.twi << g.tw_sh, oh0 = tw.thi << g.th_sh, n0 = tw.tni * g.tn;
-                const int bn0 = tw.nt * g.bn;
-                int kcoord = 0;
-                for (int rr = 0; rr < g.r && ok; ++rr) {
-                    // input row of output row oh for this tap: ih = oh*stride + d, d = rr - pad
-                    //   = stride * (oh + (d - p) / stride) + p with p = d mod stride (0 <= p < stride)
-                    const int dh = rr - g.pad_h;
-                    const int ph = dh & sh_h;
-                    const int yh = oh0 + ((dh - ph) >> sh_h);
-                    for (int ss = 0; ss < g.s && ok; ++ss) {
-                        const int dw = ss - g.pad_w;
-                        const int pw = dw & sh_w;
-                        const int xw = ow0 + ((dw - pw) >> sh_w);
-                        const CUtensorMap *amap = &maps.a[ph * 2 + pw];
-                        for (int cc = 0; cc < g.c; cc += g.bk, kcoord += g.bk) {
-                            if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
-                                atomicCAS(g.status, 0, kErrProducerWait);
-                                *abort_flag = 1;
-                                ok = false;
-                                break;
-                            }
-                            const uint32_t fb = full_bar(stage);
-                            mbar_expect_tx(fb, tx_bytes);
-                            tma_load_4d(base + L.a + stage * a_tile_bytes, amap, fb, cc, xw, yh, n0);
+            // this lane's first k-block
+            int kb = lane % kblocks;
+            int tile = blockIdx.x;
+            TileWalker tw;
+            tw.init(g, tile);
+            for (int i = lane / kblocks; i > 0; --i) {
+                tile += gridDim.x;
+                tw.advance(g);
+            }
+            uint32_t phase = 0;
+            // Lanes whose sequence has ended drop out of `mask`; the others meet at every poll, so a
+            // lane whose stage has become free issues in that same pass of the loop.
+            const unsigned mask0 = slots >= 32 ? 0xffffffffu : ((1u << slots) - 1u);
+            bool valid = tile < total_tiles;
+            unsigned mask = __ballot_sync(mask0, valid);
+            while (valid) {
+                // k-block -> (tap row, tap column, channel chunk); the divisions are multiplications by
+                // reciprocals the host rounded up (exact for operands below 2^15)
+                const int tap = (int)(((uint64_t)(uint32_t)kb * g.rcp_cchunks) >> 30);
+                const int cc = (kb - tap * cchunks) * g.bk;
+                const int rr = (int)(((uint64_t)(uint32_t)tap * g.rcp_s) >> 30);
+                const int ss = tap - rr * g.s;
+                // input row of output row oh for this tap: ih = oh*stride + d, d = rr - pad
+                //   = stride * (oh + (d - p) / stride) + p with p = d mod stride (0 <= p < stride)
+                const int dh = rr - g.pad_h, ph = dh & sh_h;
+                const int dw = ss - g.pad_w, pw = dw & sh_w;
+                const int yh = (tw.thi << g.th_sh) + ((dh - ph) >> sh_h);
+                const int xw = (tw.twi << g.tw_sh) + ((dw - pw) >> sh_w);
+                const int n0 = tw.tni * g.tn;
+                const CUtensorMap *amap = &maps.a[ph * 2 + pw];
+                const long long t0 = clock64();
+                int spins = 0;
+                bool done = false, failed = false;
+                do {
+                    if (!done) {
+                        if (mbar_try_wait(eb, phase ^ 1)) {
+                            if (first)
+                                mbar_expect_tx(fb, tx_bytes);
+                            if (g.a_wide)   // rows of tw pixels x 32 bytes, in 8-byte elements
+                                tma_load_3d(a_dst, amap, fb, xw << 2, yh, n0);
+                            else
+                                tma_load_4d(a_dst, amap, fb, cc, xw, yh, n0);
                             if (!g.b_resident)
-                                tma_load_2d(base + L.b + stage * b_tile_bytes, &maps.b, fb, kcoord, bn0);
-                            if (++stage == g.stages) {
-                                stage = 0;
-                                phase ^= 1;
-                            }
+                                tma_load_2d(b_dst, &maps.b, fb, kb * g.bk, tw.nt * g.bn);
+                            done = true;
+                        } else if ((++spins & 255) == 0 && (*abort_flag != 0 || clock64() - t0 > kWaitCycles)) {
+                            atomicCAS(g.status, 0, kErrProducerWait);
+                            *abort_flag = 1;
+                            failed = true;
+                            done = true;
                         }
                     }
+                } while (!__all_sync(mask, done));
+                if (__any_sync(mask, failed))
+                    break;
+                phase ^= 1;
+                kb += slots;
+                while (kb >= kblocks) {
+                    kb -= kblocks;
+                    tile += gridDim.x;
+                    tw.advance(g);
                 }
+                valid = tile < total_tiles;
+                mask = __ballot_sync(mask, valid);
             }
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
-        if (lane == 0) {
+        // The whole warp walks the loop (uniform control flow); lane 0 alone issues.  Descriptors of
+        // one operand differ only in the start-address field, so only their low words are computed.
+        {
+            const uint32_t lead = lane == 0 ? 1u : 0u;
             int stage = 0;
             uint32_t phase = 0;
             int as = 0;
@@ -506,36 +568,52 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             bool ok = true;
             const uint64_t adesc0 = make_smem_desc(base + L.a, g.bk);
             const uint64_t bdesc0 = make_smem_desc(base + L.b, g.bk);
+            const uint32_t desc_hi = (uint32_t)(adesc0 >> 32);        // the same for A and B
+            const uint32_t a_lo0 = (uint32_t)adesc0, b_lo0 = (uint32_t)bdesc0;
             const uint32_t a_step = a_tile_bytes >> 4, b_step = b_tile_bytes >> 4;   // descriptor address units
+            const uint32_t a_grp = a_step * g.kgroup, b_grp = b_step * g.kgroup;
             const int ksteps = g.bk / 32;
+            const int groups = kblocks / g.kgroup;
+            const uint32_t idesc = g.idesc;
             if (g.b_resident && blockIdx.x < total_tiles && !mbar_wait(bres_bar, 0, abort_flag)) {
-                atomicCAS(g.status, 0, kErrMmaFullWait);
+                if (lead)
+                    atomicCAS(g.status, 0, kErrMmaFullWait);
                 *abort_flag = 1;
                 ok = false;
             }
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
                 if (!mbar_wait(tempty_bar(as), aphase ^ 1, abort_flag)) {
-                    atomicCAS(g.status, 0, kErrMmaTmemWait);
+                    if (lead)
+                        atomicCAS(g.status, 0, kErrMmaTmemWait);
                     *abort_flag = 1;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(as * g.bn);
-                for (int kb = 0; kb < kblocks; ++kb) {
+                uint32_t accumulate = 0;
+                for (int grp = 0; grp < groups; ++grp) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
-                        atomicCAS(g.status, 0, kErrMmaFullWait);
+                        if (lead)
+                            atomicCAS(g.status, 0, kErrMmaFullWait);
                         *abort_flag = 1;
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint64_t adesc = adesc0 + (uint64_t)(stage * a_step);
-                    const uint64_t bdesc = bdesc0 + (uint64_t)((g.b_resident ? kb : stage) * b_step);
-                    for (int ks = 0; ks < ksteps; ++ks) {
-                        // advance 32 bytes of K inside the swizzle atom: +2 in 16-byte units
-                        mma_i8(d_tmem, adesc + 2ull * ks, bdesc + 2ull * ks, g.idesc, (kb | ks) != 0);
+                    uint32_t a_lo = a_lo0 + stage * a_grp;
+                    uint32_t b_lo = b_lo0 + (g.b_resident ? grp : stage) * b_grp;
+                    for (int j = 0; j < g.kgroup; ++j, a_lo += a_step, b_lo += b_step) {
+                        // a k-block is 1, 2 or 4 MMAs of K = 32 bytes: +2 (16-byte units) inside the swizzle atom
+                        mma_i8(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate, lead);
+                        accumulate = 1;
+                        if (ksteps >= 2)
+                            mma_i8(d_tmem, a_lo + 2, b_lo + 2, desc_hi, idesc, 1, lead);
+                        if (ksteps == 4) {
+                            mma_i8(d_tmem, a_lo + 4, b_lo + 4, desc_hi, idesc, 1, lead);
+                            mma_i8(d_tmem, a_lo + 6, b_lo + 6, desc_hi, idesc, 1, lead);
+                        }
                     }
-                    mma_commit(empty_bar(stage));   // frees the smem stage when these MMAs are done
+                    mma_commit(empty_bar(stage), lead);   // frees the smem stage when the group's MMAs are done
                     if (++stage == g.stages) {
                         stage = 0;
                         phase ^= 1;
@@ -543,7 +621,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 }
                 if (!ok)
                     break;
-                mma_commit(tfull_bar(as));          // accumulator complete
+                mma_commit(tfull_bar(as), lead);          // accumulator complete
                 if (++as == kAccStages) {
                     as = 0;
                     aphase ^= 1;
@@ -720,13 +798,13 @@ CUtensorMapSwizzle swizzle_for(int bytes)
 }
 
 int encode(CUtensorMap *m, void *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides_bytes,
-           const cuuint32_t *box, CUtensorMapSwizzle sw)
+           const cuuint32_t *box, CUtensorMapSwizzle sw, CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_UINT8)
 {
     EncodeTiledFn fn = encode_fn();
     if (!fn)
         return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     cuuint32_t estr[5] = { 1, 1, 1, 1, 1 };
-    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, base, dims, strides_bytes, box, estr,
+    CUresult r = fn(m, dtype, (cuuint32_t)rank, base, dims, strides_bytes, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
@@ -739,7 +817,7 @@ int encode(CUtensorMap *m, void *base, int rank, const cuuint64_t *dims, const c
 
 struct ConvIgemmPlan {
     ConvGeom g;
-    int bk = 0, bn = 0, stages = 0, ob = 0, kpad = 0, b_resident = 0;
+    int bk = 0, bn = 0, stages = 0, kgroup = 1, ob = 0, kpad = 0, b_resident = 0, a_wide = 0;
     int n_row_cls = 0, n_col_cls = 0;
     int generic_requant = 0;
     int8_t *w_dev = nullptr;        // [kpad][r][s][c]
@@ -779,6 +857,7 @@ int conv_igemm_supported(const ConvGeom &g, char *why, size_t why_len)
     else if (g.k < 16) msg = "fewer than 16 output channels";
     else if (g.stride_h > 2 || g.stride_w > 2) msg = "stride > 2";
     else if (g.h < g.stride_h || g.w < g.stride_w) msg = "input smaller than the stride";
+    else if ((long long)g.r * g.s * (g.c / 32) >= 32768) msg = "more than 32767 k-blocks per tile";
     if (msg) {
         snprintf(why, why_len, "%s", msg);
         return 0;
@@ -815,8 +894,10 @@ static void tap_classes(int out, int in, int kernel, int pad, int stride, std::v
 
 int conv_igemm_create(
     const ConvGeom &g, const std::vector<int8_t> &w_s8, const int32_t *bias, const uint32_t *mult,
-    const int32_t *shift, ConvIgemmPlan **out)
+    const int32_t *shift, ConvIgemmPlan **out, bool a_row_swizzled)
 {
+    if (a_row_swizzled && !(g.c == 32 && g.s == 1 && g.stride_w == 1 && g.pad_w == 0 && g.w == g.ow))
+        return fail(B200_ERR_INVALID, "conv(igemm): pre-swizzled rows need 32 channels and an r x 1 kernel");
     // The epilogue adds the accumulator offset in 64-bit arithmetic, where the reference's int32
     // accumulator would wrap; and its folded addend needs shift <= 53 to stay inside int64.
     {
@@ -834,6 +915,7 @@ int conv_igemm_create(
     }
     ConvIgemmPlan *p = new ConvIgemmPlan();
     p->g = g;
+    p->a_wide = a_row_swizzled ? 1 : 0;
     p->bk = g.c % 128 == 0 ? 128 : (g.c % 64 == 0 ? 64 : 32);
     // output-channel tile: a multiple of 16 up to 256 that wastes little of Cout
     {
@@ -862,13 +944,35 @@ int conv_igemm_create(
         const int kblocks = g.r * g.s * (g.c / p->bk);
         // weights resident when there is one channel tile and they leave room for >= 3 A stages
         p->b_resident = n_tiles_n == 1 && smem_layout(3, kblocks, p->bk, p->bn).total + 1024 <= 227 * 1024;
+        // Narrow k-blocks (few bytes per barrier round trip) travel in groups: the largest divisor of
+        // the tile's k-blocks that keeps a stage at or under kGroupBytes.
+        const int kb_bytes = kTileM * p->bk + (p->b_resident ? 0 : p->bn * p->bk);
+        int kgroup = 1;
+        for (int d = 1; d <= kblocks; ++d)
+            if (kblocks % d == 0 && d * kb_bytes <= kGroupBytes && d <= kMaxGroup)
+                kgroup = d;
+        if (const char *e = getenv("B200_IGEMM_KGROUP")) {   // tuning aid: a divisor of the k-blocks, else ignored
+            int v = atoi(e);
+            if (v >= 1 && v <= kMaxGroup && kblocks % v == 0)
+                kgroup = v;
+        }
         int stages = kMaxStages;
-        while (stages > 2 && smem_layout(stages, p->b_resident ? kblocks : stages, p->bk, p->bn).total + 1024 > 227 * 1024)
+        auto fits = [&](int st, int kg) {
+            return smem_layout(st * kg, p->b_resident ? kblocks : st * kg, p->bk, p->bn).total + 1024 <= 227 * 1024;
+        };
+        while (kgroup > 1 && !fits(3, kgroup)) {   // keep at least three stages in flight
+            int d = kgroup - 1;
+            while (kblocks % d != 0)
+                --d;
+            kgroup = d;
+        }
+        while (stages > 2 && (!fits(stages, kgroup) || stages * kgroup > 32))
             --stages;
         // a deep ring lets the producer run several tiles ahead when a tile has few k-blocks
         p->stages = stages;
+        p->kgroup = kgroup;
     }
-    if (smem_layout(p->stages, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages, p->bk, p->bn).total + 1024 > 227 * 1024) {
+    if (smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages * p->kgroup, p->bk, p->bn).total + 1024 > 227 * 1024) {
         delete p;
         return fail(B200_ERR_UNSUPPORTED, "conv(igemm): tile does not fit shared memory");
     }
@@ -955,10 +1059,10 @@ void conv_igemm_destroy(ConvIgemmPlan *p)
 
 // Chooses the M-tile box (tw, th, tn), powers of two with product 128, that covers the output with
 // the fewest tiles; ties go to the wider box.
-static void choose_tile(int ow, int oh, int n, int *tw, int *th, int *tn)
+static void choose_tile(int ow, int oh, int n, int *tw, int *th, int *tn, int min_a = 0, int max_a = 7)
 {
     long long best = -1;
-    for (int a = 0; a <= 7; ++a)
+    for (int a = min_a; a <= max_a; ++a)
         for (int b = 0; a + b <= 7; ++b) {
             int w = 1 << a, h = 1 << b, nn = 1 << (7 - a - b);
             long long tiles = (long long)((ow + w - 1) / w) * ((oh + h - 1) / h) * ((n + nn - 1) / nn);
@@ -981,12 +1085,17 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.n = n; a.oh = g.oh; a.ow = g.ow; a.cout = g.k;
     a.r = g.r; a.s = g.s; a.pad_h = g.pad_h; a.pad_w = g.pad_w; a.stride_h = g.stride_h; a.stride_w = g.stride_w;
     a.c = g.c;
-    choose_tile(g.ow, g.oh, n, &a.tw, &a.th, &a.tn);
+    if (p->a_wide)   // whole swizzle atoms (8 pixels) per row segment, at most 256 8-byte elements
+        choose_tile(g.ow, g.oh, n, &a.tw, &a.th, &a.tn, 3, 6);
+    else
+        choose_tile(g.ow, g.oh, n, &a.tw, &a.th, &a.tn);
     a.tiles_w = (g.ow + a.tw - 1) / a.tw;
     a.tiles_h = (g.oh + a.th - 1) / a.th;
     a.tiles_n = (n + a.tn - 1) / a.tn;
     a.n_tiles_n = p->kpad / p->bn;
-    a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.ob = p->ob; a.b_resident = p->b_resident;
+    a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.kgroup = p->kgroup;
+    a.rcp_cchunks = (uint32_t)(((1ull << 30) + (uint64_t)(g.c / p->bk) - 1) / (uint64_t)(g.c / p->bk));
+    a.rcp_s = (uint32_t)(((1ull << 30) + (uint64_t)g.s - 1) / (uint64_t)g.s); a.ob = p->ob; a.b_resident = p->b_resident; a.a_wide = p->a_wide;
     for (a.tw_sh = 0; (1 << a.tw_sh) < a.tw; ++a.tw_sh) {}
     for (a.th_sh = 0; (1 << a.th_sh) < a.th; ++a.th_sh) {}
     for (a.ob_sh = 0; (1 << a.ob_sh) < a.ob; ++a.ob_sh) {}
@@ -1016,6 +1125,17 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
             // input pixels (ph + stride_h * i, pw + stride_w * j): a dense 4-D tensor (c, j, i, image)
             if (ph >= g.h || pw >= g.w) {
                 p->maps.a[ph * 2 + pw] = p->maps.a[0];
+                continue;
+            }
+            if (p->a_wide) {
+                // rows of this parity as a 3-D tensor (ow * 32 bytes in 8-byte elements, row, image);
+                // no swizzle: the bytes are already laid out as the MMA's 32-byte swizzle wants them
+                cuuint64_t dims[3] = { (cuuint64_t)g.w * 4, (cuuint64_t)((g.h - ph + g.stride_h - 1) / g.stride_h), (cuuint64_t)n };
+                cuuint64_t strides[2] = { (cuuint64_t)g.stride_h * g.w * 32, (cuuint64_t)g.h * g.w * 32 };
+                cuuint32_t box[3] = { (cuuint32_t)a.tw * 4, (cuuint32_t)a.th, (cuuint32_t)a.tn };
+                void *base = (void *)(x + (size_t)ph * g.w * 32);
+                B200_TRY(encode(&p->maps.a[ph * 2 + pw], base, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                CU_TENSOR_MAP_DATA_TYPE_UINT64));
                 continue;
             }
             cuuint64_t dims[4] = { (cuuint64_t)g.c, (cuuint64_t)((g.w - pw + g.stride_w - 1) / g.stride_w),
@@ -1058,7 +1178,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
         a.step_h = gsz % a.tiles_h;
         a.step_n = gsz / a.tiles_h;
     }
-    p->smem = smem_layout(p->stages, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages, p->bk, p->bn).total + 1024;
+    p->smem = smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages * p->kgroup, p->bk, p->bn).total + 1024;
     if (!p->attr_set) {
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         p->attr_set = true;

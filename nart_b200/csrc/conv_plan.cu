@@ -166,7 +166,7 @@ int b200_conv2d_create(
                 for (int rr = 0; rr < g.r; ++rr)
                     for (int j = 0; j < g.s; ++j)
                         w_low[((size_t)k * gl.c + j * 4 + c) * g.r + rr] = w_s8[(((size_t)k * 4 + c) * g.r + rr) * g.s + j];
-        rc = conv_igemm_create(gl, w_low, bias, mult.data(), shift.data(), &cv->igemm);
+        rc = conv_igemm_create(gl, w_low, bias, mult.data(), shift.data(), &cv->igemm, true);
         if (rc == B200_OK) {
             cv->algo = B200_CONV_ALGO_IGEMM;
             cv->lowered = true;

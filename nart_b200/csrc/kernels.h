@@ -61,7 +61,10 @@ int conv_direct_launch(
     cudaStream_t st);
 
 // Row lowering of a 4-channel NHWC image: out[n][ih][ow][j*4 + c] = x[n][ih][ow*stride_w - pad_w + j][c]
-// for j < kLowerWindow, the byte izp where the pixel lies outside the image.
+// for j < kLowerWindow, the byte izp where the pixel lies outside the image.  The two 16-byte
+// halves of an output pixel are stored swapped when bit 2 of ow is set: that is the 32-byte
+// shared-memory swizzle, applied in global memory, so that the tensor-core kernel can fetch whole
+// rows of pixels with wide unswizzled copies (see conv_igemm_create, a_row_swizzled).
 constexpr int kLowerWindow = 8;
 int conv_lower_rows_launch(const ConvGeom &g, const uint8_t *x, int n, uint8_t *out, cudaStream_t st);
 
@@ -70,7 +73,9 @@ struct ConvIgemmPlan;
 int conv_igemm_supported(const ConvGeom &g, char *why, size_t why_len);
 int conv_igemm_create(
     const ConvGeom &g, const std::vector<int8_t> &w_s8 /* [k][c][r][s] */, const int32_t *bias,
-    const uint32_t *mult, const int32_t *shift, ConvIgemmPlan **plan);
+    const uint32_t *mult, const int32_t *shift, ConvIgemmPlan **plan, bool a_row_swizzled = false);
+// a_row_swizzled: the activation tensor has 32 channels, the kernel is r x 1 with no horizontal
+// stride or padding, and the tensor was written by conv_lower_rows_launch (halves swapped by ow bit 2).
 // status_word: device int that a bounded wait writes its code into; nullptr = the per-device word
 // that b200_device_status reads.
 int conv_igemm_launch(ConvIgemmPlan *plan, const uint8_t *x, int n, uint8_t *y, cudaStream_t st,
