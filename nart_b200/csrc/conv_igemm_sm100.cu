@@ -329,8 +329,9 @@ struct EpiConsts {
 // FAST also assumes obits == 8, where the pack's saturation to 0..255 is the whole clamp.
 // SMEM_OFF reads the addends from shared memory (layers with a single border class) instead of
 // the per-class rows in global memory.  All flags are compile-time so that the body is one
-// straight-line block of independent chains.
-template <bool FAST, bool SMEM_OFF, int NCOL>
+// straight-line block of independent chains.  FLOOR = false drops the ReLU floor when it is 0, where
+// the pack's own clamp already applies it.
+template <bool FAST, bool SMEM_OFF, int NCOL, bool FLOOR = true>
 __device__ __forceinline__ void epi_chunk(const uint32_t (&v)[32], int c0, const long long *off_row, const EpiConsts &ec)
 {
     uint32_t packed[NCOL / 4];
@@ -363,8 +364,11 @@ __device__ __forceinline__ void epi_chunk(const uint32_t (&v)[32], int c0, const
             q2 = min((int)(p2 >> s4.z), ec.qmax);
             q3 = min((int)(p3 >> s4.w), ec.qmax);
         }
-        // the pack saturates to 0..255; the ReLU floor is applied first
-        packed[q4] = pack_sat_u8x4(max(q0, ec.relu_lo), max(q1, ec.relu_lo), max(q2, ec.relu_lo), max(q3, ec.relu_lo));
+        // the pack saturates to 0..255; a ReLU floor above 0 is applied first (FLOOR)
+        if (FLOOR)
+            packed[q4] = pack_sat_u8x4(max(q0, ec.relu_lo), max(q1, ec.relu_lo), max(q2, ec.relu_lo), max(q3, ec.relu_lo));
+        else
+            packed[q4] = pack_sat_u8x4(q0, q1, q2, q3);
     }
     // staging: sub-tile (col / ob), row-major rows of `ob` bytes, 16-byte chunks XOR-swizzled with the
     // row index exactly as the TMA store's swizzle mode expects
@@ -659,6 +663,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
 
         const EpiConsts ec = { s_mult, s_shift, s_off, s_out, g.ob, g.ob_sh, sw, row, g.qmax, g.relu_lo };
         const bool fast_epi = !g.generic_requant && g.qmax == 255;
+        const bool no_floor = g.relu_lo <= 0;
 
         TileWalker tw;
         tw.init(g, blockIdx.x);
@@ -713,10 +718,17 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 tmem_ld_wait();
                 // the common case is one straight-line block of 32 independent chains
                 if (fast_epi && ncol == 32) {
-                    if (single_class)
-                        epi_chunk<true, true, 32>(v, c0, off_row, ec);
-                    else
-                        epi_chunk<true, false, 32>(v, c0, off_row, ec);
+                    if (single_class) {
+                        if (no_floor)
+                            epi_chunk<true, true, 32, false>(v, c0, off_row, ec);
+                        else
+                            epi_chunk<true, true, 32>(v, c0, off_row, ec);
+                    } else {
+                        if (no_floor)
+                            epi_chunk<true, false, 32, false>(v, c0, off_row, ec);
+                        else
+                            epi_chunk<true, false, 32>(v, c0, off_row, ec);
+                    }
                 } else if (fast_epi) {
                     epi_chunk<true, false, 16>(v, c0, off_row, ec);
                 } else if (ncol == 32) {

@@ -188,7 +188,8 @@ __device__ __forceinline__ int elt_finish(int t, const EltwiseArgs &a)
 // FAST: obits == 8 and the final rounding term 2^(s0-1) << b[0] fits into add[0] (folded there by
 // the host, exact because it is a multiple of 2^b[0]); then y = sat_u8(max((t >> s0) + ozp, relu_lo))
 // and the saturation comes with the pack.  32 bytes per input per thread and iteration.
-template <int N_IN, bool FAST>
+// PLAIN (with FAST): ozp == 0 and no floor above 0, so y = sat_u8(t >> s0) and the pack does the rest.
+template <int N_IN, bool FAST, bool PLAIN = false>
 __global__ void __launch_bounds__(256) eltwise_sum_kernel(EltwiseArgs a, uint8_t *__restrict__ y, size_t count)
 {
     constexpr int VPT = 2;   // 16-byte vectors per input per thread
@@ -216,7 +217,7 @@ __global__ void __launch_bounds__(256) eltwise_sum_kernel(EltwiseArgs a, uint8_t
                     const int xv = (int)__byte_perm(xin[i][wd], 0, 0x4440 | e);   // byte e, zero-extended
                     t += (xv * a.m[i] + a.add[i]) >> a.b[i];
                 }
-                r[e] = FAST ? max((t >> a.s0) + a.ozp, a.relu_lo) : elt_finish(t, a);
+                r[e] = PLAIN ? (t >> a.s0) : (FAST ? max((t >> a.s0) + a.ozp, a.relu_lo) : elt_finish(t, a));
             }
             o[wd] = FAST ? pack_sat_u8x4(r[0], r[1], r[2], r[3]) : pack4(r[0], r[1], r[2], r[3]);
         }
@@ -469,7 +470,12 @@ int b200_eltwise_sum_u8(
     if (fast) {
         switch (n_in) {
         case 1: eltwise_sum_kernel<1, true><<<grid, 256, 0, st>>>(a, y, count); break;
-        case 2: eltwise_sum_kernel<2, true><<<grid, 256, 0, st>>>(a, y, count); break;
+        case 2:
+            if (a.ozp == 0 && a.relu_lo <= 0)
+                eltwise_sum_kernel<2, true, true><<<grid, 256, 0, st>>>(a, y, count);
+            else
+                eltwise_sum_kernel<2, true><<<grid, 256, 0, st>>>(a, y, count);
+            break;
         case 3: eltwise_sum_kernel<3, true><<<grid, 256, 0, st>>>(a, y, count); break;
         default: eltwise_sum_kernel<4, true><<<grid, 256, 0, st>>>(a, y, count); break;
         }
