@@ -23,10 +23,11 @@
 // Warp roles (576 threads, one CTA per SM, persistent over tiles):
 //   warp 0      TMA producer (one lane per pipeline slot)
 //   warp 1      tensor-memory allocation, MMA issue (one elected lane)
-//   warps 2..17 epilogue, two groups of 8 warps (two per tensor-memory lane quarter); group i
+//   warps 2..17 epilogue, two groups of 8 warps (two per tensor-memory lane quarter) or, for narrow
+//               channel tiles with a short mainloop, four groups of 4 warps; group i
 //               owns accumulator stage i: tcgen05.ld -> requantize -> pack -> swizzled smem -> TMA store
-// Two accumulator stages in tensor memory let the epilogue of tile i overlap the mainloop of
-// tile i+1 and the epilogue of tile i+1 (the other group).  No cluster launch, no multicast.  Every wait is bounded: when one runs out the
+// One accumulator stage per group in tensor memory lets the epilogue of tile i overlap the mainloop
+// of the next tiles and their epilogues (the other groups).  No cluster launch, no multicast.  Every wait is bounded: when one runs out the
 // kernel records a code in the status word, all roles leave their loops, tensor memory is freed
 // and the kernel returns.
 #include <cuda.h>
@@ -42,11 +43,8 @@ namespace b200 {
 
 namespace {
 
-constexpr int kAccStages = 2;                 // accumulator stages in tensor memory = epilogue groups
-constexpr int kWarpsPerQuarter = 2;           // warps of one epilogue group per tensor-memory lane quarter
-constexpr int kGroupWarps = 4 * kWarpsPerQuarter;
-constexpr int kGroupThreads = kGroupWarps * 32;
-constexpr int kEpiWarps = kAccStages * kGroupWarps;
+constexpr int kMaxAccStages = 4;              // accumulator stages in tensor memory = epilogue groups: 2 or 4
+constexpr int kEpiWarps = 16;                 // split into 2 groups of 8 warps or 4 groups of 4
 constexpr int kThreads = 64 + kEpiWarps * 32;
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 8;
@@ -79,6 +77,7 @@ struct IgemmArgs {
     int bk;              // channels per k-block (32, 64, 128) == swizzle span of the operands
     int bn;              // output channels per tile (multiple of 16, <= 256)
     int stages;          // smem pipeline depth
+    int groups;          // epilogue groups = accumulator stages in tensor memory (2 or 4)
     int kgroup;          // k-blocks per pipeline stage (divides the k-blocks of a tile): one barrier round trip per group
     uint32_t rcp_cchunks, rcp_s;   // ceil(2^30 / (c / bk)), ceil(2^30 / s): k-block index -> tap, tap -> row
     int b_resident;      // 1: all k-blocks of B stay in shared memory (one channel tile, weights fit)
@@ -275,14 +274,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32])
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// Named barriers of one epilogue group (ids 1, 2 for group 0 and 3, 4 for group 1).
-__device__ __forceinline__ void epi_bar_sync(int group)
+// Named barriers of one epilogue group (ids 1 + 2g and 2 + 2g for group g).
+__device__ __forceinline__ void epi_bar_sync(int group, int group_threads)
 {
-    asm volatile("bar.sync %0, %1;" ::"r"(1 + 2 * group), "n"(kGroupThreads) : "memory");
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + 2 * group), "r"(group_threads) : "memory");
 }
 // AND-reduction of a predicate over the threads of one epilogue group: every thread gets
 // the same answer, so all of them leave the tile loop together.
-__device__ __forceinline__ bool epi_bar_all(int group, bool pred)
+__device__ __forceinline__ bool epi_bar_all(int group, int group_threads, bool pred)
 {
     uint32_t out;
     asm volatile(
@@ -291,7 +290,7 @@ __device__ __forceinline__ bool epi_bar_all(int group, bool pred)
         "barrier.cta.red.and.pred q, %3, %2, p;\n\t"
         "selp.u32 %0, 1, 0, q;\n\t}"
         : "=r"(out)
-        : "r"((uint32_t)pred), "n"(kGroupThreads), "r"(2 + 2 * group)
+        : "r"((uint32_t)pred), "r"(group_threads), "r"(2 + 2 * group)
         : "memory");
     return out != 0;
 }
@@ -391,7 +390,7 @@ struct SmemLayout {
 };
 // b_slots: B tiles held in shared memory -- one per pipeline stage, or every k-block of the layer
 // when the weights stay resident.
-__host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int bk, int bn)
+__host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int bk, int bn, int groups)
 {
     SmemLayout L;
     uint32_t o = 0;
@@ -401,13 +400,13 @@ __host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int 
     uint32_t b_tile = ((uint32_t)bn * bk + 1023u) & ~1023u;
     o += (uint32_t)b_slots * b_tile;
     L.out = o;
-    o += 2u * (uint32_t)kTileM * bn;   // two output staging buffers, used alternately
+    o += (uint32_t)groups * kTileM * bn;   // one output staging buffer per epilogue group
     o = (o + 1023u) & ~1023u;
     L.tables = o;                      // per epilogue group: mult[bn], shift[bn] (int32), off[bn] (int64)
-    o += (uint32_t)kAccStages * bn * 16;
+    o += (uint32_t)groups * bn * 16;
     o = (o + 15u) & ~15u;
     L.bars = o;
-    o += (2 * kMaxStages + 2 * kAccStages + 1) * 8;
+    o += (2 * kMaxStages + 2 * kMaxAccStages + 1) * 8;
     L.tmem_slot = o;
     o += 8;
     L.abort_flag = o;
@@ -425,7 +424,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
     uint8_t *smem = smem_raw + (base - raw_addr);
     const int kblocks_all = g.r * g.s * (g.c / g.bk);
     const int slots = g.stages * g.kgroup;
-    const SmemLayout L = smem_layout(slots, g.b_resident ? kblocks_all : slots, g.bk, g.bn);
+    const SmemLayout L = smem_layout(slots, g.b_resident ? kblocks_all : slots, g.bk, g.bn, g.groups);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -435,8 +434,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
     auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * kMaxStages + s); };
-    auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * kMaxStages + kAccStages + s); };
-    const uint32_t bres_bar = bar0 + 8u * (2 * kMaxStages + 2 * kAccStages);   // resident weights have landed
+    auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * kMaxStages + kMaxAccStages + s); };
+    const uint32_t bres_bar = bar0 + 8u * (2 * kMaxStages + 2 * kMaxAccStages);   // resident weights have landed
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem + L.tmem_slot);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + L.abort_flag);
 
@@ -446,9 +445,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(bres_bar, 1);
-        for (int s = 0; s < kAccStages; ++s) {
+        for (int s = 0; s < g.groups; ++s) {
             mbar_init(tfull_bar(s), 1);
-            mbar_init(tempty_bar(s), kGroupWarps);   // one arrival per warp of the stage's epilogue group
+            mbar_init(tempty_bar(s), kEpiWarps / g.groups);   // one arrival per warp of the stage's epilogue group
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -626,7 +625,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 if (!ok)
                     break;
                 mma_commit(tfull_bar(as), lead);          // accumulator complete
-                if (++as == kAccStages) {
+                if (++as == g.groups) {
                     as = 0;
                     aphase ^= 1;
                 }
@@ -637,9 +636,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
         // Two independent groups of 8 warps; group i owns accumulator stage i, i.e. every second
         // tile of this CTA, with its own staging buffer, tables and named barriers, so that one
         // group's waits and barriers overlap the other group's arithmetic.
-        const int group = (warp - 2) / kGroupWarps;
-        const int gw = (warp - 2) % kGroupWarps;     // warp inside the group
-        const int et = gw * 32 + lane;               // thread inside the group, 0..kGroupThreads-1
+        const int group_warps = kEpiWarps / g.groups;      // 8 or 4: a multiple of four, one or two warps per lane quarter
+        const int group_threads = group_warps * 32;
+        const int group = (warp - 2) / group_warps;
+        const int gw = (warp - 2) % group_warps;     // warp inside the group
+        const int et = gw * 32 + lane;               // thread inside the group
         const int quarter = warp & 3;                // TMEM lanes 32*quarter .. +31 belong to this warp
         const int sub_warp = gw >> 2;                // which of the group's warps of that quarter
         const int row = quarter * 32 + lane;         // accumulator row = pixel of the tile
@@ -667,9 +668,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
 
         TileWalker tw;
         tw.init(g, blockIdx.x);
-        if (group == 1)
+        for (int i = 0; i < group; ++i)
             tw.advance(g);
-        for (int tile = blockIdx.x + group * gridDim.x; tile < total_tiles; tile += 2 * gridDim.x, tw.advance(g), tw.advance(g)) {
+        for (int tile = blockIdx.x + group * gridDim.x; tile < total_tiles; tile += g.groups * gridDim.x) {
             const int nt = tw.nt;
             const int ow0 = tw.twi << g.tw_sh, oh0 = tw.thi << g.th_sh, n0 = tw.tni * g.tn;
             const int k0 = nt * g.bn;
@@ -682,8 +683,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             // per-channel tables change with the channel tile (all threads are past the previous
             // tile's compute once they are through the barrier below)
             if (nt != cur_nt) {
-                epi_bar_sync(group);
-                for (int j = et; j < g.bn; j += kGroupThreads) {
+                epi_bar_sync(group, group_threads);
+                for (int j = et; j < g.bn; j += group_threads) {
                     const int sft = g.shift[k0 + j];
                     s_mult[j] = (int)g.mult[k0 + j];
                     s_shift[j] = fast_epi ? sft - 32 : sft;   // the fast form shifts the high word only
@@ -697,7 +698,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 tma_store_wait_read();
             // one barrier: makes the staging buffer and the tables safe, and makes the outcome of the
             // bounded wait uniform over the epilogue threads
-            if (!epi_bar_all(group, mbar_wait(tfull_bar(as), aphase, abort_flag))) {
+            if (!epi_bar_all(group, group_threads, mbar_wait(tfull_bar(as), aphase, abort_flag))) {
                 if (et == 0) {
                     atomicCAS(g.status, 0, kErrEpilogueWait);
                     *abort_flag = 1;
@@ -708,7 +709,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * g.bn);
             // The warps that share a lane quarter take 32-column chunks round-robin; with four warps
             // per scheduler the tensor-memory read of one warp overlaps the arithmetic of the others.
-            for (int c0 = sub_warp * 32; c0 < g.bn; c0 += kWarpsPerQuarter * 32) {
+            for (int c0 = sub_warp * 32; c0 < g.bn; c0 += (group_warps >> 2) * 32) {
                 uint32_t v[32];
                 const int ncol = min(32, g.bn - c0);   // 32, or 16 for the last chunk of bn % 32 == 16
                 if (ncol == 32)
@@ -746,7 +747,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
 
             if (g.use_tma_store) {
                 fence_async_smem();
-                epi_bar_sync(group);
+                epi_bar_sync(group, group_threads);
                 if (et == 0) {
                     for (int sub = 0; sub < n_sub; ++sub) {
                         if (k0 + (sub << g.ob_sh) < g.cout)
@@ -757,7 +758,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 store_pending = true;
             } else {
                 // plain stores for channel counts the TMA store cannot address (Cout % 16 != 0)
-                epi_bar_sync(group);
+                epi_bar_sync(group, group_threads);
                 if (pix_valid && sub_warp == 0) {
                     uint8_t *dst = g.y + (((size_t)img * g.oh + oh) * g.ow + ow) * g.cout + k0;
                     const int nvalid = min(g.bn, g.cout - k0);
@@ -768,6 +769,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                     }
                 }
             }
+            for (int i = 0; i < g.groups; ++i)
+                tw.advance(g);
         }
         if (store_pending && et == 0)
             tma_store_wait_all();
@@ -829,6 +832,7 @@ int encode(CUtensorMap *m, void *base, int rank, const cuuint64_t *dims, const c
 
 struct ConvIgemmPlan {
     ConvGeom g;
+    int groups = 2;
     int bk = 0, bn = 0, stages = 0, kgroup = 1, ob = 0, kpad = 0, b_resident = 0, a_wide = 0;
     int n_row_cls = 0, n_col_cls = 0;
     int generic_requant = 0;
@@ -955,7 +959,15 @@ int conv_igemm_create(
     {
         const int kblocks = g.r * g.s * (g.c / p->bk);
         // weights resident when there is one channel tile and they leave room for >= 3 A stages
-        p->b_resident = n_tiles_n == 1 && smem_layout(3, kblocks, p->bk, p->bn).total + 1024 <= 227 * 1024;
+        // four epilogue groups (four tiles in flight behind the mainloop) when the tiles are narrow:
+        // their per-tile latency chain, not their arithmetic, sets the epilogue rate
+        p->groups = (p->bn <= 64 || (p->bn <= 128 && kblocks * p->bk <= 256)) ? 4 : 2;
+        if (const char *e = getenv("B200_IGEMM_GROUPS")) {   // tuning aid: 2, or 4 when four accumulators fit
+            int v = atoi(e);
+            if (v == 2 || (v == 4 && 4 * p->bn <= 512))
+                p->groups = v;
+        }
+        p->b_resident = n_tiles_n == 1 && smem_layout(3, kblocks, p->bk, p->bn, p->groups).total + 1024 <= 227 * 1024;
         // Narrow k-blocks (few bytes per barrier round trip) travel in groups: the largest divisor of
         // the tile's k-blocks that keeps a stage at or under kGroupBytes.
         const int kb_bytes = kTileM * p->bk + (p->b_resident ? 0 : p->bn * p->bk);
@@ -970,7 +982,7 @@ int conv_igemm_create(
         }
         int stages = kMaxStages;
         auto fits = [&](int st, int kg) {
-            return smem_layout(st * kg, p->b_resident ? kblocks : st * kg, p->bk, p->bn).total + 1024 <= 227 * 1024;
+            return smem_layout(st * kg, p->b_resident ? kblocks : st * kg, p->bk, p->bn, p->groups).total + 1024 <= 227 * 1024;
         };
         while (kgroup > 1 && !fits(3, kgroup)) {   // keep at least three stages in flight
             int d = kgroup - 1;
@@ -984,7 +996,7 @@ int conv_igemm_create(
         p->stages = stages;
         p->kgroup = kgroup;
     }
-    if (smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages * p->kgroup, p->bk, p->bn).total + 1024 > 227 * 1024) {
+    if (smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024 > 227 * 1024) {
         delete p;
         return fail(B200_ERR_UNSUPPORTED, "conv(igemm): tile does not fit shared memory");
     }
@@ -1105,7 +1117,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.tiles_h = (g.oh + a.th - 1) / a.th;
     a.tiles_n = (n + a.tn - 1) / a.tn;
     a.n_tiles_n = p->kpad / p->bn;
-    a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.kgroup = p->kgroup;
+    a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.kgroup = p->kgroup; a.groups = p->groups;
     a.rcp_cchunks = (uint32_t)(((1ull << 30) + (uint64_t)(g.c / p->bk) - 1) / (uint64_t)(g.c / p->bk));
     a.rcp_s = (uint32_t)(((1ull << 30) + (uint64_t)g.s - 1) / (uint64_t)g.s); a.ob = p->ob; a.b_resident = p->b_resident; a.a_wide = p->a_wide;
     for (a.tw_sh = 0; (1 << a.tw_sh) < a.tw; ++a.tw_sh) {}
@@ -1115,7 +1127,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     // (1 at bit 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
     a.idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(p->bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
     uint32_t cols = 32;
-    while (cols < (uint32_t)(kAccStages * p->bn))
+    while (cols < (uint32_t)(p->groups * p->bn))
         cols <<= 1;
     a.tmem_cols = cols;
     a.off = p->off_dev; a.mult = p->mult_dev; a.shift = p->shift_dev;
@@ -1190,7 +1202,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
         a.step_h = gsz % a.tiles_h;
         a.step_n = gsz / a.tiles_h;
     }
-    p->smem = smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages * p->kgroup, p->bk, p->bn).total + 1024;
+    p->smem = smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024;
     if (!p->attr_set) {
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         p->attr_set = true;
