@@ -77,7 +77,8 @@ struct IgemmArgs {
     int bk;              // channels per k-block (32, 64, 128) == swizzle span of the operands
     int bn;              // output channels per tile (multiple of 16, <= 256)
     int stages;          // smem pipeline depth
-    int groups;          // epilogue groups = accumulator stages in tensor memory (2 or 4)
+    int groups;          // epilogue groups (2 or 4); group i takes every groups-th tile of the CTA
+    int acc_stages;      // accumulator stages in tensor memory (a multiple of groups, at most 4)
     int kgroup;          // k-blocks per pipeline stage (divides the k-blocks of a tile): one barrier round trip per group
     uint32_t rcp_cchunks, rcp_s;   // ceil(2^30 / (c / bk)), ceil(2^30 / s): k-block index -> tap, tap -> row
     int b_resident;      // 1: all k-blocks of B stay in shared memory (one channel tile, weights fit)
@@ -445,7 +446,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             mbar_init(empty_bar(s), 1);
         }
         mbar_init(bres_bar, 1);
-        for (int s = 0; s < g.groups; ++s) {
+        for (int s = 0; s < g.acc_stages; ++s) {
             mbar_init(tfull_bar(s), 1);
             mbar_init(tempty_bar(s), kEpiWarps / g.groups);   // one arrival per warp of the stage's epilogue group
         }
@@ -625,7 +626,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 if (!ok)
                     break;
                 mma_commit(tfull_bar(as), lead);          // accumulator complete
-                if (++as == g.groups) {
+                if (++as == g.acc_stages) {
                     as = 0;
                     aphase ^= 1;
                 }
@@ -656,7 +657,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
         const uint32_t out_bytes = (uint32_t)kTileM * g.bn;
         // this thread's pixel inside a tile (tw, th are powers of two)
         const int lw = row & (g.tw - 1), lh = (row >> g.tw_sh) & (g.th - 1), ln = row >> (g.tw_sh + g.th_sh);
-        const int as = group;                        // accumulator stage of this group
+        int as = group;                              // accumulator stage of this group's current tile
         uint32_t aphase = 0;
         int cur_nt = -1;
         bool store_pending = false;
@@ -665,6 +666,16 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
         const EpiConsts ec = { s_mult, s_shift, s_off, s_out, g.ob, g.ob_sh, sw, row, g.qmax, g.relu_lo };
         const bool fast_epi = !g.generic_requant && g.qmax == 255;
         const bool no_floor = g.relu_lo <= 0;
+
+        // Each warp owns its 32 rows of the staging buffer for the column sub-tiles it computes
+        // (sub-tile j belongs to warp j mod warps-per-quarter of the quarter), and stores them with
+        // its own TMA store of the quarter box: no barrier between the warps of a group on the way
+        // of a tile.  Group barriers remain only where the shared tables are reloaded.
+        const int wpq = group_warps >> 2;                       // warps per lane quarter: 1 or 2
+        const int own_sh = g.ob_sh > 5 ? g.ob_sh : 5;           // ownership granule: a sub-tile, at least one chunk
+        const int p0 = quarter * 32;                            // first pixel of this warp's rows inside a tile
+        const int qlw = p0 & (g.tw - 1), qlh = (p0 >> g.tw_sh) & (g.th - 1), qln = p0 >> (g.tw_sh + g.th_sh);
+        bool failed = false;   // a wait ran out: skip the work of the remaining tiles, keep meeting the group barriers
 
         TileWalker tw;
         tw.init(g, blockIdx.x);
@@ -680,8 +691,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             if (!single_class)
                 off_row += (size_t)((int)g.row_cls[min(oh, g.oh - 1)] * g.n_col_cls + (int)g.col_cls[min(ow, g.ow - 1)]) * g.kpad;
 
-            // per-channel tables change with the channel tile (all threads are past the previous
-            // tile's compute once they are through the barrier below)
+            // per-channel tables change with the channel tile: the group meets before (everyone is
+            // past the previous tile's reads) and after the reload
             if (nt != cur_nt) {
                 epi_bar_sync(group, group_threads);
                 for (int j = et; j < g.bn; j += group_threads) {
@@ -691,88 +702,105 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                     if (single_class)
                         s_off[j] = g.off[k0 + j];
                 }
+                epi_bar_sync(group, group_threads);
                 cur_nt = nt;
             }
-            // the group's previous store must have finished reading the staging buffer
-            if (store_pending && et == 0)
-                tma_store_wait_read();
-            // one barrier: makes the staging buffer and the tables safe, and makes the outcome of the
-            // bounded wait uniform over the epilogue threads
-            if (!epi_bar_all(group, group_threads, mbar_wait(tfull_bar(as), aphase, abort_flag))) {
-                if (et == 0) {
-                    atomicCAS(g.status, 0, kErrEpilogueWait);
-                    *abort_flag = 1;
+            if (!failed) {
+                // this warp's previous store must have finished reading its part of the staging buffer
+                if (store_pending) {
+                    if (lane == 0)
+                        tma_store_wait_read();
+                    __syncwarp();
                 }
-                break;
+                if (!__all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aphase, abort_flag))) {
+                    if (lane == 0) {
+                        atomicCAS(g.status, 0, kErrEpilogueWait);
+                        *abort_flag = 1;
+                    }
+                    failed = true;
+                }
             }
-            tc_fence_after();
-            const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * g.bn);
-            // The warps that share a lane quarter take 32-column chunks round-robin; with four warps
-            // per scheduler the tensor-memory read of one warp overlaps the arithmetic of the others.
-            for (int c0 = sub_warp * 32; c0 < g.bn; c0 += (group_warps >> 2) * 32) {
-                uint32_t v[32];
-                const int ncol = min(32, g.bn - c0);   // 32, or 16 for the last chunk of bn % 32 == 16
-                if (ncol == 32)
-                    tmem_ld32(t_row + c0, v);
-                else
-                    tmem_ld16(t_row + c0, v);
-                tmem_ld_wait();
-                // the common case is one straight-line block of 32 independent chains
-                if (fast_epi && ncol == 32) {
-                    if (single_class) {
-                        if (no_floor)
-                            epi_chunk<true, true, 32, false>(v, c0, off_row, ec);
-                        else
-                            epi_chunk<true, true, 32>(v, c0, off_row, ec);
+            if (!failed) {
+                tc_fence_after();
+                const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * g.bn);
+                for (int c0 = 0; c0 < g.bn; c0 += 32) {
+                    if (((c0 >> own_sh) & (wpq - 1)) != sub_warp)
+                        continue;
+                    uint32_t v[32];
+                    const int ncol = min(32, g.bn - c0);   // 32, or 16 for the last chunk of bn % 32 == 16
+                    if (ncol == 32)
+                        tmem_ld32(t_row + c0, v);
+                    else
+                        tmem_ld16(t_row + c0, v);
+                    tmem_ld_wait();
+                    // the common case is one straight-line block of 32 independent chains
+                    if (fast_epi && ncol == 32) {
+                        if (single_class) {
+                            if (no_floor)
+                                epi_chunk<true, true, 32, false>(v, c0, off_row, ec);
+                            else
+                                epi_chunk<true, true, 32>(v, c0, off_row, ec);
+                        } else {
+                            if (no_floor)
+                                epi_chunk<true, false, 32, false>(v, c0, off_row, ec);
+                            else
+                                epi_chunk<true, false, 32>(v, c0, off_row, ec);
+                        }
+                    } else if (fast_epi) {
+                        epi_chunk<true, false, 16>(v, c0, off_row, ec);
+                    } else if (ncol == 32) {
+                        epi_chunk<false, false, 32>(v, c0, off_row, ec);
                     } else {
-                        if (no_floor)
-                            epi_chunk<true, false, 32, false>(v, c0, off_row, ec);
-                        else
-                            epi_chunk<true, false, 32>(v, c0, off_row, ec);
+                        epi_chunk<false, false, 16>(v, c0, off_row, ec);
                     }
-                } else if (fast_epi) {
-                    epi_chunk<true, false, 16>(v, c0, off_row, ec);
-                } else if (ncol == 32) {
-                    epi_chunk<false, false, 32>(v, c0, off_row, ec);
+                }
+                // accumulator stage drained: hand it back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                    mbar_arrive(tempty_bar(as));
+
+                if (g.use_tma_store) {
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        for (int sub = 0; sub < n_sub; ++sub) {
+                            // ownership is by granules of max(ob, 32) bytes (with ob == 16 two neighbouring
+                            // sub-tiles form one granule)
+                            if (((((sub << g.ob_sh) >> own_sh) & (wpq - 1)) == sub_warp) && k0 + (sub << g.ob_sh) < g.cout)
+                                tma_store_4d(&maps.y, smem_u32(s_out + (((size_t)sub * kTileM + p0) << g.ob_sh)),
+                                             k0 + (sub << g.ob_sh), ow0 + qlw, oh0 + qlh, n0 + qln);
+                        }
+                        tma_store_commit();
+                    }
+                    store_pending = true;
                 } else {
-                    epi_chunk<false, false, 16>(v, c0, off_row, ec);
+                    // plain stores for channel counts the TMA store cannot address (Cout % 16 != 0):
+                    // every thread copies the columns its warp computed for its pixel
+                    __syncwarp();
+                    if (pix_valid) {
+                        uint8_t *dst = g.y + (((size_t)img * g.oh + oh) * g.ow + ow) * g.cout + k0;
+                        const int nvalid = min(g.bn, g.cout - k0);
+                        for (int j = 0; j < nvalid; ++j) {
+                            if (((j >> own_sh) & (wpq - 1)) != sub_warp)
+                                continue;
+                            const int sub = j >> g.ob_sh, cin = j & (g.ob - 1);
+                            const int chunk = cin >> 4;
+                            dst[j] = s_out[(((size_t)sub * kTileM + row) << g.ob_sh) + ((chunk ^ sw) << 4) + (cin & 15)];
+                        }
+                    }
+                    __syncwarp();
                 }
             }
-            // accumulator stage drained: hand it back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0)
-                mbar_arrive(tempty_bar(as));
-            aphase ^= 1;
-
-            if (g.use_tma_store) {
-                fence_async_smem();
-                epi_bar_sync(group, group_threads);
-                if (et == 0) {
-                    for (int sub = 0; sub < n_sub; ++sub) {
-                        if (k0 + (sub << g.ob_sh) < g.cout)
-                            tma_store_4d(&maps.y, smem_u32(s_out + (((size_t)sub * kTileM) << g.ob_sh)), k0 + (sub << g.ob_sh), ow0, oh0, n0);
-                    }
-                    tma_store_commit();
-                }
-                store_pending = true;
-            } else {
-                // plain stores for channel counts the TMA store cannot address (Cout % 16 != 0)
-                epi_bar_sync(group, group_threads);
-                if (pix_valid && sub_warp == 0) {
-                    uint8_t *dst = g.y + (((size_t)img * g.oh + oh) * g.ow + ow) * g.cout + k0;
-                    const int nvalid = min(g.bn, g.cout - k0);
-                    for (int j = 0; j < nvalid; ++j) {
-                        const int sub = j >> g.ob_sh, cin = j & (g.ob - 1);
-                        const int chunk = cin >> 4;
-                        dst[j] = s_out[(((size_t)sub * kTileM + row) << g.ob_sh) + ((chunk ^ sw) << 4) + (cin & 15)];
-                    }
-                }
+            as += g.groups;                          // the group's next tile: stage (as + groups) mod acc_stages
+            if (as >= g.acc_stages) {
+                as -= g.acc_stages;
+                aphase ^= 1;
             }
             for (int i = 0; i < g.groups; ++i)
                 tw.advance(g);
         }
-        if (store_pending && et == 0)
+        if (store_pending && lane == 0)
             tma_store_wait_all();
     }
 
@@ -832,7 +860,7 @@ int encode(CUtensorMap *m, void *base, int rank, const cuuint64_t *dims, const c
 
 struct ConvIgemmPlan {
     ConvGeom g;
-    int groups = 2;
+    int groups = 2, acc_stages = 2;
     int bk = 0, bn = 0, stages = 0, kgroup = 1, ob = 0, kpad = 0, b_resident = 0, a_wide = 0;
     int n_row_cls = 0, n_col_cls = 0;
     int generic_requant = 0;
@@ -951,8 +979,11 @@ int conv_igemm_create(
             p->bn = best;
         }
     }
-    // staging sub-tile width: the largest of 128/64/32/16 that divides bn
-    p->ob = p->bn % 128 == 0 ? 128 : (p->bn % 64 == 0 ? 64 : (p->bn % 32 == 0 ? 32 : 16));
+    if (const char *e = getenv("B200_IGEMM_BN")) {   // tuning aid: channel-tile width, a multiple of 16 up to 256
+        int v = atoi(e);
+        if (v >= 16 && v <= 256 && v % 16 == 0 && v <= (g.k + 15) / 16 * 16)
+            p->bn = v;
+    }
     const int n_tiles_n = (g.k + p->bn - 1) / p->bn;
     p->kpad = n_tiles_n * p->bn;
     // pipeline depth from the shared memory left after the staging buffer
@@ -966,6 +997,23 @@ int conv_igemm_create(
             int v = atoi(e);
             if (v == 2 || (v == 4 && 4 * p->bn <= 512))
                 p->groups = v;
+        }
+        // staging sub-tile width: the largest of 128/64/32/16 that divides bn and, where possible,
+        // gives the warps that share a lane quarter the same number of sub-tiles
+        {
+            const int wpq = (kEpiWarps / p->groups) / 4;
+            p->ob = 0;
+            for (int ob = 128; ob >= 16 && !p->ob; ob >>= 1)
+                if (p->bn % ob == 0 && (p->bn / ob) % wpq == 0)
+                    p->ob = ob;
+            if (!p->ob)
+                p->ob = p->bn % 128 == 0 ? 128 : (p->bn % 64 == 0 ? 64 : (p->bn % 32 == 0 ? 32 : 16));
+        }
+        p->acc_stages = 4 * p->bn <= 512 ? 4 : p->groups;
+        if (const char *e = getenv("B200_IGEMM_ACC")) {
+            int v = atoi(e);
+            if ((v == 2 || v == 4) && v * p->bn <= 512 && v >= p->groups)
+                p->acc_stages = v;
         }
         p->b_resident = n_tiles_n == 1 && smem_layout(3, kblocks, p->bk, p->bn, p->groups).total + 1024 <= 227 * 1024;
         // Narrow k-blocks (few bytes per barrier round trip) travel in groups: the largest divisor of
@@ -1117,7 +1165,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.tiles_h = (g.oh + a.th - 1) / a.th;
     a.tiles_n = (n + a.tn - 1) / a.tn;
     a.n_tiles_n = p->kpad / p->bn;
-    a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.kgroup = p->kgroup; a.groups = p->groups;
+    a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.kgroup = p->kgroup; a.groups = p->groups; a.acc_stages = p->acc_stages;
     a.rcp_cchunks = (uint32_t)(((1ull << 30) + (uint64_t)(g.c / p->bk) - 1) / (uint64_t)(g.c / p->bk));
     a.rcp_s = (uint32_t)(((1ull << 30) + (uint64_t)g.s - 1) / (uint64_t)g.s); a.ob = p->ob; a.b_resident = p->b_resident; a.a_wide = p->a_wide;
     for (a.tw_sh = 0; (1 << a.tw_sh) < a.tw; ++a.tw_sh) {}
@@ -1127,7 +1175,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     // (1 at bit 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
     a.idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(p->bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
     uint32_t cols = 32;
-    while (cols < (uint32_t)(p->groups * p->bn))
+    while (cols < (uint32_t)(p->acc_stages * p->bn))
         cols <<= 1;
     a.tmem_cols = cols;
     a.off = p->off_dev; a.mult = p->mult_dev; a.shift = p->shift_dev;
@@ -1185,7 +1233,11 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     if (a.use_tma_store) {
         cuuint64_t dims[4] = { (cuuint64_t)g.k, (cuuint64_t)g.ow, (cuuint64_t)g.oh, (cuuint64_t)n };
         cuuint64_t strides[3] = { (cuuint64_t)g.k, (cuuint64_t)g.ow * g.k, (cuuint64_t)g.oh * g.ow * g.k };
-        cuuint32_t box[4] = { (cuuint32_t)p->ob, (cuuint32_t)a.tw, (cuuint32_t)a.th, (cuuint32_t)a.tn };
+        // one store covers the 32 pixels of a tensor-memory lane quarter: a sub-box of the tile
+        cuuint32_t qw = a.tw >= 32 ? 32 : a.tw;
+        cuuint32_t qh = a.tw >= 32 ? 1 : (a.tw * a.th >= 32 ? 32 / a.tw : a.th);
+        cuuint32_t qn = a.tw * a.th >= 32 ? 1 : 32 / (a.tw * a.th);
+        cuuint32_t box[4] = { (cuuint32_t)p->ob, qw, qh, qn };
         B200_TRY(encode(&p->maps.y, y, 4, dims, strides, box, swizzle_for(p->ob)));
     } else {
         p->maps.y = p->maps.b;
