@@ -41,6 +41,22 @@ int status_word_ptr(int **dev_ptr);
 // Number of SMs of the current device (cached).
 int sm_count();
 
+// Grid of a grid-stride kernel: the blocks that are resident at one time (occupancy x SMs), or
+// fewer when there is less work.  A larger grid would run a second, partly filled wave.
+template <auto Kernel, int Threads>
+int resident_grid(size_t blocks_wanted)
+{
+    static const int per_sm = [] {
+        int occ = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, Kernel, Threads, 0) != cudaSuccess || occ < 1)
+            occ = 1;
+        return occ;
+    }();
+    const size_t cap = (size_t)sm_count() * per_sm;
+    const size_t blocks = blocks_wanted < cap ? blocks_wanted : cap;
+    return (int)(blocks < 1 ? 1 : blocks);
+}
+
 // Host restatement of quant_helper.h:60-118 (see b200_get_quant_scale).
 void get_quant_scale(float x, int bits, uint32_t *mult, int8_t *shift);
 // Host restatement of quant_helper.h:55-58.

@@ -229,10 +229,7 @@ int conv_lower_rows_launch(const ConvGeom &g, const uint8_t *x, int n, uint8_t *
     if (g.c != 4 || (((uintptr_t)x) & 3) != 0 || (((uintptr_t)out) & 15) != 0)
         return fail(B200_ERR_INVALID, "conv(lower): needs a 4-channel, word-aligned input");
     const size_t total = (size_t)n * g.h * g.ow;
-    size_t blocks = (total + 255) / 256;
-    const size_t cap = (size_t)sm_count() * 16;
-    if (blocks > cap)
-        blocks = cap;
+    const int blocks = resident_grid<conv_lower_rows_kernel, 256>((total + 255) / 256);
     conv_lower_rows_kernel<<<(unsigned)blocks, 256, 0, st>>>(
         reinterpret_cast<const uint32_t *>(x), reinterpret_cast<uint4 *>(out), n, g.h, g.w, g.ow, g.stride_w, g.pad_w,
         (uint32_t)g.izp * 0x01010101u);

@@ -264,18 +264,6 @@ __global__ void __launch_bounds__(256) lut_u8_kernel(
             y[e] = lut[x[e]];
 }
 
-static int grid_for(size_t work_items, int threads, int per_sm)
-{
-    size_t blocks = (work_items + threads - 1) / threads;
-    size_t cap = (size_t)sm_count() * per_sm;
-    if (blocks > cap)
-        blocks = cap;
-    if (blocks < 1)
-        blocks = 1;
-    return (int)blocks;
-}
-
-
 int relu_build_lut(
     float ialpha, uint8_t izp, float oalpha, uint8_t ozp, uint8_t obits, uint8_t lut[256])
 {
@@ -304,7 +292,7 @@ int lut_u8_launch(const uint8_t *x, uint8_t *y, size_t count, const uint8_t *lut
         return fail(B200_ERR_INVALID, "relu: buffers must be 16-byte aligned");
     if (count == 0)
         return B200_OK;
-    int grid = grid_for(count / 16 + 1, 256, 8);
+    const int grid = resident_grid<lut_u8_kernel, 256>((count / 16 + 1 + 255) / 256);
     lut_u8_kernel<<<grid, 256, 0, st>>>(x, y, count, lut_dev);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
@@ -465,28 +453,31 @@ int b200_eltwise_sum_u8(
         else
             fast = false;
     }
-    int grid = grid_for(count / 32 + 1, 256, 8);
+    const size_t want = (count / 32 + 1 + 255) / 256;
     cudaStream_t st = as_stream(stream);
+#define B200_ELT_LAUNCH(...) \
+    eltwise_sum_kernel<__VA_ARGS__><<<resident_grid<eltwise_sum_kernel<__VA_ARGS__>, 256>(want), 256, 0, st>>>(a, y, count)
     if (fast) {
         switch (n_in) {
-        case 1: eltwise_sum_kernel<1, true><<<grid, 256, 0, st>>>(a, y, count); break;
+        case 1: B200_ELT_LAUNCH(1, true); break;
         case 2:
             if (a.ozp == 0 && a.relu_lo <= 0)
-                eltwise_sum_kernel<2, true, true><<<grid, 256, 0, st>>>(a, y, count);
+                B200_ELT_LAUNCH(2, true, true);
             else
-                eltwise_sum_kernel<2, true><<<grid, 256, 0, st>>>(a, y, count);
+                B200_ELT_LAUNCH(2, true);
             break;
-        case 3: eltwise_sum_kernel<3, true><<<grid, 256, 0, st>>>(a, y, count); break;
-        default: eltwise_sum_kernel<4, true><<<grid, 256, 0, st>>>(a, y, count); break;
+        case 3: B200_ELT_LAUNCH(3, true); break;
+        default: B200_ELT_LAUNCH(4, true); break;
         }
     } else {
         switch (n_in) {
-        case 1: eltwise_sum_kernel<1, false><<<grid, 256, 0, st>>>(a, y, count); break;
-        case 2: eltwise_sum_kernel<2, false><<<grid, 256, 0, st>>>(a, y, count); break;
-        case 3: eltwise_sum_kernel<3, false><<<grid, 256, 0, st>>>(a, y, count); break;
-        default: eltwise_sum_kernel<4, false><<<grid, 256, 0, st>>>(a, y, count); break;
+        case 1: B200_ELT_LAUNCH(1, false); break;
+        case 2: B200_ELT_LAUNCH(2, false); break;
+        case 3: B200_ELT_LAUNCH(3, false); break;
+        default: B200_ELT_LAUNCH(4, false); break;
         }
     }
+#undef B200_ELT_LAUNCH
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

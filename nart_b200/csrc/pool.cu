@@ -240,17 +240,15 @@ int pool_launch(
         : (c % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 3) == 0)       ? 4
                                                                            : 1;
     size_t total = (size_t)n * g.oh * g.ow * (c / vec);
-    size_t blocks = (total + 255) / 256;
-    size_t cap = (size_t)sm_count() * 8;
-    int grid = (int)(blocks < cap ? blocks : cap);
+    const size_t blocks = (total + 255) / 256;
     if (method == 0) {
-        if (vec == 16) pool_max_kernel<16><<<grid, 256, 0, st>>>(x, y, g, lut_dev);
-        else if (vec == 4) pool_max_kernel<4><<<grid, 256, 0, st>>>(x, y, g, lut_dev);
-        else pool_max_kernel<1><<<grid, 256, 0, st>>>(x, y, g, lut_dev);
+        if (vec == 16) pool_max_kernel<16><<<resident_grid<pool_max_kernel<16>, 256>(blocks), 256, 0, st>>>(x, y, g, lut_dev);
+        else if (vec == 4) pool_max_kernel<4><<<resident_grid<pool_max_kernel<4>, 256>(blocks), 256, 0, st>>>(x, y, g, lut_dev);
+        else pool_max_kernel<1><<<resident_grid<pool_max_kernel<1>, 256>(blocks), 256, 0, st>>>(x, y, g, lut_dev);
     } else {
-        if (vec == 16) pool_avg_kernel<16><<<grid, 256, 0, st>>>(x, y, g, tab);
-        else if (vec == 4) pool_avg_kernel<4><<<grid, 256, 0, st>>>(x, y, g, tab);
-        else pool_avg_kernel<1><<<grid, 256, 0, st>>>(x, y, g, tab);
+        if (vec == 16) pool_avg_kernel<16><<<resident_grid<pool_avg_kernel<16>, 256>(blocks), 256, 0, st>>>(x, y, g, tab);
+        else if (vec == 4) pool_avg_kernel<4><<<resident_grid<pool_avg_kernel<4>, 256>(blocks), 256, 0, st>>>(x, y, g, tab);
+        else pool_avg_kernel<1><<<resident_grid<pool_avg_kernel<1>, 256>(blocks), 256, 0, st>>>(x, y, g, tab);
     }
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
