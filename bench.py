@@ -179,6 +179,26 @@ def run_reference_arm(a):
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
+def fused_residual_convs(spec):
+    """Names of the conv outputs whose residual add the case runner folds into the conv: the later
+    produced input of a two-input eltwise op, when a conv makes it and nothing else reads it."""
+    ops = spec["ops"]
+    producer = {op["out"]: i for i, op in enumerate(ops)}
+    readers = {}
+    for op in ops:
+        for n in op["ins"]:
+            readers[n] = readers.get(n, 0) + 1
+    readers[spec["output"]] = readers.get(spec["output"], 0) + 1
+    out = set()
+    for op in ops:
+        if op["op"] != "eltwise" or len(op["ins"]) != 2:
+            continue
+        p = max(producer.get(op["ins"][0], -1), producer.get(op["ins"][1], -1))
+        if p >= 0 and ops[p]["op"] == "conv" and readers.get(ops[p]["out"], 0) == 1:
+            out.add(ops[p]["out"])
+    return out
+
+
 def conv_bytes_ops(spec, batch):
     """Algorithmic bytes and ops of each conv op: every tensor once (1 B/element), weights and
     bias once, 2*MACs; true dims."""
@@ -258,18 +278,30 @@ def run_gpu_arm(a):
     igemm_ms = 0.0
     igemm_launches = 0
     igemm_bytes = igemm_ops = 0.0
-    cb = conv_bytes_ops(spec, batch)
+    # conv launches come in the order of the spec's conv / ip ops; a conv that carries a residual add
+    # in its epilogue also reads the residual tensor (1 B per output element)
+    cb = [c for c in conv_bytes_ops(spec, batch) if c is not None]
+    fused = fused_residual_convs(spec)
+    if cs.launch_count() != len(spec["ops"]) + 3 - len(fused):   # input layout, row lowering, output; one less per fusion
+        fused = set()
+    conv_names = [op["out"] for op in spec["ops"] if op["op"] in ("conv", "ip")]
     for _ in range(a.steps):
         cs.run_device(batch, stream)
         prof = cs.profile()
-        for i, (ms, kind) in enumerate(prof):
+        ci = 0
+        for ms, kind in prof:
             per_kind[kind] = per_kind.get(kind, 0.0) + ms
-            if kind == 1:
-                igemm_ms += ms
-                igemm_launches += 1
-                byts, ops = cb[i - 1]   # launch 0 is the input layout kernel
-                igemm_bytes += byts
-                igemm_ops += ops
+            if kind in (1, 2):
+                byts, ops = cb[ci]
+                if conv_names[ci] in fused:
+                    t = spec["tensors"][conv_names[ci]]
+                    byts += batch * t["c"] * t["h"] * t["w"]
+                ci += 1
+                if kind == 1:
+                    igemm_ms += ms
+                    igemm_launches += 1
+                    igemm_bytes += byts
+                    igemm_ops += ops
     cs.set_profiling(False)
 
     # ---- end to end through the host-buffer entry points ------------------------------------------
@@ -328,6 +360,7 @@ def run_gpu_arm(a):
                         l2="working set per step (5.6 GB of activations) is far larger than L2; no flush needed",
                         launch="one CUDA graph per step" if not a.no_graph else "op by op",
                         kernel_times="CUDA events around every launch, a second pass of the same K steps",
+                        fused_residual_adds=len(fused),
                         conv_tops=igemm_ops / sec / 1e12, ms_per_step_by_kernel=breakdown,
                         conv_gop_per_image=nets.conv_ops_per_image(spec) / 1e9, logits_checksum=logits_checksum),
             roofline=dict(bound="hbm", achieved=hbm_ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=hbm_ach / peaks["hbm_gbs"],

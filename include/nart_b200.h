@@ -153,6 +153,26 @@ B200_API int b200_conv2d_destroy(b200_conv_t *conv);
 B200_API int b200_conv2d_run_static_scratch(
     b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, b200_stream_t stream);
 
+/* Residual add fused into the conv (no such op in the reference's CPU module; its GPU module
+ * fuses ReLU into conv and eltwise the same way, python/nart/modules/cuda_quant.py:300-330).
+ * After b200_conv2d_fuse_residual_add the plan computes, in one kernel,
+ *     y = eltwise_sum(conv(x), res)      -- op_quant_eltwise_accumulate_output_sum,
+ *                                           art/modules/quant/src/op/eltwise.c:137-174
+ * bit for bit as the two separate ops would: the conv's value is requantized and saturated to
+ * uint8 first, then both inputs go through the eltwise integer formula.  conv_input (0 or 1) says
+ * which eltwise input is the conv's output; ialpha / izp / coeff (NULL = all 1) are the eltwise
+ * op's two-entry arrays in its own input order, ialpha[conv_input] and izp[conv_input] must be the
+ * conv's oalpha and ozp.  Returns B200_ERR_UNSUPPORTED, leaving the plan unchanged, when the plan
+ * cannot take it (not on the tensor-core path, output channels not a multiple of 32, obits != 8,
+ * a requantize shift below 33): the caller then runs b200_eltwise_sum_u8 as a separate step.
+ * A fused plan runs only through b200_conv2d_run_residual (res: NHWC, the dims of y). */
+B200_API int b200_conv2d_fuse_residual_add(
+    b200_conv_t *conv, int32_t conv_input, const float *ialpha, const uint8_t *izp,
+    const float *coeff, float oalpha, uint8_t ozp, uint8_t obits, int32_t relu);
+B200_API int b200_conv2d_run_residual(
+    b200_conv_t *conv, const uint8_t *x, int32_t n, const uint8_t *res, uint8_t *y,
+    b200_stream_t stream);
+
 /* ---- ip (fully connected) -------------------------------------------------------------------
  * op_quant_ip_u8xu8_run (art/modules/quant/src/op/ip.cpp:133-209): a conv whose kernel covers
  * the whole c x h x w input.  weights: host [k][c*h*w] in the reference's flattened-NCHW column
@@ -282,6 +302,15 @@ B200_API int b200_case_submit_host(
 B200_API int b200_case_wait(b200_case_t *cs);
 /* Number of kernels one b200_case_run_device launches. */
 B200_API int b200_case_launch_count(const b200_case_t *cs, int32_t *launches);
+/* Folds residual adds into the convs that feed them (default: off; call before b200_case_prepare).
+ * Off by default because on B200 the conv epilogue is bound by instruction issue, not by memory:
+ * ResNet-50 at batch 256 runs 3.62 ms per step fused against 3.39 ms with the adds as kernels of
+ * their own, although the fused form moves 2.7 GB less.
+ * A two-input eltwise SUM whose later-produced input is the output of a tensor-core conv that
+ * nothing else reads then runs in that conv's epilogue (b200_conv2d_fuse_residual_add) and its own
+ * kernel is skipped; results are unchanged.  No counterpart in the reference's CPU module, whose
+ * parade runs every op as its own pass (art/src/parade.c:184-197). */
+B200_API int b200_case_set_fusion(b200_case_t *cs, int32_t enable);
 /* Replays b200_case_run_device as one CUDA graph per (batch, stream) instead of launching op by op
  * (the reference's parade_run loop, art/src/parade.c:184-197, launches one op at a time): the first
  * run at a batch size is eager, the second is captured, later ones replay.  Off by default; ignored

@@ -58,6 +58,9 @@ SIGNATURES = {
     "b200_conv2d_run_acc": (C.c_int, [vp, vp, i32, vp, vp, vp]),
     "b200_conv2d_destroy": (C.c_int, [vp]),
     "b200_conv2d_run_static_scratch": (C.c_int, [vp, vp, i32, vp, vp]),
+    "b200_conv2d_fuse_residual_add": (C.c_int, [vp, i32, C.POINTER(f32), C.POINTER(u8), C.POINTER(f32), f32, u8, u8,
+                                               i32]),
+    "b200_conv2d_run_residual": (C.c_int, [vp, vp, i32, vp, vp, vp]),
     "b200_ip_create": (C.c_int, [i32, i32, i32, i32, f32, u8, C.POINTER(f32), i32, u8, f32, u8, u8,
                                  vp, vp, C.POINTER(vp)]),
     "b200_quantize_u8": (C.c_int, [vp, vp, i32, i32, i32, i32, f32, u8, u8, i32, vp]),
@@ -95,6 +98,7 @@ SIGNATURES = {
     "b200_case_wait": (C.c_int, [vp]),
     "b200_case_launch_count": (C.c_int, [vp, pi32]),
     "b200_case_use_graph": (C.c_int, [vp, i32]),
+    "b200_case_set_fusion": (C.c_int, [vp, i32]),
     "b200_case_set_profiling": (C.c_int, [vp, i32]),
     "b200_case_profile": (C.c_int, [vp, C.POINTER(f32), pi32, i32, pi32]),
 }

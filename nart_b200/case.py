@@ -124,6 +124,10 @@ class Case:
         """Replay run_device as one CUDA graph per batch size (see b200_case_use_graph)."""
         check(lib.b200_case_use_graph(self._h, int(enable)))
 
+    def set_fusion(self, enable: bool):
+        """Residual adds inside the feeding conv's epilogue (default off); call before prepare."""
+        check(lib.b200_case_set_fusion(self._h, int(enable)))
+
     def set_profiling(self, enable: bool):
         check(lib.b200_case_set_profiling(self._h, int(enable)))
 

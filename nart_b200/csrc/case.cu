@@ -30,6 +30,8 @@ struct CaseOp {
     int out = -1;
     // conv / ip
     b200_conv_t *conv = nullptr;
+    int residual = -1;        // tensor added in the conv's epilogue (a fused eltwise SUM), or -1
+    bool skipped = false;     // an eltwise op whose work a conv has taken over
     // eltwise
     std::vector<float> ialpha, coeff;
     std::vector<uint8_t> izp;
@@ -63,6 +65,8 @@ struct b200_case {
     std::vector<CaseIO> inputs, outputs;
     int max_batch = 0;
     bool prepared = false;
+    bool fuse = false;                 // fold residual adds into the convs that feed them (b200_case_set_fusion)
+    int fused_adds = 0;
     int device = 0;
     // per-launch timing (off by default)
     bool profiling = false;
@@ -110,6 +114,45 @@ int check_tensor(const b200_case *cs, int id, const char *what)
     if (id < 0 || id >= (int)cs->tensors.size())
         return fail(B200_ERR_INVALID, "%s: tensor id %d does not exist", what, id);
     return B200_OK;
+}
+
+// A two-input eltwise SUM whose later-produced input comes from a conv that nothing else reads is
+// folded into that conv's epilogue: the conv then writes the eltwise op's output tensor and the
+// eltwise op is skipped.  The values are those of the two separate ops (see
+// b200_conv2d_fuse_residual_add); convs that cannot take the fusion keep the separate kernel.
+void fuse_residual_adds(b200_case *cs)
+{
+    const int n_ops = (int)cs->ops.size();
+    std::vector<int> readers(cs->tensors.size(), 0), producer(cs->tensors.size(), -1);
+    for (int i = 0; i < n_ops; ++i) {
+        for (int t : cs->ops[i].ins)
+            readers[t]++;
+        producer[cs->ops[i].out] = i;
+    }
+    for (const auto &io : cs->outputs)
+        readers[io.tensor]++;
+    for (int i = 0; i < n_ops; ++i) {
+        CaseOp &add = cs->ops[i];
+        if (add.kind != OpKind::Eltwise || add.ins.size() != 2 || add.ins[0] == add.ins[1])
+            continue;
+        // the input produced last is the one whose producer can see the other input complete
+        const int p0 = producer[add.ins[0]], p1 = producer[add.ins[1]];
+        const int ci = p0 > p1 ? 0 : 1;
+        const int pi = ci == 0 ? p0 : p1;
+        if (pi < 0 || pi >= i)
+            continue;
+        CaseOp &conv = cs->ops[pi];
+        if (conv.kind != OpKind::Conv || conv.residual >= 0 || readers[conv.out] != 1)
+            continue;
+        const float *coeff = add.has_coeff ? add.coeff.data() : nullptr;
+        if (b200_conv2d_fuse_residual_add(conv.conv, ci, add.ialpha.data(), add.izp.data(), coeff, add.oalpha,
+                                          add.ozp, add.obits, add.relu) != B200_OK)
+            continue;   // not this conv: the eltwise kernel stays
+        conv.residual = add.ins[1 - ci];
+        conv.out = add.out;
+        add.skipped = true;
+        cs->fused_adds++;
+    }
 }
 
 }  // namespace
@@ -351,6 +394,8 @@ int b200_case_prepare(b200_case_t *cs, int32_t max_batch)
     if (max_batch <= 0)
         return fail(B200_ERR_INVALID, "case_prepare: max_batch must be positive");
     cs->max_batch = max_batch;
+    if (cs->fuse)
+        fuse_residual_adds(cs);
     for (auto &t : cs->tensors) {
         // 256 spare bytes: vector loads of the last pixel may read past a ragged channel count
         size_t bytes = t.bytes_per_image() * max_batch + 256;
@@ -525,11 +570,16 @@ static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream, int p
         return B200_OK;
     for (auto &op : cs->ops) {
         int kind = 0;
+        if (op.skipped)
+            continue;
         CaseTensor &to = cs->tensors[op.out];
         const CaseTensor &ti = cs->tensors[op.ins[0]];
         switch (op.kind) {
         case OpKind::Conv:
-            B200_TRY(b200_conv2d_run(op.conv, ti.dev, batch, to.dev, stream));
+            if (op.residual >= 0)
+                B200_TRY(b200_conv2d_run_residual(op.conv, ti.dev, batch, cs->tensors[op.residual].dev, to.dev, stream));
+            else
+                B200_TRY(b200_conv2d_run(op.conv, ti.dev, batch, to.dev, stream));
             kind = b200_conv2d_algo(op.conv) == B200_CONV_ALGO_IGEMM ? 1 : 2;
             break;
         case OpKind::Eltwise: {
@@ -565,6 +615,13 @@ static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream, int p
         cs->last_stream = cst;
         cs->have_profile = true;
     }
+    return B200_OK;
+}
+
+int b200_case_set_fusion(b200_case_t *cs, int32_t enable)
+{
+    B200_TRY(check_building(cs, "case_set_fusion"));
+    cs->fuse = enable != 0;
     return B200_OK;
 }
 
@@ -684,9 +741,12 @@ int b200_case_launch_count(const b200_case_t *cs, int32_t *launches)
     if (!cs || !launches)
         return fail(B200_ERR_INVALID, "case_launch_count: NULL argument");
     int n = (int)(cs->inputs.size() + cs->ops.size() + cs->outputs.size());
-    for (const auto &op : cs->ops)
+    for (const auto &op : cs->ops) {
         if (op.conv && op.conv->lowered)
             ++n;   // the row-lowering kernel runs ahead of the convolution kernel
+        if (op.skipped)
+            --n;   // an eltwise op that runs inside a conv's epilogue
+    }
     *launches = n;
     return B200_OK;
 }

@@ -98,6 +98,11 @@ struct IgemmArgs {
     int use_tma_store;       // 0: plain stores (Cout not a multiple of 16)
     uint8_t *y;
     int *status;
+    // fused residual add (eltwise SUM of this conv's output and `res`, see EltwiseArgs): index 0 is
+    // the conv's own output, index 1 the residual tensor (NHWC, the dims of y); res == nullptr: off
+    const uint8_t *res;
+    int r_m[2], r_add[2], r_b[2];
+    int r_s0, r_ozp, r_lo;
 };
 
 // Tile index -> (Cout tile, ow tile, oh tile, image tile), Cout tile fastest.  A persistent CTA
@@ -319,6 +324,7 @@ struct EpiConsts {
     uint8_t *s_out;            // staging buffer of this epilogue group
     int ob, ob_sh, sw, row;
     int qmax, relu_lo;
+    int r_m0, r_add0, r_b0, r_m1, r_add1, r_b1, r_s0, r_ozp, r_lo;   // fused residual add
 };
 
 // One chunk of NCOL (32 or 16) accumulator columns of this thread's row: requantize, pack, write to
@@ -331,8 +337,9 @@ struct EpiConsts {
 // the per-class rows in global memory.  All flags are compile-time so that the body is one
 // straight-line block of independent chains.  FLOOR = false drops the ReLU floor when it is 0, where
 // the pack's own clamp already applies it.
-template <bool FAST, bool SMEM_OFF, int NCOL, bool FLOOR = true>
-__device__ __forceinline__ void epi_chunk(const uint32_t (&v)[32], int c0, const long long *off_row, const EpiConsts &ec)
+template <bool FAST, bool SMEM_OFF, int NCOL, bool FLOOR = true, bool RES = false>
+__device__ __forceinline__ void epi_chunk(const uint32_t (&v)[32], int c0, const long long *off_row, const EpiConsts &ec,
+                                          const uint32_t (&rv)[8])
 {
     uint32_t packed[NCOL / 4];
 #pragma unroll
@@ -364,6 +371,20 @@ __device__ __forceinline__ void epi_chunk(const uint32_t (&v)[32], int c0, const
             q2 = min((int)(p2 >> s4.z), ec.qmax);
             q3 = min((int)(p3 >> s4.w), ec.qmax);
         }
+        if (RES) {
+            // fused eltwise SUM with the residual bytes rv: the conv's own value is first saturated as
+            // it would have been stored (floor, then 0..255), then both inputs go through
+            // (x * m + add) >> b, the sum through >> s0 plus the output zero point and floor
+            const uint32_t rw = rv[q4];
+            const int a0 = min(max(q0, ec.relu_lo), 255), a1 = min(max(q1, ec.relu_lo), 255);
+            const int a2 = min(max(q2, ec.relu_lo), 255), a3 = min(max(q3, ec.relu_lo), 255);
+            const int t0 = ((a0 * ec.r_m0 + ec.r_add0) >> ec.r_b0) + (((int)(rw & 0xff) * ec.r_m1 + ec.r_add1) >> ec.r_b1);
+            const int t1 = ((a1 * ec.r_m0 + ec.r_add0) >> ec.r_b0) + (((int)((rw >> 8) & 0xff) * ec.r_m1 + ec.r_add1) >> ec.r_b1);
+            const int t2 = ((a2 * ec.r_m0 + ec.r_add0) >> ec.r_b0) + (((int)((rw >> 16) & 0xff) * ec.r_m1 + ec.r_add1) >> ec.r_b1);
+            const int t3 = ((a3 * ec.r_m0 + ec.r_add0) >> ec.r_b0) + (((int)(rw >> 24) * ec.r_m1 + ec.r_add1) >> ec.r_b1);
+            packed[q4] = pack_sat_u8x4(max((t0 >> ec.r_s0) + ec.r_ozp, ec.r_lo), max((t1 >> ec.r_s0) + ec.r_ozp, ec.r_lo),
+                                       max((t2 >> ec.r_s0) + ec.r_ozp, ec.r_lo), max((t3 >> ec.r_s0) + ec.r_ozp, ec.r_lo));
+        } else
         // the pack saturates to 0..255; a ReLU floor above 0 is applied first (FLOOR)
         if (FLOOR)
             packed[q4] = pack_sat_u8x4(max(q0, ec.relu_lo), max(q1, ec.relu_lo), max(q2, ec.relu_lo), max(q3, ec.relu_lo));
@@ -663,7 +684,8 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
         bool store_pending = false;
         uint8_t *s_out = smem + L.out + (size_t)group * out_bytes;
 
-        const EpiConsts ec = { s_mult, s_shift, s_off, s_out, g.ob, g.ob_sh, sw, row, g.qmax, g.relu_lo };
+        const EpiConsts ec = { s_mult, s_shift, s_off, s_out, g.ob, g.ob_sh, sw, row, g.qmax, g.relu_lo,
+                               g.r_m[0], g.r_add[0], g.r_b[0], g.r_m[1], g.r_add[1], g.r_b[1], g.r_s0, g.r_ozp, g.r_lo };
         const bool fast_epi = !g.generic_requant && g.qmax == 255;
         const bool no_floor = g.relu_lo <= 0;
 
@@ -687,6 +709,9 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             const int k0 = nt * g.bn;
             const int ow = ow0 + lw, oh = oh0 + lh, img = n0 + ln;
             const bool pix_valid = ow < g.ow && oh < g.oh && img < g.n;
+            const uint8_t *res_row = g.res;
+            if (g.res != nullptr && pix_valid)
+                res_row += (((size_t)img * g.oh + oh) * g.ow + ow) * g.cout + k0;
             const long long *off_row = g.off + k0;
             if (!single_class)
                 off_row += (size_t)((int)g.row_cls[min(oh, g.oh - 1)] * g.n_col_cls + (int)g.col_cls[min(ow, g.ow - 1)]) * g.kpad;
@@ -727,31 +752,44 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                     if (((c0 >> own_sh) & (wpq - 1)) != sub_warp)
                         continue;
                     uint32_t v[32];
+                    uint32_t rv[8] = { 0, 0, 0, 0, 0, 0, 0, 0 };
                     const int ncol = min(32, g.bn - c0);   // 32, or 16 for the last chunk of bn % 32 == 16
                     if (ncol == 32)
                         tmem_ld32(t_row + c0, v);
                     else
                         tmem_ld16(t_row + c0, v);
+                    if (g.res != nullptr && pix_valid) {
+                        // the residual bytes of this pixel's 32 channels, in flight with the accumulator read
+                        const uint4 *rp = reinterpret_cast<const uint4 *>(res_row + c0);
+                        const uint4 ra = __ldg(rp), rb = __ldg(rp + 1);
+                        rv[0] = ra.x; rv[1] = ra.y; rv[2] = ra.z; rv[3] = ra.w;
+                        rv[4] = rb.x; rv[5] = rb.y; rv[6] = rb.z; rv[7] = rb.w;
+                    }
                     tmem_ld_wait();
                     // the common case is one straight-line block of 32 independent chains
-                    if (fast_epi && ncol == 32) {
+                    if (g.res != nullptr) {          // host guarantees the fast form and whole 32-column chunks
+                        if (single_class)
+                            epi_chunk<true, true, 32, true, true>(v, c0, off_row, ec, rv);
+                        else
+                            epi_chunk<true, false, 32, true, true>(v, c0, off_row, ec, rv);
+                    } else if (fast_epi && ncol == 32) {
                         if (single_class) {
                             if (no_floor)
-                                epi_chunk<true, true, 32, false>(v, c0, off_row, ec);
+                                epi_chunk<true, true, 32, false>(v, c0, off_row, ec, rv);
                             else
-                                epi_chunk<true, true, 32>(v, c0, off_row, ec);
+                                epi_chunk<true, true, 32>(v, c0, off_row, ec, rv);
                         } else {
                             if (no_floor)
-                                epi_chunk<true, false, 32, false>(v, c0, off_row, ec);
+                                epi_chunk<true, false, 32, false>(v, c0, off_row, ec, rv);
                             else
-                                epi_chunk<true, false, 32>(v, c0, off_row, ec);
+                                epi_chunk<true, false, 32>(v, c0, off_row, ec, rv);
                         }
                     } else if (fast_epi) {
-                        epi_chunk<true, false, 16>(v, c0, off_row, ec);
+                        epi_chunk<true, false, 16>(v, c0, off_row, ec, rv);
                     } else if (ncol == 32) {
-                        epi_chunk<false, false, 32>(v, c0, off_row, ec);
+                        epi_chunk<false, false, 32>(v, c0, off_row, ec, rv);
                     } else {
-                        epi_chunk<false, false, 16>(v, c0, off_row, ec);
+                        epi_chunk<false, false, 16>(v, c0, off_row, ec, rv);
                     }
                 }
                 // accumulator stage drained: hand it back to the MMA warp
@@ -869,7 +907,12 @@ struct ConvIgemmPlan {
     uint32_t *mult_dev = nullptr;   // [kpad]
     int32_t *shift_dev = nullptr;   // [kpad]
     uint8_t *row_cls_dev = nullptr, *col_cls_dev = nullptr;
+    // fused residual add (conv_igemm_set_residual)
+    bool has_res = false;
+    int r_m[2] = { 0, 0 }, r_add[2] = { 0, 0 }, r_b[2] = { 1, 1 };
+    int r_s0 = 1, r_ozp = 0, r_lo = 0;
     // tensor maps of the last (x, y, n) seen
+    const uint8_t *last_res = nullptr;
     const uint8_t *last_x = nullptr;
     uint8_t *last_y = nullptr;
     int last_n = -1;
@@ -882,6 +925,7 @@ struct ConvIgemmPlan {
     // a few earlier launch configurations (callers that rotate through a handful of buffers)
     struct Saved {
         const uint8_t *x;
+        const uint8_t *res;
         uint8_t *y;
         int n;
         int *status;
@@ -1147,7 +1191,25 @@ static void choose_tile(int ow, int oh, int n, int *tw, int *th, int *tn, int mi
         }
 }
 
-static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, int *status_word)
+int conv_igemm_set_residual(ConvIgemmPlan *p, const EltwiseArgs &e, int conv_input)
+{
+    // the fused form exists for the straight-line epilogue only: high-word requantize, 8-bit output,
+    // whole 32-channel chunks stored through TMA
+    if (p->generic_requant || p->g.qmax != 255 || p->g.k % 32 != 0 || p->bn % 32 != 0)
+        return fail(B200_ERR_UNSUPPORTED, "conv(igemm): residual add needs the fast requantize form and Cout %% 32 == 0");
+    if (e.n_in != 2 || e.qmax != 255 || conv_input < 0 || conv_input > 1)
+        return fail(B200_ERR_UNSUPPORTED, "conv(igemm): residual add takes a two-input, 8-bit eltwise SUM");
+    const int other = 1 - conv_input;
+    p->r_m[0] = e.m[conv_input]; p->r_add[0] = e.add[conv_input]; p->r_b[0] = e.b[conv_input];
+    p->r_m[1] = e.m[other]; p->r_add[1] = e.add[other]; p->r_b[1] = e.b[other];
+    p->r_s0 = e.s0; p->r_ozp = e.ozp; p->r_lo = e.relu_lo;
+    p->has_res = true;
+    p->last_n = -1;        // cached launch configurations carry the old constants
+    p->saved.clear();
+    return B200_OK;
+}
+
+static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, int *status_word, const uint8_t *res)
 {
     const ConvGeom &g = p->g;
     if ((((uintptr_t)x | (uintptr_t)y) & 15) != 0)
@@ -1185,6 +1247,11 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.generic_requant = p->generic_requant;
     a.use_tma_store = (g.k % 16 == 0) ? 1 : 0;
     a.y = y;
+    a.res = res;
+    for (int i = 0; i < 2; ++i) {
+        a.r_m[i] = p->r_m[i]; a.r_add[i] = p->r_add[i]; a.r_b[i] = p->r_b[i];
+    }
+    a.r_s0 = p->r_s0; a.r_ozp = p->r_ozp; a.r_lo = p->r_lo;
     if (status_word)
         a.status = status_word;       // caller-provided word (the allocation-free entry point)
     else
@@ -1260,30 +1327,38 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
         p->attr_set = true;
     }
     p->last_x = x;
+    p->last_res = res;
     p->last_y = y;
     p->last_n = n;
     p->last_status = status_word;
     return B200_OK;
 }
 
-int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cudaStream_t st, int *status_word)
+int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cudaStream_t st, int *status_word,
+                      const uint8_t *res)
 {
     if (n == 0)
         return B200_OK;
-    if (p->last_x != x || p->last_y != y || p->last_n != n || p->last_status != status_word) {
+    if (res != nullptr && !p->has_res)
+        return fail(B200_ERR_INVALID, "conv(igemm): a residual tensor was given but no residual add is set");
+    if (res == nullptr && p->has_res)
+        return fail(B200_ERR_INVALID, "conv(igemm): this conv was fused with a residual add and needs the residual tensor");
+    if (res != nullptr && (((uintptr_t)res) & 15) != 0)
+        return fail(B200_ERR_INVALID, "conv(igemm): the residual tensor must be 16-byte aligned");
+    if (p->last_x != x || p->last_y != y || p->last_n != n || p->last_status != status_word || p->last_res != res) {
         bool hit = false;
         for (const auto &sv : p->saved)
-            if (sv.x == x && sv.y == y && sv.n == n && sv.status == status_word) {
+            if (sv.x == x && sv.y == y && sv.n == n && sv.status == status_word && sv.res == res) {
                 p->maps = sv.maps;
                 p->args = sv.args;
                 p->grid = sv.grid;
-                p->last_x = x; p->last_y = y; p->last_n = n; p->last_status = status_word;
+                p->last_x = x; p->last_y = y; p->last_n = n; p->last_status = status_word; p->last_res = res;
                 hit = true;
                 break;
             }
         if (!hit) {
-            B200_TRY(build_launch(p, x, n, y, status_word));
-            ConvIgemmPlan::Saved sv = { x, y, n, status_word, p->maps, p->args, p->grid };
+            B200_TRY(build_launch(p, x, n, y, status_word, res));
+            ConvIgemmPlan::Saved sv = { x, res, y, n, status_word, p->maps, p->args, p->grid };
             constexpr size_t kMaxSaved = 8;
             if (p->saved.size() < kMaxSaved) {
                 p->saved.push_back(sv);

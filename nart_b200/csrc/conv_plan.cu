@@ -79,6 +79,7 @@ int b200_conv2d_create(
     g.ow = (p->w + 2 * p->pad_w - p->s) / p->stride_w + 1;
     g.izp = p->izp; g.ozp = p->ozp; g.qmax = (1 << p->obits) - 1;
     g.relu_lo = p->relu ? p->ozp : 0;
+    cv->oalpha = p->oalpha;
     cudaGetDevice(&cv->device);
 
     const int cg = g.c / g.group, taps = g.r * g.s;
@@ -225,6 +226,8 @@ int b200_conv2d_run(b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, 
         return fail(B200_ERR_INVALID, "conv: bad argument");
     if (n == 0)
         return B200_OK;
+    if (conv->fused_residual)
+        return fail(B200_ERR_INVALID, "conv: this plan has a residual add, run it with b200_conv2d_run_residual");
     if (conv->lowered) {
         const ConvGeom &g = conv->g;
         const size_t need = (size_t)n * g.h * g.ow * (kLowerWindow * 4);
@@ -242,6 +245,40 @@ int b200_conv2d_run(b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, 
     if (conv->algo == B200_CONV_ALGO_IGEMM)
         return conv_igemm_launch(conv->igemm, x, n, y, as_stream(stream));
     return conv_direct_launch(conv->g, conv->direct, x, n, y, nullptr, as_stream(stream));
+}
+
+int b200_conv2d_fuse_residual_add(
+    b200_conv_t *conv, int32_t conv_input, const float *ialpha, const uint8_t *izp,
+    const float *coeff, float oalpha, uint8_t ozp, uint8_t obits, int32_t relu)
+{
+    if (!conv || !ialpha || !izp || conv_input < 0 || conv_input > 1)
+        return fail(B200_ERR_INVALID, "conv(fuse): bad argument");
+    if (conv->algo != B200_CONV_ALGO_IGEMM || conv->lowered || !conv->igemm)
+        return fail(B200_ERR_UNSUPPORTED, "conv(fuse): only plans on the tensor-core path take a residual add");
+    if (conv->fused_residual)
+        return fail(B200_ERR_INVALID, "conv(fuse): the plan already has a residual add");
+    if (izp[conv_input] != (uint8_t)conv->g.ozp || ialpha[conv_input] != conv->oalpha)
+        return fail(B200_ERR_UNSUPPORTED, "conv(fuse): the eltwise input's scale / zero point are not the conv's output ones");
+    EltwiseArgs e;
+    bool fast = false;
+    B200_TRY(eltwise_prepare(2, ialpha, izp, coeff, oalpha, ozp, obits, relu, &e, &fast));
+    if (!fast)
+        return fail(B200_ERR_UNSUPPORTED, "conv(fuse): the eltwise rounding term does not fold (or obits != 8)");
+    B200_TRY(conv_igemm_set_residual(conv->igemm, e, conv_input));
+    conv->fused_residual = true;
+    return B200_OK;
+}
+
+int b200_conv2d_run_residual(
+    b200_conv_t *conv, const uint8_t *x, int32_t n, const uint8_t *res, uint8_t *y, b200_stream_t stream)
+{
+    if (!conv || n < 0 || (n > 0 && (!x || !y || !res)))
+        return fail(B200_ERR_INVALID, "conv(residual): bad argument");
+    if (!conv->fused_residual)
+        return fail(B200_ERR_INVALID, "conv(residual): the plan has no residual add (b200_conv2d_fuse_residual_add)");
+    if (n == 0)
+        return B200_OK;
+    return conv_igemm_launch(conv->igemm, x, n, y, as_stream(stream), nullptr, res);
 }
 
 int b200_conv2d_run_acc(

@@ -167,18 +167,6 @@ __global__ void dequantize_flat_kernel(const uint8_t *__restrict__ in, float *__
 // add_i = 2^(b_i-1) - zp_i * m_i is built on the host, one multiply-add and one shift per input.
 // m_i < 2^22, so every intermediate fits int32 for b_i <= 30.
 // ---------------------------------------------------------------------------------------------
-constexpr int kMaxEltIn = 4;
-struct EltwiseArgs {
-    const uint8_t *x[kMaxEltIn];
-    int m[kMaxEltIn];
-    int add[kMaxEltIn];
-    int b[kMaxEltIn];
-    int n_in;
-    int s0;        // final shift (>= 1)
-    int round0;    // 2^(s0-1)
-    int ozp, qmax, relu_lo;
-};
-
 __device__ __forceinline__ int elt_finish(int t, const EltwiseArgs &a)
 {
     int v = ((t + a.round0) >> a.s0) + a.ozp;
@@ -300,6 +288,75 @@ int lut_u8_launch(const uint8_t *x, uint8_t *y, size_t count, const uint8_t *lut
 
 }  // namespace b200
 
+namespace b200 {
+
+// Host side of eltwise SUM: the per-input multipliers, addends and shifts of the kernel's
+// arithmetic (see the comment above EltwiseArgs' kernel) from the reference's scale decomposition.
+// *fast_out: obits == 8 and the final rounding term folded into the first input's addend.
+int eltwise_prepare(
+    int n_in, const float *ialpha, const uint8_t *izp, const float *coeff, float oalpha, uint8_t ozp,
+    uint8_t obits, int relu, EltwiseArgs *out, bool *fast_out)
+{
+    if (n_in > kMaxEltIn)
+        return fail(B200_ERR_UNSUPPORTED, "eltwise: at most %d inputs, got %d", kMaxEltIn, n_in);
+    if (!(oalpha > 0.f))
+        return fail(B200_ERR_INVALID, "eltwise: oalpha must be positive");
+    EltwiseArgs &a = *out;
+    uint32_t m[kMaxEltIn];
+    int8_t s[kMaxEltIn];
+    int s0 = 127;
+    for (int i = 0; i < n_in; ++i) {
+        float scale = (coeff ? coeff[i] : 1.0f) * ialpha[i] / oalpha;
+        if (!(scale > 0.f))
+            return fail(B200_ERR_INVALID, "eltwise: scale of input %d must be positive", i);
+        get_quant_scale(scale, 23, &m[i], &s[i]);
+        if (s[i] < s0)
+            s0 = s[i];
+    }
+    s0 -= 1;  // eltwise.c:150
+    if (s0 < 1 || s0 > 30)
+        return fail(B200_ERR_UNSUPPORTED, "eltwise: final shift %d outside 1..30 (scale ratio too extreme)", s0);
+    for (int i = 0; i < kMaxEltIn; ++i) {
+        a.x[i] = nullptr; a.m[i] = 0; a.add[i] = 0; a.b[i] = 1;
+    }
+    for (int i = 0; i < n_in; ++i) {
+        int b = (int)s[i] - s0;
+        if (b < 1 || b > 30)
+            return fail(B200_ERR_UNSUPPORTED, "eltwise: per-input shift %d outside 1..30", b);
+        a.m[i] = (int)m[i];
+        a.b[i] = b;
+        a.add[i] = (int)((1ll << (b - 1)) - (long long)izp[i] * (long long)m[i]);
+    }
+    {
+        long long worst = 1ll << (s0 - 1);
+        for (int i = 0; i < n_in; ++i)
+            worst += ((255ll * a.m[i]) >> a.b[i]) + 1;
+        if (worst >= (1ll << 31))
+            return fail(B200_ERR_UNSUPPORTED, "eltwise: the int32 sum could overflow");
+    }
+    a.n_in = n_in;
+    a.s0 = s0;
+    a.round0 = 1 << (s0 - 1);
+    a.ozp = ozp;
+    a.qmax = (1 << obits) - 1;
+    a.relu_lo = relu ? ozp : 0;
+    // fold the final rounding term into the first input's addend when that stays inside int32
+    bool fast = a.qmax == 255;
+    {
+        long long folded = (long long)a.add[0] + ((long long)a.round0 << a.b[0]);
+        long long worst = folded < 0 ? -folded : folded;
+        worst += 255ll * a.m[0];
+        if (fast && worst < (1ll << 31))
+            a.add[0] = (int)folded;
+        else
+            fast = false;
+    }
+    *fast_out = fast;
+    return B200_OK;
+}
+
+}  // namespace b200
+
 using namespace b200;
 
 extern "C" {
@@ -392,67 +449,18 @@ int b200_eltwise_sum_u8(
 {
     if (!xs || !ialpha || !izp || !y || n_in < 1 || obits < 1 || obits > 8)
         return fail(B200_ERR_INVALID, "eltwise: bad argument");
-    if (n_in > kMaxEltIn)
-        return fail(B200_ERR_UNSUPPORTED, "eltwise: at most %d inputs, got %d", kMaxEltIn, n_in);
-    if (!(oalpha > 0.f))
-        return fail(B200_ERR_INVALID, "eltwise: oalpha must be positive");
     EltwiseArgs a;
-    uint32_t m[kMaxEltIn];
-    int8_t s[kMaxEltIn];
-    int s0 = 127;
+    bool fast = false;
+    B200_TRY(eltwise_prepare(n_in, ialpha, izp, coeff, oalpha, ozp, obits, relu, &a, &fast));
     for (int i = 0; i < n_in; ++i) {
-        float scale = (coeff ? coeff[i] : 1.0f) * ialpha[i] / oalpha;
-        if (!(scale > 0.f))
-            return fail(B200_ERR_INVALID, "eltwise: scale of input %d must be positive", i);
-        get_quant_scale(scale, 23, &m[i], &s[i]);
-        if (s[i] < s0)
-            s0 = s[i];
         if (((uintptr_t)xs[i] & 15) != 0)
             return fail(B200_ERR_INVALID, "eltwise: input %d is not 16-byte aligned", i);
+        a.x[i] = xs[i];
     }
     if (((uintptr_t)y & 15) != 0)
         return fail(B200_ERR_INVALID, "eltwise: output is not 16-byte aligned");
-    s0 -= 1;  // eltwise.c:150
-    if (s0 < 1 || s0 > 30)
-        return fail(B200_ERR_UNSUPPORTED, "eltwise: final shift %d outside 1..30 (scale ratio too extreme)", s0);
-    for (int i = 0; i < kMaxEltIn; ++i) {
-        a.x[i] = nullptr; a.m[i] = 0; a.add[i] = 0; a.b[i] = 1;
-    }
-    for (int i = 0; i < n_in; ++i) {
-        int b = (int)s[i] - s0;
-        if (b < 1 || b > 30)
-            return fail(B200_ERR_UNSUPPORTED, "eltwise: per-input shift %d outside 1..30", b);
-        a.x[i] = xs[i];
-        a.m[i] = (int)m[i];
-        a.b[i] = b;
-        a.add[i] = (int)((1ll << (b - 1)) - (long long)izp[i] * (long long)m[i]);
-    }
-    {
-        long long worst = 1ll << (s0 - 1);
-        for (int i = 0; i < n_in; ++i)
-            worst += ((255ll * a.m[i]) >> a.b[i]) + 1;
-        if (worst >= (1ll << 31))
-            return fail(B200_ERR_UNSUPPORTED, "eltwise: the int32 sum could overflow");
-    }
-    a.n_in = n_in;
-    a.s0 = s0;
-    a.round0 = 1 << (s0 - 1);
-    a.ozp = ozp;
-    a.qmax = (1 << obits) - 1;
-    a.relu_lo = relu ? ozp : 0;
     if (count == 0)
         return B200_OK;
-    // fold the final rounding term into the first input's addend when that stays inside int32
-    bool fast = a.qmax == 255;
-    {
-        long long folded = (long long)a.add[0] + ((long long)a.round0 << a.b[0]);
-        long long worst = folded < 0 ? -folded : folded;
-        worst += 255ll * a.m[0];
-        if (fast && worst < (1ll << 31))
-            a.add[0] = (int)folded;
-        else
-            fast = false;
-    }
     const size_t want = (count / 32 + 1 + 255) / 256;
     cudaStream_t st = as_stream(stream);
 #define B200_ELT_LAUNCH(...) \

@@ -36,6 +36,25 @@ int relu_build_lut(
     float ialpha, uint8_t izp, float oalpha, uint8_t ozp, uint8_t obits, uint8_t lut[256]);
 int lut_u8_launch(const uint8_t *x, uint8_t *y, size_t count, const uint8_t *lut_dev, cudaStream_t st);
 
+// ---- eltwise SUM ----------------------------------------------------------------------------
+// Arithmetic of eltwise.c:137-174 of the reference in the form the kernels use: per input i
+// term_i = (x_i * m[i] + add[i]) >> b[i] (add[i] = 2^(b[i]-1) - zp_i * m[i]); t = sum term_i;
+// y = sat_u(((t + round0) >> s0) + ozp), floored at relu_lo.
+constexpr int kMaxEltIn = 4;
+struct EltwiseArgs {
+    const uint8_t *x[kMaxEltIn];
+    int m[kMaxEltIn];
+    int add[kMaxEltIn];
+    int b[kMaxEltIn];
+    int n_in;
+    int s0;        // final shift (>= 1)
+    int round0;    // 2^(s0-1)
+    int ozp, qmax, relu_lo;
+};
+int eltwise_prepare(
+    int n_in, const float *ialpha, const uint8_t *izp, const float *coeff, float oalpha, uint8_t ozp,
+    uint8_t obits, int relu, EltwiseArgs *out, bool *fast_out);
+
 // ---- conv -----------------------------------------------------------------------------------
 // Geometry and quantization of one prepared convolution, shared by both kernels.
 struct ConvGeom {
@@ -78,8 +97,13 @@ int conv_igemm_create(
 // stride or padding, and the tensor was written by conv_lower_rows_launch (halves swapped by ow bit 2).
 // status_word: device int that a bounded wait writes its code into; nullptr = the per-device word
 // that b200_device_status reads.
+// res: the second input of a fused residual add (conv_igemm_set_residual), else nullptr.
 int conv_igemm_launch(ConvIgemmPlan *plan, const uint8_t *x, int n, uint8_t *y, cudaStream_t st,
-                      int *status_word = nullptr);
+                      int *status_word = nullptr, const uint8_t *res = nullptr);
+// Fuses y = eltwise_sum(conv(x), res) into the epilogue: `e` holds the eltwise constants and
+// conv_input says which of its two inputs is this conv's output.  B200_ERR_UNSUPPORTED when the
+// plan's epilogue form cannot take it (the caller then keeps the separate eltwise kernel).
+int conv_igemm_set_residual(ConvIgemmPlan *plan, const EltwiseArgs &e, int conv_input);
 void conv_igemm_destroy(ConvIgemmPlan *plan);
 
 }  // namespace b200
@@ -97,4 +121,6 @@ struct b200_conv {
     b200::ConvGeom g_low;
     uint8_t *scratch = nullptr;     // [n][h][ow][32]
     size_t scratch_bytes = 0;
+    float oalpha = 0.f;             // output scale, kept for b200_conv2d_fuse_residual_add
+    bool fused_residual = false;    // the plan computes eltwise_sum(conv(x), res)
 };

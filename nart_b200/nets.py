@@ -193,10 +193,13 @@ def conv_ops_per_image(spec) -> float:
     return total
 
 
-def to_case(spec, max_batch: int, algo: int = ALGO_AUTO, output_f32: bool = True, extra_outputs=()):
-    """Builds and prepares the GPU case.  Returns (case, tensor-id map)."""
+def to_case(spec, max_batch: int, algo: int = ALGO_AUTO, output_f32: bool = True, extra_outputs=(),
+            fuse: bool = False):
+    """Builds and prepares the GPU case.  Returns (case, tensor-id map).  ``fuse`` True folds the
+    residual adds into the convs that feed them (see b200_case_set_fusion)."""
     from .case import Case
     cs = Case()
+    cs.set_fusion(fuse)
     T = spec["tensors"]
     c, h, w = spec["in_chw"]
     ids = {"input": cs.input_u8(c, h, w)}

@@ -81,6 +81,26 @@ class Conv2d:
         check(lib.b200_conv2d_run(self._h, x.data_ptr(), n, y.data_ptr(), _stream()))
         return y
 
+    def fuse_residual_add(self, conv_input, ialpha, izp, oalpha, ozp, obits=8, coeff=None, relu=False):
+        """Folds ``eltwise_sum((conv(x), res)[order], ...)`` into this plan (b200_conv2d_fuse_residual_add);
+        raises B200Error (status ERR_UNSUPPORTED) when the plan cannot take it."""
+        ia = (C.c_float * 2)(*[float(a) for a in ialpha])
+        iz = (C.c_uint8 * 2)(*[int(z) for z in izp])
+        cf = None if coeff is None else (C.c_float * 2)(*[float(v) for v in coeff])
+        check(lib.b200_conv2d_fuse_residual_add(self._h, int(conv_input), ia, iz, cf, float(oalpha), int(ozp),
+                                                int(obits), int(relu)))
+
+    def run_residual(self, x: torch.Tensor, res: torch.Tensor):
+        """y = eltwise_sum(conv(x), res) of a fused plan; res is NHWC with the output's shape."""
+        _dev_u8(x)
+        _dev_u8(res)
+        n = x.shape[0]
+        y = torch.empty((n, self.out_hw[0], self.out_hw[1], self.k), dtype=torch.uint8, device=x.device)
+        if tuple(res.shape) != tuple(y.shape):
+            raise ValueError("residual %s does not match the output %s" % (tuple(res.shape), tuple(y.shape)))
+        check(lib.b200_conv2d_run_residual(self._h, x.data_ptr(), n, res.data_ptr(), y.data_ptr(), _stream()))
+        return y
+
     def close(self):
         if self._h:
             lib.b200_conv2d_destroy(self._h)
