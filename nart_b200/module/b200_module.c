@@ -251,6 +251,7 @@ typedef struct {
     float *ialpha, *walpha, *oalpha;
     uint8_t *izp, *wzp, *ozp;
     uint8_t *ibits, *wbits, *obits;
+    size_t n_walpha;   /* entries of SETTING_QUANT_WALPHA */
 } qsettings_t;
 
 static void get_in_q(op_t *op, qsettings_t *q)
@@ -265,6 +266,7 @@ static void get_w_q(op_t *op, qsettings_t *q)
 {
     size_t len;
     CHECK(op_setting_array_get(op, SETTING_QUANT_WALPHA, dtFLOAT32, &len, &q->walpha));
+    q->n_walpha = len;
     CHECK(op_setting_array_get(op, SETTING_QUANT_WZERO_POINT, dtUINT8, &len, &q->wzp));
     CHECK(op_setting_array_get(op, SETTING_QUANT_WBITS, dtUINT8, &len, &q->wbits));
 }
@@ -380,7 +382,10 @@ void op_b200_conv_2d_tp_prepare(op_t *op)
     p.wzp = c->q.wzp[0];
     p.oalpha = c->q.oalpha[0]; p.ozp = c->q.ozp[0]; p.obits = c->q.obits[0];
     p.walpha = c->q.walpha;
-    p.n_walpha = 1;   /* the reference reads walpha[0] only (conv_2d_uint8_impl.c:61) */
+    /* The reference reads walpha[0] only (conv_2d_uint8_impl.c:61) and its exporter writes one entry
+     * per weight tensor.  An array with one entry per output channel is taken as per-channel scales
+     * (an extension; no file the reference writes has one). */
+    p.n_walpha = (c->q.n_walpha == (size_t)c->num_output && c->num_output > 1) ? (int32_t)c->num_output : 1;
     p.relu = c->relu_flag ? 1 : 0;
     p.algo = B200_CONV_ALGO_AUTO;
     const uint8_t *wt = (const uint8_t *)mem_cpu_data(op->input_tensors[1]->mem);
@@ -461,7 +466,8 @@ void op_b200_ip_tp_prepare(op_t *op)
     const uint8_t *wt = (const uint8_t *)mem_cpu_data(op->input_tensors[1]->mem);
     const int32_t *bias = op->input_size == 3 ? (const int32_t *)mem_cpu_data(op->input_tensors[2]->mem) : NULL;
     B200_CALL(b200_ip_create(
-        ch, h, w, (int32_t)c->num_output, c->q.ialpha[0], c->q.izp[0], c->q.walpha, 1, c->q.wzp[0],
+        ch, h, w, (int32_t)c->num_output, c->q.ialpha[0], c->q.izp[0], c->q.walpha,
+        (c->q.n_walpha == (size_t)c->num_output && c->num_output > 1) ? (int32_t)c->num_output : 1, c->q.wzp[0],
         c->q.oalpha[0], c->q.ozp[0], c->q.obits[0], wt, bias, &c->plan));
     c->plan_c = ch; c->plan_h = h; c->plan_w = w;
     op->run_func = op_b200_ip_run;

@@ -214,6 +214,43 @@ class Ref(_Common):
         self.lib.ref_use_module.restype = None
         self.lib.ref_use_module(ptr, int(whole_batch), int(conv_relu))
 
+    def constant(self, name: str):
+        """Value of a named constant of the reference's headers (None if the shim does not list it)."""
+        found = C.c_int(0)
+        self.lib.ref_constant.restype = C.c_uint64
+        self.lib.ref_constant.argtypes = [C.c_char_p, C.POINTER(C.c_int)]
+        v = self.lib.ref_constant(name.encode(), C.byref(found))
+        return int(v) if found.value else None
+
+    def run_engine(self, path, inputs, output_dtypes):
+        """Loads a serialized case with the reference's own deserializer and parade, bound to the
+        module selected by use_module, and runs it once.  inputs: numpy arrays in the file's input
+        order and shapes; returns one flat numpy array per output."""
+        L = self.lib
+        L.ref_parade_open.restype = C.c_void_p
+        L.ref_parade_open.argtypes = [C.c_char_p]
+        L.ref_parade_io_bytes.restype = C.c_size_t
+        L.ref_parade_io_bytes.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.ref_parade_run.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]
+        L.ref_parade_close.argtypes = [C.c_void_p]
+        h = L.ref_parade_open(os.fsencode(path))
+        if not h:
+            raise RuntimeError("the reference could not load %s" % path)
+        try:
+            ins = [np.ascontiguousarray(a) for a in inputs]
+            for i, a in enumerate(ins):
+                want = L.ref_parade_io_bytes(h, 0, i)
+                if a.nbytes != want:
+                    raise ValueError("input %d has %d bytes, the case expects %d" % (i, a.nbytes, want))
+            outs = [np.empty(L.ref_parade_io_bytes(h, 1, i) // np.dtype(dt).itemsize, dtype=dt)
+                    for i, dt in enumerate(output_dtypes)]
+            ip = (C.c_void_p * len(ins))(*[a.ctypes.data for a in ins])
+            op = (C.c_void_p * len(outs))(*[o.ctypes.data for o in outs])
+            assert L.ref_parade_run(h, ip, op) == 0
+            return outs
+        finally:
+            L.ref_parade_close(h)
+
     def conv2d_u8(self, x, w, bias, stride, pad, group, ialpha, izp, walpha, wzp, oalpha, ozp,
                   obits=8):
         x, w = _u8(x), _u8(w)

@@ -365,3 +365,122 @@ REF_API int ref_dequantize_u8(const uint8_t *x, size_t count, float ialpha, uint
     tensor_delete(tx);
     return 0;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * A serialized case (engine.bin, format v2: art/src/serialize_v2.c:26-103) through the
+ * reference's own loader and parade, the way its drivers do it (tools/promark.cpp:58-72):
+ * deserialize_parade with the current module's workspace, parade_prepare, then per run copy the
+ * inputs in, parade_run, copy the outputs out (art/src/parade.c:184-197).
+ * With the reference `quant` module the conv scratch of every conv op is cleared once after
+ * prepare, and the batch must be 1 (see the constraints at the top of this file).
+ * ------------------------------------------------------------------------------------------ */
+#include <stdio.h>
+
+#include "art/parade.h"
+#include "art/serialize.h"
+#include "src/parade_impl.h"   /* art/src: the parade struct, for the op list */
+
+static size_t read_file_chunk(size_t sz, void *data, void *param)
+{
+    return fread(data, 1, sz, (FILE *)param);
+}
+
+REF_API parade_t *ref_parade_open(const char *path)
+{
+    FILE *fp = fopen(path, "rb");
+    buffer_t *buf;
+    parade_t *parade;
+    workspace_t *wss[2];
+    deserialize_param_t params;
+    size_t i;
+    if (!fp)
+        return NULL;
+    buf = nart_buffer_new(0x8000);
+    buffer_set_buffer_read_func(buf, read_file_chunk, (void *)fp);
+    wss[0] = ws();
+    wss[1] = NULL;
+    params.workspaces = wss;
+    params.input_mem_tp = workspace_memtype(ws());
+    parade = deserialize_parade(buf, &params);
+    nart_buffer_delete(buf);
+    fclose(fp);
+    if (!parade)
+        return NULL;
+    parade_prepare(parade);
+    if (g_module == &quant_module_tp) {
+        for (i = 0; i < parade->op_count; ++i) {
+            op_t *op = parade->ops[i];
+            if (op->entry->tp->op_tp_code == OP_CONV_2D) {
+                op_conv_2d_t *conv_op = (op_conv_2d_t *)op;
+                if (conv_op->temp_data)
+                    memset(mem_cpu_data(conv_op->temp_data), 0, mem_sizeof(conv_op->temp_data));
+            }
+        }
+    }
+    return parade;
+}
+
+/* Byte size of input / output `index` of the loaded case (whole batch). */
+REF_API size_t ref_parade_io_bytes(parade_t *parade, int is_output, int index)
+{
+    size_t count = 0;
+    tensor_array_t arr = NULL;
+    if (is_output)
+        parade_get_output_tensors(parade, &count, &arr);
+    else
+        parade_get_input_tensors(parade, &count, &arr);
+    if (index < 0 || (size_t)index >= count)
+        return 0;
+    return shape_count(&arr[index]->shape) * datatype_sizeof(arr[index]->dtype);
+}
+
+/* One run: inputs[i] / outputs[i] are host arrays of ref_parade_io_bytes bytes. */
+REF_API int ref_parade_run(parade_t *parade, const void *const *inputs, void *const *outputs)
+{
+    size_t n_in = 0, n_out = 0, i;
+    tensor_array_t in = NULL, out = NULL;
+    parade_get_input_tensors(parade, &n_in, &in);
+    parade_get_output_tensors(parade, &n_out, &out);
+    for (i = 0; i < n_in; ++i)
+        memcpy(mem_cpu_data(in[i]->mem), inputs[i], shape_count(&in[i]->shape) * datatype_sizeof(in[i]->dtype));
+    parade_run(parade);
+    for (i = 0; i < n_out; ++i)
+        memcpy(outputs[i], mem_cpu_data(out[i]->mem), shape_count(&out[i]->shape) * datatype_sizeof(out[i]->dtype));
+    return 0;
+}
+
+REF_API void ref_parade_close(parade_t *parade)
+{
+    if (parade)
+        parade_delete(parade);
+}
+
+/* Numeric value of a named constant of the reference's headers, for pinning the tables of the
+ * engine writer; returns 0 and sets *found = 0 for an unknown name. */
+REF_API uint64_t ref_constant(const char *name, int *found)
+{
+#define REF_CONST(x)             \
+    if (strcmp(name, #x) == 0) { \
+        *found = 1;              \
+        return (uint64_t)(x);    \
+    }
+    REF_CONST(OP_CONV_2D) REF_CONST(OP_IP) REF_CONST(OP_ELTWISE) REF_CONST(OP_ADD) REF_CONST(OP_RELU)
+    REF_CONST(OP_POOL) REF_CONST(OP_QUANT_QUANTIZE) REF_CONST(OP_QUANT_DEQUANTIZE)
+    REF_CONST(SETTING_CONV_2D_RELU_FLAG) REF_CONST(SETTING_CONV_2D_NUM_OUTPUT) REF_CONST(SETTING_CONV_2D_KERNEL_H)
+    REF_CONST(SETTING_CONV_2D_KERNEL_W) REF_CONST(SETTING_CONV_2D_PAD_H) REF_CONST(SETTING_CONV_2D_PAD_W)
+    REF_CONST(SETTING_CONV_2D_STRIDE_H) REF_CONST(SETTING_CONV_2D_STRIDE_W) REF_CONST(SETTING_CONV_2D_GROUP)
+    REF_CONST(SETTING_IP_NUM_OUTPUT) REF_CONST(SETTING_ELTWISE_OPERATION) REF_CONST(SETTING_ELTWISE_OP_SUM)
+    REF_CONST(SETTING_ELTWISE_COEFF) REF_CONST(SETTING_POOL_METHOD) REF_CONST(SETTING_POOL_KERNEL_H)
+    REF_CONST(SETTING_POOL_KERNEL_W) REF_CONST(SETTING_POOL_PAD_H) REF_CONST(SETTING_POOL_PAD_W)
+    REF_CONST(SETTING_POOL_STRIDE_H) REF_CONST(SETTING_POOL_STRIDE_W) REF_CONST(SETTING_POOL_CEIL_MODE)
+    REF_CONST(SETTING_POOL_MAX) REF_CONST(SETTING_POOL_AVE)
+    REF_CONST(SETTING_QUANT_IALPHA) REF_CONST(SETTING_QUANT_IZERO_POINT) REF_CONST(SETTING_QUANT_IBITS)
+    REF_CONST(SETTING_QUANT_OALPHA) REF_CONST(SETTING_QUANT_OZERO_POINT) REF_CONST(SETTING_QUANT_OBITS)
+    REF_CONST(SETTING_QUANT_WALPHA) REF_CONST(SETTING_QUANT_WZERO_POINT) REF_CONST(SETTING_QUANT_WBITS)
+    REF_CONST(SETTING_QUANT_QTYPE) REF_CONST(SETTING_QUANT_BIASED)
+    REF_CONST(dtUINT8) REF_CONST(dtINT8) REF_CONST(dtUINT32) REF_CONST(dtINT32) REF_CONST(dtFLOAT32)
+    REF_CONST(dtBOOL) REF_CONST(dtSTR)
+#undef REF_CONST
+    *found = 0;
+    return 0;
+}

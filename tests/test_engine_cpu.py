@@ -1,0 +1,45 @@
+"""The engine.bin writer and reader (nart_b200/engine.py) against the reference's own loader:
+a written case must load with deserialize_parade (art/src/serialize_v2.c) and, run by the reference's
+parade on its CPU `quant` module, give what the op-by-op walk of the same network gives."""
+import os
+
+import numpy as np
+import pytest
+
+from nart_b200 import engine, nets
+
+
+def test_constants_match_the_reference_headers(ref):
+    for name, value in engine.CONSTANTS.items():
+        assert ref.constant(name) == value, name
+
+
+def test_write_read_round_trip(tmp_path):
+    spec = nets.resnet(18, seed=21, hw=32, width_div=8, spread=True, num_classes=10)
+    path = os.path.join(tmp_path, "engine.bin")
+    engine.write_engine(spec, path, batch=3, per_channel=True)
+    m = engine.read_engine(path)
+    assert [i["dims"] for i in m["inputs"]] == [[3, 3, 32, 32]]
+    convs = [op for op in spec["ops"] if op["op"] in ("conv", "ip")]
+    assert len(m["weights"]) == 2 * len(convs)
+    n_relu_ops = sum(1 for op in spec["ops"] if op["op"] == "eltwise" and op["relu"])
+    assert len(m["ops"]) == len(spec["ops"]) + n_relu_ops + 1        # + the final dequantize
+    first = m["ops"][0]
+    assert first["code"] == (6 << 32) | engine.OP_CONV_2D and first["ins"][0] == 0
+    w0 = m["weights"][first["ins"][1]]["data"]
+    np.testing.assert_array_equal(w0, convs[0]["w"])
+    np.testing.assert_array_equal(first["settings"][engine.Q_WALPHA], convs[0]["walpha"].astype(np.float32))
+    assert m["outputs"][0]["name"] == "logits"
+
+
+def test_written_case_runs_on_the_reference_parade(ref, tmp_path):
+    """Batch 1 (the reference conv cannot take more), one weight scale per layer, activations as
+    relu ops of their own: the file's result equals the op-by-op walk through the same module."""
+    spec = nets.resnet(18, seed=22, hw=96, width_div=4, spread=True, num_classes=12)
+    path = os.path.join(tmp_path, "engine.bin")
+    engine.write_engine(spec, path, batch=1, per_channel=False, conv_relu_flag=False)
+    x = np.random.default_rng(3).integers(0, 256, (1, 3, 96, 96), dtype=np.uint8)
+    ref.use_module()
+    (got,) = ref.run_engine(path, [x], [np.float32])
+    want, _, _ = nets.run_cpu(spec, x, ref, per_channel=False)
+    np.testing.assert_array_equal(got.view(np.uint32), want.reshape(-1).view(np.uint32))

@@ -1,0 +1,46 @@
+"""GPU: serialized cases (engine.bin).  (1) A file read by nart_b200.engine runs on the GPU case
+runner.  (2) The same file, untouched, loaded by the reference's own deserializer and parade with
+the b200 plugin as the only workspace -- the drop-in: what `promark -m engine.bin` does when the
+runtime JSON lists "b200" (tools/promark.cpp:58-72,122-187).  Both give the CPU restatement's bits."""
+import os
+
+import numpy as np
+import pytest
+
+from gpu_util import assert_same
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PLUGIN = os.path.join(ROOT, "nart_b200", "libart_module_b200.so")
+
+
+@pytest.mark.parametrize("depth,relu_flag", [(18, True), (50, True), (18, False)])
+def test_engine_file_on_the_case_runner(port, tmp_path, depth, relu_flag):
+    from nart_b200 import engine, nets
+    spec = nets.resnet(depth, seed=30 + depth, hw=64, width_div=2, spread=True, num_classes=40)
+    path = os.path.join(tmp_path, "engine.bin")
+    engine.write_engine(spec, path, batch=3, per_channel=True, conv_relu_flag=relu_flag)
+    x = np.random.default_rng(depth).integers(0, 256, (3, 3, 64, 64), dtype=np.uint8)
+    want, _, _ = nets.run_cpu(spec, x, port)
+    cs, outs = engine.engine_to_case(engine.read_engine(path), 4)
+    assert outs == [(True, (40, 1, 1))]
+    (got,) = cs.run_host([x], [(np.float32, (40, 1, 1))])
+    cs.close()
+    assert_same(got.reshape(want.shape).view(np.uint32), want.view(np.uint32), "engine.bin on the case runner")
+
+
+def test_engine_file_through_the_reference_parade_on_the_plugin(ref, port, tmp_path):
+    if not os.path.exists(PLUGIN):
+        pytest.skip("libart_module_b200.so was not built (the art headers were not available)")
+    from nart_b200 import engine, nets
+    spec = nets.resnet(50, seed=41, hw=64, width_div=2, spread=True, num_classes=24)
+    path = os.path.join(tmp_path, "engine.bin")
+    engine.write_engine(spec, path, batch=2, per_channel=True, conv_relu_flag=True)
+    x = np.random.default_rng(8).integers(0, 256, (2, 3, 64, 64), dtype=np.uint8)
+    want, _, _ = nets.run_cpu(spec, x, port)
+    ref.use_module(PLUGIN, "b200_module_tp", whole_batch=True)
+    try:
+        (got,) = ref.run_engine(path, [x], [np.float32])
+    finally:
+        ref.use_module()
+    assert_same(got.reshape(want.shape).view(np.uint32), want.view(np.uint32), "engine.bin through parade + plugin")
