@@ -1,0 +1,97 @@
+"""Times a serialized case on the GPU case runner, with the options and the report of the
+reference's benchmark driver (tools/promark.cpp:208-522 of ModelTC/NART):
+
+    python -m nart_b200.promark -m engine.bin [-n runs] [-b batch] [-i input.bin ...] [-s] [-d] [-y]
+
+  -m  the case file (format version 2)
+  -n  timed runs (default 10), after one warm-up run
+  -b  batch size (default: the batch recorded in the file)
+  -i  raw input file in the input's dtype and NCHW shape, one per model input
+  -s  save the outputs as nart-out-<name>.bin (raw, NCHW)
+  -d  fresh random input data before every run
+  -y  include the host<->device copies in the timed region (otherwise the device-resident run)
+  --fuse  fold residual adds into the convs that feed them
+
+promark's `-c` (runtime JSON choosing the modules) has no meaning here: this driver always runs the
+b200 case runner.  To run the same file through the reference's own parade, list "b200" in the
+runtime JSON of the reference's promark.
+"""
+from __future__ import annotations
+
+import argparse
+import sys
+import time
+
+import numpy as np
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="python -m nart_b200.promark", add_help=True)
+    ap.add_argument("-m", dest="model", required=True)
+    ap.add_argument("-n", dest="runs", type=int, default=10)
+    ap.add_argument("-b", dest="batch", type=int, default=-1)
+    ap.add_argument("-i", dest="inputs", action="append", default=[])
+    ap.add_argument("-s", dest="save", action="store_true")
+    ap.add_argument("-d", dest="random", action="store_true")
+    ap.add_argument("-y", dest="copies", action="store_true")
+    ap.add_argument("--fuse", action="store_true")
+    a = ap.parse_args(argv)
+
+    import torch
+    from . import engine
+    print("parse args ...")
+    model = engine.read_engine(a.model)
+    inp = model["inputs"][0]
+    batch = a.batch if a.batch > 0 else int(inp["dims"][0])
+    cs, outs = engine.engine_to_case(model, batch, fuse=a.fuse)
+    in_dtype = np.float32 if inp["dtype"] == engine.DT_FLOAT32 else np.uint8
+    in_shape = (batch,) + tuple(inp["dims"][1:])
+    print("input tensors:")
+    print("\t%s: %s" % (inp["name"], ", ".join(str(d) for d in in_shape)))
+    print("output tensors:")
+    for o, (is_f32, chw) in zip(model["outputs"], outs):
+        print("\t%s: %s" % (o["name"], ", ".join(str(d) for d in (batch,) + tuple(chw))))
+
+    rng = np.random.default_rng(0)
+
+    def random_input():
+        if in_dtype == np.uint8:
+            return rng.integers(0, 256, in_shape, dtype=np.uint8)
+        return rng.standard_normal(in_shape).astype(np.float32)
+
+    x = random_input()
+    if a.inputs:
+        x = np.fromfile(a.inputs[0], dtype=in_dtype).reshape(in_shape)
+    out_spec = [(np.float32 if is_f32 else np.uint8, chw) for is_f32, chw in outs]
+    stream = torch.cuda.Stream()
+    result = cs.run_host([x], out_spec, stream.cuda_stream)          # warm-up; also fills the device input
+    print("\nFinish warm up")
+    total = 0.0
+    for i in range(a.runs):
+        if a.random:
+            print("use randomized data.")
+            x = random_input()
+            if not a.copies:
+                cs.run_host([x], out_spec, stream.cuda_stream)
+        t0 = time.perf_counter()
+        if a.copies:
+            result = cs.run_host([x], out_spec, stream.cuda_stream)
+        else:
+            cs.run_device(batch, stream.cuda_stream)
+            stream.synchronize()
+        ms = (time.perf_counter() - t0) * 1e3
+        total += ms
+        print("Process %d : cost %gms" % (i, ms))
+    print("\nTest finised, average cost: %gms\n" % (total / max(1, a.runs)))
+    print("%.1f images/s at batch %d" % (batch * a.runs / (total / 1e3), batch))
+    if a.save:
+        result = cs.run_host([x], out_spec, stream.cuda_stream)
+        print("Info: Saving output tensors ...", file=sys.stderr)
+        for o, arr in zip(model["outputs"], result):
+            arr.tofile("nart-out-%s.bin" % o["name"].replace("/", "_"))
+    cs.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

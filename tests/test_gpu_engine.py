@@ -44,3 +44,22 @@ def test_engine_file_through_the_reference_parade_on_the_plugin(ref, port, tmp_p
     finally:
         ref.use_module()
     assert_same(got.reshape(want.shape).view(np.uint32), want.view(np.uint32), "engine.bin through parade + plugin")
+
+
+def test_promark_cli(port, tmp_path, monkeypatch, capsys):
+    """python -m nart_b200.promark: the reference benchmark driver's options on the case runner;
+    -i / -s read and write raw NCHW files."""
+    from nart_b200 import engine, nets, promark
+    spec = nets.resnet(18, seed=51, hw=64, width_div=4, spread=True, num_classes=10)
+    path = os.path.join(tmp_path, "engine.bin")
+    engine.write_engine(spec, path, batch=2)
+    x = np.random.default_rng(4).integers(0, 256, (2, 3, 64, 64), dtype=np.uint8)
+    x.tofile(os.path.join(tmp_path, "in.bin"))
+    monkeypatch.chdir(tmp_path)
+    assert promark.main(["-m", path, "-n", "2", "-y", "-s", "-i", "in.bin"]) == 0
+    text = capsys.readouterr().out
+    assert "input tensors:" in text and "Process 1 : cost" in text and "average cost" in text
+    got = np.fromfile(os.path.join(tmp_path, "nart-out-logits.bin"), dtype=np.float32)
+    want, _, _ = nets.run_cpu(spec, x, port)
+    assert_same(got.view(np.uint32), want.reshape(-1).view(np.uint32), "promark -s")
+    assert promark.main(["-m", path, "-n", "2", "-b", "4", "-d"]) == 0      # device-resident timing, other batch
