@@ -33,6 +33,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 BATCH = 256
+# DRAM bytes per launch of the conv kernel, averaged over the 54 launches of one batch-256 step:
+# dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this script (3.850 GB per step)
+IGEMM_DRAM_BYTES_PER_LAUNCH = 3.850e9 / 54
 WORKLOAD = "BASELINE configs[3]: ResNet-50 v1.5 int8, batch 256 per GPU, 3x224x224 uint8 input"
 SEED = 3
 
@@ -364,7 +367,11 @@ def run_gpu_arm(a):
                         conv_tops=igemm_ops / sec / 1e12, ms_per_step_by_kernel=breakdown,
                         conv_gop_per_image=nets.conv_ops_per_image(spec) / 1e9, logits_checksum=logits_checksum),
             roofline=dict(bound="hbm", achieved=hbm_ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=hbm_ach / peaks["hbm_gbs"],
-                          traffic=None, kernel="conv_igemm_i8_kernel", launches_per_step=igemm_launches // a.steps,
+                          traffic=IGEMM_DRAM_BYTES_PER_LAUNCH if batch == BATCH else None,
+                          traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum over the 54 launches of one "
+                                         "step at batch 256, average per launch (profiles/resnet50_b256_igemm_dram_traffic.md)",
+                          algorithmic_bytes_per_launch=igemm_bytes / max(1, igemm_launches),
+                          kernel="conv_igemm_i8_kernel", launches_per_step=igemm_launches // a.steps,
                           peak_source=peaks["src"]),
             roofline_tensor=dict(bound="tensor", achieved=tops_ach, peak=int8_peak / 1.0, unit="TOP/s",
                                  frac=tops_ach / int8_peak,
