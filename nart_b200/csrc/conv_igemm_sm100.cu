@@ -68,7 +68,7 @@ struct IgemmArgs {
     // problem
     int n, oh, ow, cout;
     int r, s, pad_h, pad_w, stride_h, stride_w;
-    int c;               // input channels
+    int c;               // input channels, rounded up to a multiple of 32 (the k-blocks' extent)
     // tiling
     int tw, th, tn;      // M-tile box (ow, oh, image), tw*th*tn == 128, each a power of two
     int tw_sh, th_sh;    // log2(tw), log2(th)
@@ -899,6 +899,7 @@ int encode(CUtensorMap *m, void *base, int rank, const cuuint64_t *dims, const c
 struct ConvIgemmPlan {
     ConvGeom g;
     int groups = 2, acc_stages = 2;
+    int cpad = 0;                   // input channels rounded up to a multiple of 32
     int bk = 0, bn = 0, stages = 0, kgroup = 1, ob = 0, kpad = 0, b_resident = 0, a_wide = 0;
     int n_row_cls = 0, n_col_cls = 0;
     int generic_requant = 0;
@@ -941,11 +942,11 @@ int conv_igemm_supported(const ConvGeom &g, char *why, size_t why_len)
 {
     const char *msg = nullptr;
     if (g.group != 1) msg = "group != 1";
-    else if (g.c % 32 != 0) msg = "input channels not a multiple of 32";
+    else if (g.c % 16 != 0) msg = "input channels not a multiple of 16";   // the pixel stride of a TMA map
     else if (g.k < 16) msg = "fewer than 16 output channels";
     else if (g.stride_h > 2 || g.stride_w > 2) msg = "stride > 2";
     else if (g.h < g.stride_h || g.w < g.stride_w) msg = "input smaller than the stride";
-    else if ((long long)g.r * g.s * (g.c / 32) >= 32768) msg = "more than 32767 k-blocks per tile";
+    else if ((long long)g.r * g.s * ((g.c + 31) / 32) >= 32768) msg = "more than 32767 k-blocks per tile";
     if (msg) {
         snprintf(why, why_len, "%s", msg);
         return 0;
@@ -1004,7 +1005,11 @@ int conv_igemm_create(
     ConvIgemmPlan *p = new ConvIgemmPlan();
     p->g = g;
     p->a_wide = a_row_swizzled ? 1 : 0;
-    p->bk = g.c % 128 == 0 ? 128 : (g.c % 64 == 0 ? 64 : 32);
+    // K of an 8-bit MMA is 32 bytes: the channel count is rounded up to a multiple of 32 in the
+    // repacked weights (zero weights); on the activation side the TMA box runs past the tensor's
+    // channel extent and reads zeros there
+    p->cpad = (g.c + 31) / 32 * 32;
+    p->bk = p->cpad % 128 == 0 ? 128 : (p->cpad % 64 == 0 ? 64 : 32);
     // output-channel tile: a multiple of 16 up to 256 that wastes little of Cout
     {
         const int k16 = (g.k + 15) / 16 * 16;
@@ -1032,7 +1037,7 @@ int conv_igemm_create(
     p->kpad = n_tiles_n * p->bn;
     // pipeline depth from the shared memory left after the staging buffer
     {
-        const int kblocks = g.r * g.s * (g.c / p->bk);
+        const int kblocks = g.r * g.s * (p->cpad / p->bk);
         // weights resident when there is one channel tile and they leave room for >= 3 A stages
         // four epilogue groups (four tiles in flight behind the mainloop) when the tiles are narrow:
         // their per-tile latency chain, not their arithmetic, sets the epilogue rate
@@ -1088,18 +1093,18 @@ int conv_igemm_create(
         p->stages = stages;
         p->kgroup = kgroup;
     }
-    if (smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024 > 227 * 1024) {
+    if (smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (p->cpad / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024 > 227 * 1024) {
         delete p;
         return fail(B200_ERR_UNSUPPORTED, "conv(igemm): tile does not fit shared memory");
     }
 
     const int taps = g.r * g.s;
     // ---- weights [kpad][r][s][c] ---------------------------------------------------------------
-    std::vector<int8_t> wp((size_t)p->kpad * taps * g.c, 0);
+    std::vector<int8_t> wp((size_t)p->kpad * taps * p->cpad, 0);
     for (int k = 0; k < g.k; ++k)
         for (int c = 0; c < g.c; ++c)
             for (int t = 0; t < taps; ++t)
-                wp[((size_t)k * taps + t) * g.c + c] = w_s8[((size_t)k * g.c + c) * taps + t];
+                wp[((size_t)k * taps + t) * p->cpad + c] = w_s8[((size_t)k * g.c + c) * taps + t];
     // ---- border classes and offsets ---------------------------------------------------------------
     std::vector<uint8_t> row_cls, col_cls;
     std::vector<std::vector<char>> row_valid, col_valid;
@@ -1218,7 +1223,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     memset(&a, 0, sizeof(a));
     a.n = n; a.oh = g.oh; a.ow = g.ow; a.cout = g.k;
     a.r = g.r; a.s = g.s; a.pad_h = g.pad_h; a.pad_w = g.pad_w; a.stride_h = g.stride_h; a.stride_w = g.stride_w;
-    a.c = g.c;
+    a.c = p->cpad;
     if (p->a_wide)   // whole swizzle atoms (8 pixels) per row segment, at most 256 8-byte elements
         choose_tile(g.ow, g.oh, n, &a.tw, &a.th, &a.tn, 3, 6);
     else
@@ -1228,7 +1233,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.tiles_n = (n + a.tn - 1) / a.tn;
     a.n_tiles_n = p->kpad / p->bn;
     a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.kgroup = p->kgroup; a.groups = p->groups; a.acc_stages = p->acc_stages;
-    a.rcp_cchunks = (uint32_t)(((1ull << 30) + (uint64_t)(g.c / p->bk) - 1) / (uint64_t)(g.c / p->bk));
+    a.rcp_cchunks = (uint32_t)(((1ull << 30) + (uint64_t)(p->cpad / p->bk) - 1) / (uint64_t)(p->cpad / p->bk));
     a.rcp_s = (uint32_t)(((1ull << 30) + (uint64_t)g.s - 1) / (uint64_t)g.s); a.ob = p->ob; a.b_resident = p->b_resident; a.a_wide = p->a_wide;
     for (a.tw_sh = 0; (1 << a.tw_sh) < a.tw; ++a.tw_sh) {}
     for (a.th_sh = 0; (1 << a.th_sh) < a.th; ++a.th_sh) {}
@@ -1291,7 +1296,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
             p->maps.a[i] = p->maps.a[0];
     }
     {
-        const int ktot = g.r * g.s * g.c;
+        const int ktot = g.r * g.s * p->cpad;
         cuuint64_t dims[2] = { (cuuint64_t)ktot, (cuuint64_t)p->kpad };
         cuuint64_t strides[1] = { (cuuint64_t)ktot };
         cuuint32_t box[2] = { (cuuint32_t)p->bk, (cuuint32_t)p->bn };
@@ -1321,7 +1326,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
         a.step_h = gsz % a.tiles_h;
         a.step_n = gsz / a.tiles_h;
     }
-    p->smem = smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (g.c / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024;
+    p->smem = smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (p->cpad / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024;
     if (!p->attr_set) {
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         p->attr_set = true;

@@ -24,7 +24,7 @@ def algos_for(ops, c, k, group):
     a = [ops.ALGO_DIRECT]
     if os.environ.get("B200_TEST_ALGOS") == "direct":   # debugging aid: CUDA-core path only
         return a
-    if group == 1 and c % 32 == 0 and k % 16 == 0:
+    if group == 1 and c % 16 == 0 and k % 16 == 0:
         a.append(ops.ALGO_IGEMM)
     return a
 
@@ -246,3 +246,17 @@ def test_conv_requantize_variants_on_both_paths(ops, port, k):
             for algo in (ops.ALGO_DIRECT, ops.ALGO_IGEMM):
                 got = run_conv(ops, x, wt, bias, 1, 1, 1, algo, walpha=walpha, relu=relu, **q)
                 assert_same(got, want, "k=%d oalpha=%g obits=%d relu=%s algo=%d" % (k, oalpha, obits, relu, algo))
+
+
+@pytest.mark.parametrize("c,k,ks,st,hw", [(16, 96, 1, 1, 14), (48, 32, 3, 1, 9), (80, 48, 3, 2, 12), (144, 24, 1, 1, 7),
+                                          (16, 16, 3, 1, 8), (208, 64, 1, 2, 10), (96, 576, 1, 1, 6)])
+def test_conv_channels_not_multiple_of_32_on_tensor_cores(ops, port, c, k, ks, st, hw):
+    """Input channel counts that are multiples of 16 but not of 32 (MobileNetV2's 16, 96, 144, 576 ...):
+    the tensor-core path pads the repacked weights to 32 and lets TMA zero-fill the activations."""
+    n, pd = 3, ks // 2
+    x, wt, bias, walpha = conv_inputs(900 + c + k, n, c, hw, hw, k, ks, ks, 1)
+    q = dict(ialpha=0.029, izp=101, wzp=128, oalpha=0.05 * np.sqrt(c * ks * ks) / 4, ozp=33, walpha=walpha)
+    want = port.conv2d_u8(x, wt, bias, (st, st), (pd, pd), 1, q["ialpha"], q["izp"], walpha, 128, q["oalpha"], q["ozp"],
+                          relu=True)
+    got = run_conv(ops, x, wt, bias, st, pd, 1, ops.ALGO_IGEMM, relu=True, **q)
+    assert_same(got, want, "c=%d k=%d %dx%d s%d" % (c, k, ks, ks, st))
