@@ -246,23 +246,53 @@ int b200_case_conv2d(
     op.kind = OpKind::Conv;
     op.ins = { in };
     b200_conv_params p = *params;
+    // Channel padding.  A tensor whose channel count is not a multiple of 16 lives in a device buffer
+    // with the count rounded up (c_phys), so that every conv around it can take the tensor-core path
+    // (MobileNetV2's 24-channel tensors).  Padding input channels get zero weights (stored as wzp),
+    // padding output channels zero weights and a zero bias: they add nothing to any result and
+    // their own values are never read with a non-zero weight.
+    const size_t taps = (size_t)p.r * p.s;
+    const bool depthwise = p.group > 1 && p.group == params->c && p.k == params->c;
+    if (ti.c_phys != ti.c && p.group != 1 && !depthwise)
+        return fail(B200_ERR_UNSUPPORTED, "case_conv2d: grouped conv on a channel-padded input");
+    const int c_in = ti.c_phys;
+    int k_phys = p.k;
+    if (depthwise)
+        k_phys = ti.c_phys;
+    else if (p.group == 1 && p.k % 16 != 0 && p.k >= 8)
+        k_phys = (p.k + 15) / 16 * 16;
     std::vector<uint8_t> wpad;
+    std::vector<int32_t> bpad;
+    std::vector<float> wapad;
     const uint8_t *wsrc = weights;
-    if (ti.c_phys != ti.c) {
-        // the device buffer carries padding channels: give them zero weights (stored 128)
-        if (p.group != 1)
-            return fail(B200_ERR_UNSUPPORTED, "case_conv2d: grouped conv on a channel-padded input");
-        const size_t taps = (size_t)p.r * p.s;
-        wpad.assign((size_t)p.k * ti.c_phys * taps, 128);
+    const int32_t *bsrc = bias;
+    if (c_in != ti.c || k_phys != p.k) {
+        const int cg_src = depthwise ? 1 : ti.c, cg_dst = depthwise ? 1 : c_in;
+        wpad.assign((size_t)k_phys * cg_dst * taps, p.wzp);
         for (int k = 0; k < p.k; ++k)
-            memcpy(&wpad[(size_t)k * ti.c_phys * taps], &weights[(size_t)k * ti.c * taps], (size_t)ti.c * taps);
-        p.c = ti.c_phys;
+            memcpy(&wpad[(size_t)k * cg_dst * taps], &weights[(size_t)k * cg_src * taps], (size_t)cg_src * taps);
         wsrc = wpad.data();
+        if (k_phys != p.k) {
+            bpad.assign(k_phys, 0);
+            if (bias)
+                memcpy(bpad.data(), bias, sizeof(int32_t) * p.k);
+            bsrc = bpad.data();
+            if (p.n_walpha == p.k && p.walpha) {
+                wapad.assign(p.walpha, p.walpha + p.k);
+                wapad.resize(k_phys, p.walpha[p.k - 1]);
+                p.walpha = wapad.data();
+                p.n_walpha = k_phys;
+            }
+        }
+        p.c = c_in;
+        p.k = k_phys;
+        if (depthwise)
+            p.group = c_in;
     }
-    B200_TRY(b200_conv2d_create(&p, wsrc, bias, &op.conv));
+    B200_TRY(b200_conv2d_create(&p, wsrc, bsrc, &op.conv));
     int32_t oh, ow;
     b200_conv2d_out_dims(op.conv, &oh, &ow);
-    op.out = new_tensor(cs, p.k, oh, ow, p.k);
+    op.out = new_tensor(cs, params->k, oh, ow, k_phys);
     *out = op.out;
     cs->ops.push_back(op);
     return B200_OK;
@@ -379,6 +409,8 @@ int b200_case_output_f32(b200_case_t *cs, int32_t tensor, float ialpha, uint8_t 
     B200_TRY(check_building(cs, "case_output_f32"));
     B200_TRY(check_tensor(cs, tensor, "case_output_f32"));
     const CaseTensor &t = cs->tensors[tensor];
+    if (t.c_phys != t.c)
+        return fail(B200_ERR_UNSUPPORTED, "case_output_f32: a channel-padded tensor (%d channels) can only leave as uint8", t.c);
     CaseIO io;
     io.tensor = tensor;
     io.is_f32 = true;
