@@ -194,6 +194,85 @@ __global__ void __launch_bounds__(256) conv_depthwise_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------
+// Depthwise 3x3 on dp4a.  A thread owns four consecutive channels of one output pixel.  The nine
+// tap words (four channels each) are transposed four at a time with byte permutes into words that
+// hold four taps of ONE channel, which dp4a multiplies with the matching weight word
+// [c/4][tap group][channel]: 8 permutes + 4 dp4a per 16 multiply-adds instead of 16 extractions
+// and 16 multiply-adds.  The requantize is the folded form of the tensor-core epilogue:
+// y = sat_u8(max((acc * mult + off64) >> shift, floor)), the host having checked shift >= 33.
+// Neighbouring threads read neighbouring words of a pixel and write neighbouring output words.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t (&ch)[4])
+{
+    const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);   // a0 b0 a1 b1 | c0 d0 c1 d1
+    const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c, d, 0x7362);   // a2 b2 a3 b3 | c2 d2 c3 d3
+    ch[0] = __byte_perm(t0, t1, 0x5410);
+    ch[1] = __byte_perm(t0, t1, 0x7632);
+    ch[2] = __byte_perm(t2, t3, 0x5410);
+    ch[3] = __byte_perm(t2, t3, 0x7632);
+}
+
+__global__ void __launch_bounds__(256) conv_depthwise3x3_kernel(
+    ConvGeom g, const uint32_t *__restrict__ x, const uint4 *__restrict__ w3, const int4 *__restrict__ q3,
+    uint32_t *__restrict__ y, int n)
+{
+    const uint32_t cq = (uint32_t)g.c / 4;
+    const uint32_t total = (uint32_t)n * g.oh * g.ow * cq;      // the launcher checks that it fits 32 bits
+    const uint32_t izp4 = (uint32_t)g.izp * 0x01010101u;
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const uint32_t ci = idx % cq;
+        const uint32_t pix = idx / cq;
+        const int ox = (int)(pix % (uint32_t)g.ow);
+        const uint32_t rowi = pix / (uint32_t)g.ow;
+        const int oy = (int)(rowi % (uint32_t)g.oh);
+        const uint32_t img = rowi / (uint32_t)g.oh;
+        const int iy0 = oy * g.stride_h - g.pad_h, ix0 = ox * g.stride_w - g.pad_w;
+        // word offsets fit 32 bits (checked by the launcher)
+        const uint32_t row_pitch = (uint32_t)g.w * cq;
+        const uint32_t *xc = x + (img * (uint32_t)g.h * row_pitch + ci);
+        uint32_t t[9];
+        if (iy0 >= 0 && iy0 + 2 < g.h && ix0 >= 0 && ix0 + 2 < g.w) {
+            const uint32_t *p0 = xc + ((uint32_t)iy0 * row_pitch + (uint32_t)ix0 * cq);
+#pragma unroll
+            for (int rr = 0; rr < 3; ++rr)
+#pragma unroll
+                for (int ss = 0; ss < 3; ++ss)
+                    t[rr * 3 + ss] = __ldg(p0 + (rr * row_pitch + ss * cq));
+        } else {
+#pragma unroll
+            for (int rr = 0; rr < 3; ++rr)
+#pragma unroll
+                for (int ss = 0; ss < 3; ++ss) {
+                    const int iy = iy0 + rr, ix = ix0 + ss;
+                    t[rr * 3 + ss] = (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w)
+                        ? __ldg(xc + ((uint32_t)iy * row_pitch + (uint32_t)ix * cq)) : izp4;
+                }
+        }
+        const uint4 wa = __ldg(w3 + (size_t)ci * 3), wb = __ldg(w3 + (size_t)ci * 3 + 1), wc = __ldg(w3 + (size_t)ci * 3 + 2);
+        uint32_t ch[4];
+        int acc[4];
+        transpose4x4(t[0], t[1], t[2], t[3], ch);
+        acc[0] = dp4a_us(ch[0], wa.x, 0); acc[1] = dp4a_us(ch[1], wa.y, 0);
+        acc[2] = dp4a_us(ch[2], wa.z, 0); acc[3] = dp4a_us(ch[3], wa.w, 0);
+        transpose4x4(t[4], t[5], t[6], t[7], ch);
+        acc[0] = dp4a_us(ch[0], wb.x, acc[0]); acc[1] = dp4a_us(ch[1], wb.y, acc[1]);
+        acc[2] = dp4a_us(ch[2], wb.z, acc[2]); acc[3] = dp4a_us(ch[3], wb.w, acc[3]);
+        // the ninth tap: byte j of the word against byte 0 of the weight word
+        acc[0] = dp4a_us(t[8] & 0xffu, wc.x, acc[0]); acc[1] = dp4a_us((t[8] >> 8) & 0xffu, wc.y, acc[1]);
+        acc[2] = dp4a_us((t[8] >> 16) & 0xffu, wc.z, acc[2]); acc[3] = dp4a_us(t[8] >> 24, wc.w, acc[3]);
+        int q[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int4 c4 = __ldg(q3 + (size_t)ci * 4 + j);
+            const long long off = (long long)(((unsigned long long)(uint32_t)c4.y << 32) | (uint32_t)c4.x);
+            const long long prod = (long long)acc[j] * c4.z + off;
+            q[j] = max((int)(prod >> 32) >> c4.w, g.relu_lo);
+        }
+        y[idx] = pack_sat_u8x4(q[0], q[1], q[2], q[3]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Row lowering for the tensor-core path of 4-channel images (see kernels.h).  One thread builds
 // one 32-byte window: eight 4-byte pixels, two 16-byte stores.  Neighbouring threads read
 // overlapping windows, so the image is fetched from DRAM once.
@@ -246,7 +325,15 @@ int conv_direct_launch(
     const size_t npix = (size_t)n * g.oh * g.ow;
     const int kg = g.k / g.group, cg = g.c / g.group;
     const bool depthwise = p.w_dw_dev && !acc_out && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
-    if (depthwise) {
+    const bool dw3 = depthwise && p.w_dw3_dev && p.q_dw3_dev && npix * (size_t)(g.c / 4) < 0xffffffffull
+        && (size_t)n * g.h * g.w * (size_t)(g.c / 4) < 0xffffffffull;
+    if (dw3) {
+        const size_t total = npix * (g.c / 4);
+        const int grid = resident_grid<conv_depthwise3x3_kernel, 256>((total + 255) / 256);
+        conv_depthwise3x3_kernel<<<grid, 256, 0, st>>>(
+            g, reinterpret_cast<const uint32_t *>(x), reinterpret_cast<const uint4 *>(p.w_dw3_dev), p.q_dw3_dev,
+            reinterpret_cast<uint32_t *>(y), n);
+    } else if (depthwise) {
         size_t total = npix * (g.c / 16);
         size_t blocks = (total + 255) / 256;
         size_t cap = (size_t)sm_count() * 8;

@@ -31,6 +31,8 @@ void destroy_conv(b200_conv *cv)
         return;
     cudaFree(cv->direct.w_dev);
     cudaFree(cv->direct.w_dw_dev);
+    cudaFree(cv->direct.w_dw3_dev);
+    cudaFree(cv->direct.q_dw3_dev);
     cudaFree(cv->direct.bias_fold_dev);
     cudaFree(cv->direct.mult_dev);
     cudaFree(cv->direct.shift_dev);
@@ -137,6 +139,31 @@ int b200_conv2d_create(
             for (int t = 0; t < taps; ++t)
                 w_dw[(size_t)t * g.c + c] = w_s8[(size_t)c * taps + t];
         rc = upload(w_dw, &cv->direct.w_dw_dev);
+        // the dp4a form of the 3x3 case (conv_depthwise3x3_kernel)
+        bool fast = g.r == 3 && g.s == 3 && g.qmax == 255;
+        for (int k = 0; k < g.k && fast; ++k)
+            fast = shift[k] >= 33 && shift[k] <= 53;
+        if (rc == B200_OK && fast) {
+            std::vector<uint32_t> w3((size_t)(g.c / 4) * 3 * 4, 0);
+            std::vector<int4> q3(g.c);
+            for (int c = 0; c < g.c; ++c) {
+                for (int grp = 0; grp < 3; ++grp) {
+                    uint32_t word = 0;
+                    for (int j = 0; j < 4; ++j) {
+                        const int t = grp * 4 + j;
+                        if (t < 9)
+                            word |= (uint32_t)(uint8_t)w_s8[(size_t)c * 9 + t] << (8 * j);
+                    }
+                    w3[((size_t)(c / 4) * 3 + grp) * 4 + (c % 4)] = word;
+                }
+                // (acc + bias_fold) * mult, rounded shift, + ozp  ==  (acc * mult + off64) >> shift
+                const long long off64 = (long long)bias_fold[c] * (long long)mult[c] + (1ll << (shift[c] - 1))
+                    + ((long long)g.ozp << shift[c]);
+                q3[c] = make_int4((int)(uint32_t)(unsigned long long)off64, (int)(off64 >> 32), (int)mult[c], shift[c] - 32);
+            }
+            rc = upload(w3, &cv->direct.w_dw3_dev);
+            if (rc == B200_OK) rc = upload(q3, &cv->direct.q_dw3_dev);
+        }
     }
     if (rc != B200_OK) {
         destroy_conv(cv);

@@ -70,6 +70,11 @@ struct ConvGeom {
 struct ConvDirectPlan {
     int8_t *w_dev = nullptr;
     int8_t *w_dw_dev = nullptr;   // depthwise only: [r][s][c] int8
+    // depthwise 3x3 with every requantize shift >= 33 and 8-bit output: weights as dp4a words
+    // [c/4][3 tap groups][4 channels] (taps 0-3, 4-7, 8 of one channel per word) and per channel
+    // {folded 64-bit addend, mult, shift - 32}
+    uint32_t *w_dw3_dev = nullptr;
+    int4 *q_dw3_dev = nullptr;
     int32_t *bias_fold_dev = nullptr;
     uint32_t *mult_dev = nullptr;
     int32_t *shift_dev = nullptr;
