@@ -24,7 +24,7 @@ L2_BYTES = 126 << 20
 SWEEP_SHAPES = [(64, 64, 56), (128, 128, 28), (256, 256, 14), (512, 512, 7)]
 
 
-def time_conv(c, k, hw, ks, stride, batch, group=1, algo=ops.ALGO_AUTO, iters=20, warmup=5, seed=0):
+def time_conv(c, k, hw, ks, stride, batch, group=1, algo=ops.ALGO_AUTO, iters=20, warmup=5, seed=0, graph=False):
     rng = np.random.default_rng(seed)
     w = (rng.integers(-127, 128, (k, c // group, ks, ks)) + 128).astype(np.uint8)
     b = rng.integers(-4096, 4097, k).astype(np.int32)
@@ -36,22 +36,39 @@ def time_conv(c, k, hw, ks, stride, batch, group=1, algo=ops.ALGO_AUTO, iters=20
     # rotate buffers so that a launch never finds its operands in L2 from the previous one
     nbuf = max(2, min(8, -(-2 * L2_BYTES // max(1, in_bytes + out_bytes)) + 1))
     xs = [torch.randint(0, 256, (batch, hw, hw, c), dtype=torch.uint8, device="cuda") for _ in range(nbuf)]
-    for i in range(warmup):
+    for i in range(max(warmup, nbuf)):
         y = conv(xs[i % nbuf])
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(iters):
-        y = conv(xs[i % nbuf])
-    e1.record()
-    torch.cuda.synchronize()
+    if graph:
+        # the same launches replayed from a CUDA graph: the device time per launch without the
+        # host's per-call cost (Python, output allocation, tensor-map encoding)
+        side = torch.cuda.Stream()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(g, stream=side):
+                for i in range(iters):
+                    y = conv(xs[i % nbuf])
+            g.replay()
+            side.synchronize()
+            e0.record(side)
+            g.replay()
+            e1.record(side)
+        torch.cuda.synchronize()
+    else:
+        e0.record()
+        for i in range(iters):
+            y = conv(xs[i % nbuf])
+        e1.record()
+        torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / iters
     assert ops.device_status() == 0
     ops_count = 2.0 * batch * oh * ow * k * (c // group) * ks * ks
     byts = in_bytes + out_bytes + w.size + 4 * k
     return dict(c=c, k=k, hw=hw, ks=ks, stride=stride, batch=batch, group=group,
                 algo={1: "cuda_core", 2: "tcgen05_igemm"}[conv.algo], ms=ms, tops=ops_count / ms / 1e9,
-                gbs=byts / ms / 1e6, intensity_op_per_byte=ops_count / byts, buffers=nbuf)
+                gbs=byts / ms / 1e6, intensity_op_per_byte=ops_count / byts, buffers=nbuf,
+                timing="cuda graph replay" if graph else "eager launches")
 
 
 def main(argv=None):
@@ -67,6 +84,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--direct", action="store_true", help="force the CUDA-core kernel")
+    ap.add_argument("--graph", action="store_true", help="time the launches replayed from one CUDA graph")
     a = ap.parse_args(argv)
     algo = ops.ALGO_DIRECT if a.direct else ops.ALGO_AUTO
     if a.sweep:
@@ -74,9 +92,11 @@ def main(argv=None):
             for ks in (1, 3):
                 for stride in (1, 2):
                     for batch in (1, 32, 256):
-                        print(json.dumps(time_conv(c, k, hw, ks, stride, batch, algo=algo, iters=a.iters, warmup=a.warmup)))
+                        print(json.dumps(time_conv(c, k, hw, ks, stride, batch, algo=algo, iters=a.iters, warmup=a.warmup,
+                                                   graph=a.graph)))
     else:
-        print(json.dumps(time_conv(a.c, a.k, a.hw, a.ks, a.stride, a.batch, a.group, algo, a.iters, a.warmup)))
+        print(json.dumps(time_conv(a.c, a.k, a.hw, a.ks, a.stride, a.batch, a.group, algo, a.iters, a.warmup,
+                                   graph=a.graph)))
     return 0
 
 
