@@ -161,6 +161,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok != 0;
 }
+// Non-blocking form: the producer lanes poll many barriers from one warp, where a try_wait that
+// suspends on one lane's barrier would hold back the lanes whose barrier is ready.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: returns false when the barrier did not flip within kWaitCycles or another role
 // has already given up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
@@ -524,60 +538,55 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 tw.advance(g);
             }
             uint32_t phase = 0;
-            // Lanes whose sequence has ended drop out of `mask`; the others meet at every poll, so a
-            // lane whose stage has become free issues in that same pass of the loop.
-            const unsigned mask0 = slots >= 32 ? 0xffffffffu : ((1u << slots) - 1u);
-            bool valid = tile < total_tiles;
-            unsigned mask = __ballot_sync(mask0, valid);
-            while (valid) {
-                // k-block -> (tap row, tap column, channel chunk); the divisions are multiplications by
-                // reciprocals the host rounded up (exact for operands below 2^15)
-                const int tap = (int)(((uint64_t)(uint32_t)kb * g.rcp_cchunks) >> 30);
-                const int cc = (kb - tap * cchunks) * g.bk;
-                const int rr = (int)(((uint64_t)(uint32_t)tap * g.rcp_s) >> 30);
-                const int ss = tap - rr * g.s;
-                // input row of output row oh for this tap: ih = oh*stride + d, d = rr - pad
-                //   = stride * (oh + (d - p) / stride) + p with p = d mod stride (0 <= p < stride)
-                const int dh = rr - g.pad_h, ph = dh & sh_h;
-                const int dw = ss - g.pad_w, pw = dw & sh_w;
-                const int yh = (tw.thi << g.th_sh) + ((dh - ph) >> sh_h);
-                const int xw = (tw.twi << g.tw_sh) + ((dw - pw) >> sh_w);
-                const int n0 = tw.tni * g.tn;
-                const CUtensorMap *amap = &maps.a[ph * 2 + pw];
-                const long long t0 = clock64();
-                int spins = 0;
-                bool done = false, failed = false;
-                do {
-                    if (!done) {
-                        if (mbar_try_wait(eb, phase ^ 1)) {
-                            if (first)
-                                mbar_expect_tx(fb, tx_bytes);
-                            if (g.a_wide)   // rows of tw pixels x 32 bytes, in 8-byte elements
-                                tma_load_3d(a_dst, amap, fb, xw << 2, yh, n0);
-                            else
-                                tma_load_4d(a_dst, amap, fb, cc, xw, yh, n0);
-                            if (!g.b_resident)
-                                tma_load_2d(b_dst, &maps.b, fb, kb * g.bk, tw.nt * g.bn);
-                            done = true;
-                        } else if ((++spins & 255) == 0 && (*abort_flag != 0 || clock64() - t0 > kWaitCycles)) {
-                            atomicCAS(g.status, 0, kErrProducerWait);
-                            *abort_flag = 1;
-                            failed = true;
-                            done = true;
+            // Every pass of the loop each lane polls its own stage once (without suspending: a blocked
+            // lane would hold back the ready ones); a lane whose stage is free issues its loads and
+            // moves on to its next k-block, the others poll again in the next pass.  No lane ever waits
+            // for another lane's stage.
+            const unsigned lanes_mask = slots >= 32 ? 0xffffffffu : ((1u << slots) - 1u);
+            bool active = tile < total_tiles;
+            long long t0 = clock64();
+            int spins = 0;
+            while (__any_sync(lanes_mask, active)) {
+                if (active) {
+                    if (mbar_test_wait(eb, phase ^ 1)) {
+                        // k-block -> (tap row, tap column, channel chunk); the divisions are multiplications
+                        // by reciprocals the host rounded up (exact for operands below 2^15)
+                        const int tap = (int)(((uint64_t)(uint32_t)kb * g.rcp_cchunks) >> 30);
+                        const int cc = (kb - tap * cchunks) * g.bk;
+                        const int rr = (int)(((uint64_t)(uint32_t)tap * g.rcp_s) >> 30);
+                        const int ss = tap - rr * g.s;
+                        // input row of output row oh for this tap: ih = oh*stride + d, d = rr - pad
+                        //   = stride * (oh + (d - p) / stride) + p with p = d mod stride (0 <= p < stride)
+                        const int dh = rr - g.pad_h, ph = dh & sh_h;
+                        const int dw = ss - g.pad_w, pw = dw & sh_w;
+                        const int yh = (tw.thi << g.th_sh) + ((dh - ph) >> sh_h);
+                        const int xw = (tw.twi << g.tw_sh) + ((dw - pw) >> sh_w);
+                        const int n0 = tw.tni * g.tn;
+                        const CUtensorMap *amap = &maps.a[ph * 2 + pw];
+                        if (first)
+                            mbar_expect_tx(fb, tx_bytes);
+                        if (g.a_wide)   // rows of tw pixels x 32 bytes, in 8-byte elements
+                            tma_load_3d(a_dst, amap, fb, xw << 2, yh, n0);
+                        else
+                            tma_load_4d(a_dst, amap, fb, cc, xw, yh, n0);
+                        if (!g.b_resident)
+                            tma_load_2d(b_dst, &maps.b, fb, kb * g.bk, tw.nt * g.bn);
+                        phase ^= 1;
+                        kb += slots;
+                        while (kb >= kblocks) {
+                            kb -= kblocks;
+                            tile += gridDim.x;
+                            tw.advance(g);
                         }
+                        active = tile < total_tiles;
+                        t0 = clock64();
+                        spins = 0;
+                    } else if ((++spins & 255) == 0 && (*abort_flag != 0 || clock64() - t0 > kWaitCycles)) {
+                        atomicCAS(g.status, 0, kErrProducerWait);
+                        *abort_flag = 1;
+                        active = false;
                     }
-                } while (!__all_sync(mask, done));
-                if (__any_sync(mask, failed))
-                    break;
-                phase ^= 1;
-                kb += slots;
-                while (kb >= kblocks) {
-                    kb -= kblocks;
-                    tile += gridDim.x;
-                    tw.advance(g);
                 }
-                valid = tile < total_tiles;
-                mask = __ballot_sync(mask, valid);
             }
         }
     } else if (warp == 1) {
