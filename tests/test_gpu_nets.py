@@ -109,3 +109,39 @@ def test_pipelined_submit_matches_reference(port):
             want, _, _ = nets.run_cpu(spec, x.numpy(), port)
             assert_same(y.numpy().reshape(want.shape).view(np.uint32), want.view(np.uint32), "round %d batch %d" % (rnd, i))
     cs.close()
+
+
+def test_resnet50_bench_size_paths_agree(port):
+    """The benchmark's own size (ResNet-50, batch 256): the eager run, the CUDA-graph replay, the
+    pipelined submit and the case with fused residual adds give the same 256 x 1000 logits bit for
+    bit, and images taken from both ends and the middle of the batch equal the CPU restatement."""
+    import torch
+    from nart_b200 import nets
+    spec = nets.resnet(50, seed=3)
+    batch = 256
+    x = torch.from_numpy(np.random.default_rng(11).integers(0, 256, (batch, 3, 224, 224), dtype=np.uint8)).pin_memory()
+    side = torch.cuda.Stream()
+    results = {}
+    for name, fuse in (("plain", False), ("fused", True)):
+        cs, _ = nets.to_case(spec, batch, fuse=fuse)
+        y = torch.zeros((batch, 1000), dtype=torch.float32).pin_memory()
+        cs.run_host_ptrs(batch, [x.data_ptr()], [y.data_ptr()], side.cuda_stream)
+        results[name + " eager"] = y.numpy().copy()
+        if not fuse:
+            cs.use_graph(True)
+            for _ in range(3):      # eager, capture, replay
+                y.zero_()
+                cs.run_host_ptrs(batch, [x.data_ptr()], [y.data_ptr()], side.cuda_stream)
+            results["graph replay"] = y.numpy().copy()
+            y.zero_()
+            cs.submit_host_ptrs(batch, [x.data_ptr()], [y.data_ptr()])
+            cs.wait()
+            results["submit"] = y.numpy().copy()
+        cs.close()
+    base = results["plain eager"]
+    for name, got in results.items():
+        assert_same(got.view(np.uint32), base.view(np.uint32), name + " vs plain eager")
+    pick = [0, 131, 255]
+    want, _, _ = nets.run_cpu(spec, x.numpy()[pick], port)
+    assert_same(base[pick].view(np.uint32), want.reshape(len(pick), -1).view(np.uint32), "batch-256 images vs restatement")
+    assert len(np.unique(base)) > 16          # not a collapsed network: the uint8 logits take many values
