@@ -451,6 +451,9 @@ __host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int 
     return L;
 }
 
+// HAS_RES: the instantiation whose epilogue can add a residual tensor; plans without a fused add run the
+// other one, which carries none of that code.
+template <bool HAS_RES>
 __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const IgemmArgs g)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -719,7 +722,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             const int ow = ow0 + lw, oh = oh0 + lh, img = n0 + ln;
             const bool pix_valid = ow < g.ow && oh < g.oh && img < g.n;
             const uint8_t *res_row = g.res;
-            if (g.res != nullptr && pix_valid)
+            if ((HAS_RES && g.res != nullptr) && pix_valid)
                 res_row += (((size_t)img * g.oh + oh) * g.ow + ow) * g.cout + k0;
             const long long *off_row = g.off + k0;
             if (!single_class)
@@ -767,7 +770,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                         tmem_ld32(t_row + c0, v);
                     else
                         tmem_ld16(t_row + c0, v);
-                    if (g.res != nullptr && pix_valid) {
+                    if ((HAS_RES && g.res != nullptr) && pix_valid) {
                         // the residual bytes of this pixel's 32 channels, in flight with the accumulator read
                         const uint4 *rp = reinterpret_cast<const uint4 *>(res_row + c0);
                         const uint4 ra = __ldg(rp), rb = __ldg(rp + 1);
@@ -776,7 +779,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                     }
                     tmem_ld_wait();
                     // the common case is one straight-line block of 32 independent chains
-                    if (g.res != nullptr) {          // host guarantees the fast form and whole 32-column chunks
+                    if ((HAS_RES && g.res != nullptr)) {          // host guarantees the fast form and whole 32-column chunks
                         if (single_class)
                             epi_chunk<true, true, 32, true, true>(v, c0, off_row, ec, rv);
                         else
@@ -1337,7 +1340,8 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     }
     p->smem = smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (p->cpad / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024;
     if (!p->attr_set) {
-        B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         p->attr_set = true;
     }
     p->last_x = x;
@@ -1382,7 +1386,10 @@ int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cud
             }
         }
     }
-    conv_igemm_i8_kernel<<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
+    if (res != nullptr)
+        conv_igemm_i8_kernel<true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
+    else
+        conv_igemm_i8_kernel<false><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
