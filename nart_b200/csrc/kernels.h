@@ -17,6 +17,7 @@ struct PoolGeom {
     int n, c, h, w, oh, ow;
     int kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w;
     int izp, ozp, qmax;
+    int lut_identity;   // MAX: the requantize table maps every byte to itself (equal scales and zero points)
 };
 struct PoolAvgTab {
     static constexpr int kMax = 4;

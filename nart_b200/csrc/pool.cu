@@ -89,6 +89,85 @@ __global__ void __launch_bounds__(256) pool_max_kernel(
     }
 }
 
+// MAX on 16-channel vectors for a compile-time window KH x KW and horizontal stride SW, with 32-bit
+// index arithmetic: one thread owns 16 channels of TWO output pixels side by side and loads the
+// union of their windows (KH x (KW + SW) vectors) in one unrolled batch, so that all of a thread's
+// loads are in flight together and the columns the two windows share are loaded once.  Taps
+// outside the image read as 0, the value the running maximum starts from.  IDENT skips the table
+// (it maps every byte to itself).  Results equal pool_max_kernel<16>.
+template <int KH, int KW, int SW, bool IDENT>
+__global__ void __launch_bounds__(256) pool_max_pair_kernel(
+    const uint4 *__restrict__ x, uint4 *__restrict__ y, PoolGeom g, const uint8_t *__restrict__ lut_g, uint32_t total)
+{
+    __shared__ uint8_t lut[256];
+    if (!IDENT) {
+        lut[threadIdx.x] = lut_g[threadIdx.x];
+        __syncthreads();
+    }
+    constexpr int UW = KW + SW;   // columns of the union of the two windows
+    const uint32_t cv = (uint32_t)g.c >> 4, owp = (uint32_t)g.ow >> 1;
+    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
+        const uint32_t ci = idx % cv;
+        uint32_t pix = idx / cv;
+        const uint32_t oxp = pix % owp;
+        pix /= owp;
+        const uint32_t oy = pix % (uint32_t)g.oh, n = pix / (uint32_t)g.oh;
+        const int hs = (int)oy * g.stride_h - g.pad_h;
+        const int ws = (int)oxp * 2 * SW - g.pad_w;
+        const uint4 *img = x + (size_t)n * (uint32_t)g.h * (uint32_t)g.w * cv + ci;
+        uint4 q[KH][UW];
+#pragma unroll
+        for (int r = 0; r < KH; ++r)
+#pragma unroll
+            for (int j = 0; j < UW; ++j) {
+                const int iy = hs + r, ix = ws + j;
+                q[r][j] = make_uint4(0, 0, 0, 0);
+                if ((unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w)
+                    q[r][j] = __ldg(img + ((uint32_t)iy * (uint32_t)g.w + (uint32_t)ix) * cv);
+            }
+        uint32_t m0[4] = { 0, 0, 0, 0 }, m1[4] = { 0, 0, 0, 0 };
+#pragma unroll
+        for (int r = 0; r < KH; ++r)
+#pragma unroll
+            for (int j = 0; j < UW; ++j) {
+                if (j < KW) {
+                    m0[0] = __vmaxu4(m0[0], q[r][j].x); m0[1] = __vmaxu4(m0[1], q[r][j].y);
+                    m0[2] = __vmaxu4(m0[2], q[r][j].z); m0[3] = __vmaxu4(m0[3], q[r][j].w);
+                }
+                if (j >= SW) {
+                    m1[0] = __vmaxu4(m1[0], q[r][j].x); m1[1] = __vmaxu4(m1[1], q[r][j].y);
+                    m1[2] = __vmaxu4(m1[2], q[r][j].z); m1[3] = __vmaxu4(m1[3], q[r][j].w);
+                }
+            }
+        if (!IDENT) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                m0[j] = pack4(lut[m0[j] & 0xff], lut[(m0[j] >> 8) & 0xff], lut[(m0[j] >> 16) & 0xff], lut[m0[j] >> 24]);
+                m1[j] = pack4(lut[m1[j] & 0xff], lut[(m1[j] >> 8) & 0xff], lut[(m1[j] >> 16) & 0xff], lut[m1[j] >> 24]);
+            }
+        }
+        uint4 *out = y + ((n * (uint32_t)g.oh + oy) * (uint32_t)g.ow + oxp * 2) * cv + ci;
+        out[0] = make_uint4(m0[0], m0[1], m0[2], m0[3]);
+        out[cv] = make_uint4(m1[0], m1[1], m1[2], m1[3]);
+    }
+}
+
+template <int KH, int KW, int SW>
+int pool_max_pair_launch(const uint8_t *x, uint8_t *y, const PoolGeom &g, const uint8_t *lut_dev, size_t pairs, cudaStream_t st)
+{
+    const size_t blocks = (pairs + 255) / 256;
+    const uint4 *x4 = reinterpret_cast<const uint4 *>(x);
+    uint4 *y4 = reinterpret_cast<uint4 *>(y);
+    if (g.lut_identity)
+        pool_max_pair_kernel<KH, KW, SW, true><<<resident_grid<pool_max_pair_kernel<KH, KW, SW, true>, 256>(blocks), 256, 0, st>>>(
+            x4, y4, g, lut_dev, (uint32_t)pairs);
+    else
+        pool_max_pair_kernel<KH, KW, SW, false><<<resident_grid<pool_max_pair_kernel<KH, KW, SW, false>, 256>(blocks), 256, 0, st>>>(
+            x4, y4, g, lut_dev, (uint32_t)pairs);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
 // AVE: sum of (x - izp) over the in-image part of the window; the multiplier and shift depend on
 // the padded window size (pool.c:217-221) and come from a small host-built table indexed by how
 // many rows / columns the window loses at the far edge.
@@ -176,6 +255,7 @@ int pool_prepare(
     g->kernel_h = kernel_h; g->kernel_w = kernel_w; g->pad_h = pad_h; g->pad_w = pad_w;
     g->stride_h = stride_h; g->stride_w = stride_w;
     g->izp = izp; g->ozp = ozp; g->qmax = (1 << obits) - 1;
+    g->lut_identity = 0;
     const int qmax = g->qmax;
     if (method == 0) {
         uint32_t m16;
@@ -188,6 +268,10 @@ int pool_prepare(
             int32_t r = (int32_t)(rshift_rn_host(prod, sh) + ozp);
             lut[q] = (uint8_t)(r > qmax ? qmax : (r < 0 ? 0 : r));
         }
+        g->lut_identity = 1;
+        for (int q = 0; q < 256; ++q)
+            if (lut[q] != q)
+                g->lut_identity = 0;
     } else {
         // the windows at the far edge may be cut by `in + pad` (ceil mode): index the table by the
         // number of rows / columns cut
@@ -241,6 +325,19 @@ int pool_launch(
                                                                            : 1;
     size_t total = (size_t)n * g.oh * g.ow * (c / vec);
     const size_t blocks = (total + 255) / 256;
+    const size_t cv16 = (size_t)c / 16;
+    if (method == 0 && vec == 16 && g.ow % 2 == 0 && (size_t)n * g.h * g.w * cv16 < 0xffffffffull) {
+        // two outputs per thread, unrolled window, 32-bit indices: the common window shapes
+        const size_t pairs = (size_t)n * g.oh * (g.ow / 2) * cv16;
+        if (pairs < 0xffffffffull - 256ull * 65536ull) {
+            if (g.kernel_h == 3 && g.kernel_w == 3 && g.stride_w == 2)
+                return pool_max_pair_launch<3, 3, 2>(x, y, g, lut_dev, pairs, st);
+            if (g.kernel_h == 3 && g.kernel_w == 3 && g.stride_w == 1)
+                return pool_max_pair_launch<3, 3, 1>(x, y, g, lut_dev, pairs, st);
+            if (g.kernel_h == 2 && g.kernel_w == 2 && g.stride_w == 2)
+                return pool_max_pair_launch<2, 2, 2>(x, y, g, lut_dev, pairs, st);
+        }
+    }
     if (method == 0) {
         if (vec == 16) pool_max_kernel<16><<<resident_grid<pool_max_kernel<16>, 256>(blocks), 256, 0, st>>>(x, y, g, lut_dev);
         else if (vec == 4) pool_max_kernel<4><<<resident_grid<pool_max_kernel<4>, 256>(blocks), 256, 0, st>>>(x, y, g, lut_dev);

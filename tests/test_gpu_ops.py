@@ -206,6 +206,15 @@ def test_pool(ops, port):
             want = port.pool_u8(x, m, (3, 2), (1, 0), (2, 1), 1, 0.05, 33, 0.07, 12)
             got = ops.pool(to_dev_nhwc(x), m, (3, 2), (1, 0), (2, 1), 1, 0.05, 33, 0.07, 12)
             assert_same(to_host_nchw(got), want, "pool c=%d m=%d" % (c, m))
+    # even output widths and the common windows (3x3 stride 1 or 2, 2x2 stride 2) take the
+    # two-outputs-per-thread max kernel, with and without the identity table; 3x5 stays generic
+    x = rng.integers(0, 256, (2, 48, 11, 16), dtype=np.uint8)
+    for kern, pad, stride, cm in (((3, 3), (1, 1), (1, 1), 0), ((2, 2), (0, 0), (2, 2), 1), ((3, 3), (1, 1), (2, 2), 0),
+                                  ((3, 3), (0, 0), (2, 2), 1), ((3, 5), (1, 2), (2, 2), 0)):
+        for oa, oz in ((0.05, 33), (0.07, 12)):
+            want = port.pool_u8(x, 0, kern, pad, stride, cm, 0.05, 33, oa, oz)
+            got = ops.pool(to_dev_nhwc(x), 0, kern, pad, stride, cm, 0.05, 33, oa, oz)
+            assert_same(to_host_nchw(got), want, "pool pair %s %s %s" % (kern, stride, oa))
     # the ResNet shapes: 3x3 s2 p1 max on 112x112 (ceil_mode false) and 7x7 global average
     x = rng.integers(0, 256, (2, 64, 112, 112), dtype=np.uint8)
     want = port.pool_u8(x, 0, (3, 3), (1, 1), (2, 2), 0, 0.05, 3, 0.05, 3)
