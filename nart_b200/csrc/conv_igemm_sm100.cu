@@ -1040,6 +1040,11 @@ int conv_igemm_create(
             p->bn = best;
         }
     }
+    // a 1x1 output map (an inner product run as a full-image conv) has one row per image, far too few
+    // row tiles to fill the SMs at any usual batch: narrow channel tiles spread the weight matrix over
+    // many CTAs instead (2048 -> 1000 at batch 256: 8 CTAs and 0.035 ms at 256 wide, 64 CTAs and < 0.02 ms at 32)
+    if (g.oh * g.ow == 1 && g.k >= 32)
+        p->bn = 32;
     if (const char *e = getenv("B200_IGEMM_BN")) {   // tuning aid: channel-tile width, a multiple of 16 up to 256
         int v = atoi(e);
         if (v >= 16 && v <= 256 && v % 16 == 0 && v <= (g.k + 15) / 16 * 16)
