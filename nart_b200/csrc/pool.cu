@@ -197,16 +197,29 @@ __global__ void __launch_bounds__(256) pool_avg_kernel(
 #pragma unroll
         for (int j = 0; j < VEC; ++j)
             sum[j] = 0;
-        int cnt = 0;
-        for (int iy = hs; iy < he; ++iy)
-            for (int ix = ws; ix < we; ++ix) {
-                uint32_t v[W];
-                load_words<VEC>(x + (((size_t)n * g.h + iy) * g.w + ix) * g.c + (size_t)ci * VEC, v);
+        const int cnt = max(he - hs, 0) * max(we - ws, 0);
+        // eight taps per round, loaded before any is used, so that a large window (the global average
+        // of a 7x7 map is 49 taps per thread) keeps several loads in flight
+        constexpr int UNR = 8;
+        for (int iy = hs; iy < he; ++iy) {
+            const uint8_t *row = x + (((size_t)n * g.h + iy) * g.w) * g.c + (size_t)ci * VEC;
+            for (int ix = ws; ix < we; ix += UNR) {
+                uint32_t v[UNR][W];
 #pragma unroll
-                for (int j = 0; j < VEC; ++j)
-                    sum[j] += (int)((v[j / 4] >> (8 * (j % 4))) & 0xff);
-                ++cnt;
+                for (int u = 0; u < UNR; ++u) {
+#pragma unroll
+                    for (int j = 0; j < W; ++j)
+                        v[u][j] = 0;
+                    if (ix + u < we)
+                        load_words<VEC>(row + (size_t)(ix + u) * g.c, v[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < UNR; ++u)
+#pragma unroll
+                    for (int j = 0; j < VEC; ++j)
+                        sum[j] += (int)((v[u][j / 4] >> (8 * (j % 4))) & 0xff);
             }
+        }
         uint32_t o[W];
 #pragma unroll
         for (int j = 0; j < W; ++j)
