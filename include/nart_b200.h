@@ -107,7 +107,9 @@ typedef struct b200_conv_params {
     int32_t pad_h, pad_w, stride_h, stride_w, group;
     float ialpha;           /* SETTING_QUANT_IALPHA[0]                                        */
     uint8_t izp;            /* SETTING_QUANT_IZERO_POINT[0]                                   */
-    uint8_t wzp;            /* SETTING_QUANT_WZERO_POINT[0]; only 128 (int8 weights) is built */
+    uint8_t wzp;            /* SETTING_QUANT_WZERO_POINT[0]; 128 = int8 weights stored as value + 128.
+                             * Other values cost one extra pass over the activations on the
+                             * tensor-core path (window sums of x) and rule out the fused residual add */
     uint8_t ozp;            /* SETTING_QUANT_OZERO_POINT[0]                                   */
     uint8_t obits;          /* SETTING_QUANT_OBITS[0], 1..8                                   */
     float oalpha;           /* SETTING_QUANT_OALPHA[0]                                        */
@@ -126,9 +128,15 @@ B200_API int b200_conv2d_create(
 B200_API int b200_conv2d_out_dims(const b200_conv_t *conv, int32_t *oh, int32_t *ow);
 /* The algorithm the plan resolved to (B200_CONV_ALGO_DIRECT or _IGEMM). */
 B200_API int b200_conv2d_algo(const b200_conv_t *conv);
-/* x: device NHWC [n][h][w][c]; y: device NHWC [n][oh][ow][k]. */
+/* x: device NHWC [n][h][w][c]; y: device NHWC [n][oh][ow][k].  Plans with a scratch tensor (the
+ * row-lowered 4-channel stem; window sums for wzp != 128) grow it, with a device synchronization,
+ * the first time a larger batch arrives; the old tensor is freed then. */
 B200_API int b200_conv2d_run(
     b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, b200_stream_t stream);
+/* Sizes the plan's scratch tensors for batches of up to n images now, so that no later run
+ * allocates or frees (a CUDA graph captured from a run keeps the scratch address it saw).
+ * No counterpart in the reference; a no-op for plans without scratch. */
+B200_API int b200_conv2d_reserve(b200_conv_t *conv, int32_t n);
 /* As b200_conv2d_run, also writing the int32 accumulators (bias included) as NHWC int32.
  * Debug/verification entry; always takes the CUDA-core path. */
 B200_API int b200_conv2d_run_acc(

@@ -56,6 +56,7 @@ SIGNATURES = {
     "b200_conv2d_algo": (C.c_int, [vp]),
     "b200_conv2d_run": (C.c_int, [vp, vp, i32, vp, vp]),
     "b200_conv2d_run_acc": (C.c_int, [vp, vp, i32, vp, vp, vp]),
+    "b200_conv2d_reserve": (C.c_int, [vp, i32]),
     "b200_conv2d_destroy": (C.c_int, [vp]),
     "b200_conv2d_run_static_scratch": (C.c_int, [vp, vp, i32, vp, vp]),
     "b200_conv2d_fuse_residual_add": (C.c_int, [vp, i32, C.POINTER(f32), C.POINTER(u8), C.POINTER(f32), f32, u8, u8,

@@ -438,6 +438,10 @@ int b200_case_prepare(b200_case_t *cs, int32_t max_batch)
         for (auto &io : *ios)
             B200_TRY(b200_malloc(&io.staging, io.bytes_per_image * max_batch));
     for (auto &op : cs->ops) {
+        // conv scratch tensors are sized once, for the largest batch: a graph captured at one batch size
+        // keeps their addresses, which a later, larger batch must not move
+        if (op.kind == OpKind::Conv && op.conv)
+            B200_TRY(b200_conv2d_reserve(op.conv, max_batch));
         if (op.kind == OpKind::Relu || (op.kind == OpKind::Pool && op.method == 0)) {
             B200_TRY(b200_malloc((void **)&op.lut_dev, 256));
             B200_CUDA_TRY(cudaMemcpy(op.lut_dev, op.lut, 256, cudaMemcpyHostToDevice));

@@ -62,6 +62,10 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
     const uint8_t *ximg = x + (size_t)img * g.h * g.w * g.c + (size_t)grp * cg;
 
     int acc[4] = { 0, 0, 0, 0 };
+    // wzp != 128: sum of the bytes the products see (out-of-image taps read izp, like the products),
+    // with the bytes past the group's last channel masked out of the last word
+    int xsum = 0;
+    const uint32_t last_ones = 0x01010101u >> (8 * (cg4 - cg));
     for (int item0 = 0; item0 < items; item0 += DCHUNK) {
         const int nitem = min(DCHUNK, items - item0);
         __syncthreads();
@@ -96,6 +100,8 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
                 acc[1] = dp4a_us(xv, wv.y, acc[1]);
                 acc[2] = dp4a_us(xv, wv.z, acc[2]);
                 acc[3] = dp4a_us(xv, wv.w, acc[3]);
+                if (g.wzp_d != 0)
+                    xsum = (int)__dp4a(xv, cw == cwords - 1 ? last_ones : 0x01010101u, (unsigned)xsum);
                 if (++cw == cwords) {
                     cw = 0;
                     ++tap;
@@ -112,6 +118,8 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
             break;
         int k = k0 + kq * 4 + j;
         int a = acc[j] + bias_fold[k];
+        if (g.wzp_d != 0)   // sum (x - izp) over all taps (the out-of-image ones give 0) times -(wzp - 128)
+            a -= g.wzp_d * (xsum - g.izp * g.r * g.s * cg);
         if (acc_out)
             acc_out[pix * g.k + k] = a;
         q[j] = sat_relu(requant_raw(a, mult[k], shift[k], g.ozp), g.qmax, g.relu_lo);
@@ -131,6 +139,7 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
 // formed per channel.  Weights are [r][s][c] int8.  HBM-bound: each activation byte is read once
 // from DRAM (neighbouring taps hit L1/L2), each output byte written once.
 // ---------------------------------------------------------------------------------------------
+template <bool WZP>
 __global__ void __launch_bounds__(256) conv_depthwise_kernel(
     ConvGeom g, const uint8_t *__restrict__ x, const int8_t *__restrict__ w_rsc,
     const int32_t *__restrict__ bias_fold, const uint32_t *__restrict__ mult,
@@ -155,6 +164,14 @@ __global__ void __launch_bounds__(256) conv_depthwise_kernel(
                 acc[4 * j] = b.x; acc[4 * j + 1] = b.y; acc[4 * j + 2] = b.z; acc[4 * j + 3] = b.w;
             }
         }
+        // WZP: every channel is its own group, so the correction -(wzp - 128) * sum (x - izp) is per
+        // channel: fold it into the weight, w - wzp = s8 - wzp_d, with izp at the out-of-image taps
+        // (x - izp = 0 there) and the constant izp * taps * wzp_d added back
+        if (WZP) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                acc[j] += g.izp * g.r * g.s * g.wzp_d;
+        }
         for (int rr = 0; rr < g.r; ++rr) {
             const int iy = iy0 + rr;
             for (int ss = 0; ss < g.s; ++ss) {
@@ -174,6 +191,8 @@ __global__ void __launch_bounds__(256) conv_depthwise_kernel(
                 for (int j = 0; j < 16; ++j) {
                     int xb = (int)((xw[j / 4] >> (8 * (j % 4))) & 0xff);
                     int wb = (int)(int8_t)((ww[j / 4] >> (8 * (j % 4))) & 0xff);
+                    if (WZP)
+                        wb -= g.wzp_d;   // 9 bits: fine in the 32-bit multiply
                     acc[j] += xb * wb;
                 }
             }
@@ -316,6 +335,83 @@ int conv_lower_rows_launch(const ConvGeom &g, const uint8_t *x, int n, uint8_t *
     return B200_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Window sums for the tensor-core path when wzp != 128 (see ConvGeom::wzp_d).  Two small passes:
+// the channel sum of every input pixel (one read of the activations), then the sum of those over
+// each output pixel's in-image taps, less izp for every byte summed.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) conv_channel_sum_kernel(
+    const uint8_t *__restrict__ x, int32_t *__restrict__ csum, size_t pixels, int c)
+{
+    // a quarter warp per pixel: 8 lanes stride over the pixel's 16-byte (or 4-byte, or single) pieces
+    const size_t pix = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+    const int sub = threadIdx.x & 7;
+    unsigned sum = 0;
+    if (pix < pixels) {
+        const uint8_t *px = x + pix * (size_t)c;
+        if ((c & 15) == 0 && (((uintptr_t)x) & 15) == 0) {
+            for (int i = sub; i < c / 16; i += 8) {
+                const uint4 q = __ldg(reinterpret_cast<const uint4 *>(px) + i);
+                sum = __dp4a(q.x, 0x01010101u, sum);
+                sum = __dp4a(q.y, 0x01010101u, sum);
+                sum = __dp4a(q.z, 0x01010101u, sum);
+                sum = __dp4a(q.w, 0x01010101u, sum);
+            }
+        } else if ((c & 3) == 0 && (((uintptr_t)x) & 3) == 0) {
+            for (int i = sub; i < c / 4; i += 8)
+                sum = __dp4a(__ldg(reinterpret_cast<const uint32_t *>(px) + i), 0x01010101u, sum);
+        } else {
+            for (int i = sub; i < c; i += 8)
+                sum += __ldg(px + i);
+        }
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+    if (pix < pixels && sub == 0)
+        csum[pix] = (int32_t)sum;
+}
+
+__global__ void __launch_bounds__(256) conv_window_sum_kernel(
+    ConvGeom g, const int32_t *__restrict__ csum, int32_t *__restrict__ wsum, size_t total)
+{
+    for (size_t pix = (size_t)blockIdx.x * blockDim.x + threadIdx.x; pix < total; pix += (size_t)gridDim.x * blockDim.x) {
+        const int ox = (int)(pix % g.ow);
+        const int oy = (int)((pix / g.ow) % g.oh);
+        const size_t img = pix / ((size_t)g.ow * g.oh);
+        const int iy0 = oy * g.stride_h - g.pad_h, ix0 = ox * g.stride_w - g.pad_w;
+        int sum = 0, taps = 0;
+        for (int rr = 0; rr < g.r; ++rr) {
+            const int iy = iy0 + rr;
+            if (iy < 0 || iy >= g.h)
+                continue;
+            for (int ss = 0; ss < g.s; ++ss) {
+                const int ix = ix0 + ss;
+                if (ix < 0 || ix >= g.w)
+                    continue;
+                sum += __ldg(csum + (img * g.h + iy) * g.w + ix);
+                ++taps;
+            }
+        }
+        wsum[pix] = sum - g.izp * g.c * taps;
+    }
+}
+
+int conv_window_sum_launch(const ConvGeom &g, const uint8_t *x, int n, int32_t *csum, int32_t *wsum, cudaStream_t st)
+{
+    if (n == 0)
+        return B200_OK;
+    const size_t in_pix = (size_t)n * g.h * g.w, out_pix = (size_t)n * g.oh * g.ow;
+    const size_t blocks = (in_pix * 8 + 255) / 256;
+    if (blocks > 0x7fffffffull)
+        return fail(B200_ERR_UNSUPPORTED, "conv(window sum): too many pixels");
+    conv_channel_sum_kernel<<<(unsigned)blocks, 256, 0, st>>>(x, csum, in_pix, g.c);
+    conv_window_sum_kernel<<<resident_grid<conv_window_sum_kernel, 256>((out_pix + 255) / 256), 256, 0, st>>>(
+        g, csum, wsum, out_pix);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
 int conv_direct_launch(
     const ConvGeom &g, const ConvDirectPlan &p, const uint8_t *x, int n, uint8_t *y, int32_t *acc_out,
     cudaStream_t st)
@@ -338,8 +434,10 @@ int conv_direct_launch(
         size_t blocks = (total + 255) / 256;
         size_t cap = (size_t)sm_count() * 8;
         int grid = (int)(blocks < cap ? blocks : cap);
-        conv_depthwise_kernel<<<grid, 256, 0, st>>>(
-            g, x, p.w_dw_dev, p.bias_fold_dev, p.mult_dev, p.shift_dev, y, n);
+        if (g.wzp_d != 0)
+            conv_depthwise_kernel<true><<<grid, 256, 0, st>>>(g, x, p.w_dw_dev, p.bias_fold_dev, p.mult_dev, p.shift_dev, y, n);
+        else
+            conv_depthwise_kernel<false><<<grid, 256, 0, st>>>(g, x, p.w_dw_dev, p.bias_fold_dev, p.mult_dev, p.shift_dev, y, n);
     } else {
         const int ktiles = (kg + DK - 1) / DK;
         size_t gx = (npix + DP - 1) / DP;

@@ -103,6 +103,10 @@ struct IgemmArgs {
     const uint8_t *res;
     int r_m[2], r_add[2], r_b[2];
     int r_s0, r_ozp, r_lo;
+    // weight zero point other than 128: acc -= wzp_d * wsum[pixel] before the requantize, wsum = window
+    // sums of (x - izp) per output pixel [n][oh][ow] (conv_window_sum_launch); nullptr: off
+    const int32_t *wsum;
+    int wzp_d;
 };
 
 // Tile index -> (Cout tile, ow tile, oh tile, image tile), Cout tile fastest.  A persistent CTA
@@ -453,7 +457,7 @@ __host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int 
 
 // HAS_RES: the instantiation whose epilogue can add a residual tensor; plans without a fused add run the
 // other one, which carries none of that code.
-template <bool HAS_RES>
+template <bool HAS_RES, bool HAS_WZP = false>
 __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const IgemmArgs g)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -724,6 +728,10 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             const uint8_t *res_row = g.res;
             if ((HAS_RES && g.res != nullptr) && pix_valid)
                 res_row += (((size_t)img * g.oh + oh) * g.ow + ow) * g.cout + k0;
+            // wzp != 128: this pixel's correction, the same for every channel
+            int wz_t = 0;
+            if (HAS_WZP && pix_valid)
+                wz_t = -g.wzp_d * __ldg(g.wsum + ((size_t)img * g.oh + oh) * g.ow + ow);
             const long long *off_row = g.off + k0;
             if (!single_class)
                 off_row += (size_t)((int)g.row_cls[min(oh, g.oh - 1)] * g.n_col_cls + (int)g.col_cls[min(ow, g.ow - 1)]) * g.kpad;
@@ -778,6 +786,17 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                         rv[4] = rb.x; rv[5] = rb.y; rv[6] = rb.z; rv[7] = rb.w;
                     }
                     tmem_ld_wait();
+                    if (HAS_WZP) {
+                        if (ncol == 32) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                v[i] += (uint32_t)wz_t;
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                v[i] += (uint32_t)wz_t;
+                        }
+                    }
                     // the common case is one straight-line block of 32 independent chains
                     if ((HAS_RES && g.res != nullptr)) {          // host guarantees the fast form and whole 32-column chunks
                         if (single_class)
@@ -1008,7 +1027,8 @@ int conv_igemm_create(
             if (b > max_bias)
                 max_bias = b;
         }
-        if (max_bias + (long long)g.r * g.s * g.c * 255ll * 128ll >= (1ll << 31))
+        const long long wmag = 128ll + (g.wzp_d < 0 ? -g.wzp_d : g.wzp_d);   // |s8| plus the zero-point correction
+        if (max_bias + (long long)g.r * g.s * g.c * 255ll * wmag >= (1ll << 31))
             return fail(B200_ERR_UNSUPPORTED, "conv(igemm): the int32 accumulator could wrap");
         for (int k = 0; k < g.k; ++k)
             if (shift[k] > 53)
@@ -1347,6 +1367,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     if (!p->attr_set) {
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+        B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
         p->attr_set = true;
     }
     p->last_x = x;
@@ -1358,10 +1379,14 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
 }
 
 int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cudaStream_t st, int *status_word,
-                      const uint8_t *res)
+                      const uint8_t *res, const int32_t *wsum)
 {
     if (n == 0)
         return B200_OK;
+    if ((p->g.wzp_d != 0) != (wsum != nullptr))
+        return fail(B200_ERR_INVALID, "conv(igemm): window sums are needed exactly when the weight zero point is not 128");
+    if (wsum != nullptr && res != nullptr)
+        return fail(B200_ERR_UNSUPPORTED, "conv(igemm): a fused residual add and a weight zero point other than 128 do not combine");
     if (res != nullptr && !p->has_res)
         return fail(B200_ERR_INVALID, "conv(igemm): a residual tensor was given but no residual add is set");
     if (res == nullptr && p->has_res)
@@ -1391,8 +1416,13 @@ int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cud
             }
         }
     }
+    // the window sums live in the caller's scratch, not in the launch cache's key: set them per launch
+    p->args.wsum = wsum;
+    p->args.wzp_d = p->g.wzp_d;
     if (res != nullptr)
         conv_igemm_i8_kernel<true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
+    else if (wsum != nullptr)
+        conv_igemm_i8_kernel<false, true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
     else
         conv_igemm_i8_kernel<false><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
     B200_CUDA_TRY(cudaGetLastError());

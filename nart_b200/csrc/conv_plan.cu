@@ -39,6 +39,7 @@ void destroy_conv(b200_conv *cv)
     if (cv->igemm)
         conv_igemm_destroy(cv->igemm);
     cudaFree(cv->scratch);
+    cudaFree(cv->sums);
     delete cv;
 }
 
@@ -63,10 +64,6 @@ int b200_conv2d_create(
         return fail(B200_ERR_INVALID, "conv: obits=%d outside 1..8", (int)p->obits);
     if (!p->walpha || (p->n_walpha != 1 && p->n_walpha != p->k))
         return fail(B200_ERR_INVALID, "conv: n_walpha must be 1 or k");
-    if (p->wzp != 128)
-        return fail(
-            B200_ERR_UNSUPPORTED,
-            "conv: wzp=%d; only int8 weights stored as value+128 with wzp=128 are built", (int)p->wzp);
     if (!(p->ialpha > 0.f) || !(p->oalpha > 0.f))
         return fail(B200_ERR_INVALID, "conv: ialpha and oalpha must be positive");
     if (p->algo != B200_CONV_ALGO_AUTO && p->algo != B200_CONV_ALGO_DIRECT && p->algo != B200_CONV_ALGO_IGEMM)
@@ -81,6 +78,7 @@ int b200_conv2d_create(
     g.ow = (p->w + 2 * p->pad_w - p->s) / p->stride_w + 1;
     g.izp = p->izp; g.ozp = p->ozp; g.qmax = (1 << p->obits) - 1;
     g.relu_lo = p->relu ? p->ozp : 0;
+    g.wzp_d = (int)p->wzp - 128;
     cv->oalpha = p->oalpha;
     cudaGetDevice(&cv->device);
 
@@ -88,6 +86,8 @@ int b200_conv2d_create(
     const size_t wcount = (size_t)g.k * cg * taps;
     // int32 accumulation wraps modulo 2^32 in every order, like the reference's int32 GEMM
     // (gemm/default/gemm.c:306-355), so no bound on the reduction length is needed.
+    // Any stored byte minus 128 is an int8; a weight zero point other than 128 is carried as
+    // wzp_d = wzp - 128 and applied through the sum of the activations (ConvGeom::wzp_d).
     std::vector<int8_t> w_s8(wcount);   // [k][cg][r][s], value = stored - 128
     for (size_t i = 0; i < wcount; ++i)
         w_s8[i] = (int8_t)((int)weights[i] - 128);
@@ -140,7 +140,7 @@ int b200_conv2d_create(
                 w_dw[(size_t)t * g.c + c] = w_s8[(size_t)c * taps + t];
         rc = upload(w_dw, &cv->direct.w_dw_dev);
         // the dp4a form of the 3x3 case (conv_depthwise3x3_kernel)
-        bool fast = g.r == 3 && g.s == 3 && g.qmax == 255;
+        bool fast = g.r == 3 && g.s == 3 && g.qmax == 255 && g.wzp_d == 0;
         for (int k = 0; k < g.k && fast; ++k)
             fast = shift[k] >= 33 && shift[k] <= 53;
         if (rc == B200_OK && fast) {
@@ -255,23 +255,46 @@ int b200_conv2d_run(b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, 
         return B200_OK;
     if (conv->fused_residual)
         return fail(B200_ERR_INVALID, "conv: this plan has a residual add, run it with b200_conv2d_run_residual");
+    B200_TRY(b200_conv2d_reserve(conv, n));   // grow-only scratch: the first call at a larger batch allocates (and synchronizes)
+    const ConvGeom &g = conv->g;
+    const int32_t *wsum = nullptr;
+    if (conv->algo == B200_CONV_ALGO_IGEMM && g.wzp_d != 0) {
+        int32_t *w = conv->sums + conv->sums_images * g.h * g.w;
+        B200_TRY(conv_window_sum_launch(g, x, n, conv->sums, w, as_stream(stream)));
+        wsum = w;
+    }
     if (conv->lowered) {
-        const ConvGeom &g = conv->g;
+        B200_TRY(conv_lower_rows_launch(g, x, n, conv->scratch, as_stream(stream)));
+        return conv_igemm_launch(conv->igemm, conv->scratch, n, y, as_stream(stream), nullptr, nullptr, wsum);
+    }
+    if (conv->algo == B200_CONV_ALGO_IGEMM)
+        return conv_igemm_launch(conv->igemm, x, n, y, as_stream(stream), nullptr, nullptr, wsum);
+    return conv_direct_launch(conv->g, conv->direct, x, n, y, nullptr, as_stream(stream));
+}
+
+int b200_conv2d_reserve(b200_conv_t *conv, int32_t n)
+{
+    if (!conv || n < 0)
+        return fail(B200_ERR_INVALID, "conv(reserve): bad argument");
+    const ConvGeom &g = conv->g;
+    if (conv->lowered) {
         const size_t need = (size_t)n * g.h * g.ow * (kLowerWindow * 4);
         if (need > conv->scratch_bytes) {
-            // grow-only scratch; the first call at a given batch size allocates (and synchronizes)
             B200_CUDA_TRY(cudaFree(conv->scratch));
             conv->scratch = nullptr;
             conv->scratch_bytes = 0;
             B200_TRY(b200_malloc((void **)&conv->scratch, need));
             conv->scratch_bytes = need;
         }
-        B200_TRY(conv_lower_rows_launch(g, x, n, conv->scratch, as_stream(stream)));
-        return conv_igemm_launch(conv->igemm, conv->scratch, n, y, as_stream(stream));
     }
-    if (conv->algo == B200_CONV_ALGO_IGEMM)
-        return conv_igemm_launch(conv->igemm, x, n, y, as_stream(stream));
-    return conv_direct_launch(conv->g, conv->direct, x, n, y, nullptr, as_stream(stream));
+    if (conv->algo == B200_CONV_ALGO_IGEMM && g.wzp_d != 0 && (size_t)n > conv->sums_images) {
+        B200_CUDA_TRY(cudaFree(conv->sums));
+        conv->sums = nullptr;
+        conv->sums_images = 0;
+        B200_TRY(b200_malloc((void **)&conv->sums, (size_t)n * ((size_t)g.h * g.w + (size_t)g.oh * g.ow) * sizeof(int32_t)));
+        conv->sums_images = (size_t)n;
+    }
+    return B200_OK;
 }
 
 int b200_conv2d_fuse_residual_add(
@@ -282,6 +305,8 @@ int b200_conv2d_fuse_residual_add(
         return fail(B200_ERR_INVALID, "conv(fuse): bad argument");
     if (conv->algo != B200_CONV_ALGO_IGEMM || conv->lowered || !conv->igemm)
         return fail(B200_ERR_UNSUPPORTED, "conv(fuse): only plans on the tensor-core path take a residual add");
+    if (conv->g.wzp_d != 0)
+        return fail(B200_ERR_UNSUPPORTED, "conv(fuse): a weight zero point other than 128 and a fused residual add do not combine");
     if (conv->fused_residual)
         return fail(B200_ERR_INVALID, "conv(fuse): the plan already has a residual add");
     if (izp[conv_input] != (uint8_t)conv->g.ozp || ialpha[conv_input] != conv->oalpha)

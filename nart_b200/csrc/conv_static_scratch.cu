@@ -57,6 +57,10 @@ extern "C" int b200_conv2d_run_static_scratch(
             B200_ERR_INVALID,
             "conv(static scratch): this plan uses no scratch tensor (only row-lowered 4-channel convs do); "
             "use b200_conv2d_run");
+    if (conv->g.wzp_d != 0)
+        return fail(
+            B200_ERR_UNSUPPORTED,
+            "conv(static scratch): a weight zero point other than 128 needs the window-sum tensors of b200_conv2d_run");
     if (n == 0)
         return B200_OK;
     const ConvGeom &g = conv->g;

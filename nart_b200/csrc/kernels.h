@@ -63,6 +63,11 @@ struct ConvGeom {
     int pad_h, pad_w, stride_h, stride_w, group;
     int oh, ow;
     int izp, ozp, qmax, relu_lo;
+    // Weight zero point minus 128.  The kernels multiply by s8 = stored weight - 128; for wzp != 128
+    //   sum (x - izp) * (w - wzp) = sum (x - izp) * s8  -  wzp_d * sum_valid (x - izp),
+    // and the second sum (over the window's in-image taps and the group's channels) is formed beside
+    // the products (CUDA-core kernels) or read from a window-sum tensor (tensor-core kernel).
+    int wzp_d;
 };
 
 // Direct (CUDA-core) convolution: weights [k][r][s][cg4] int8 (cg4 = c/group rounded up to 4,
@@ -93,6 +98,10 @@ int conv_direct_launch(
 constexpr int kLowerWindow = 8;
 int conv_lower_rows_launch(const ConvGeom &g, const uint8_t *x, int n, uint8_t *out, cudaStream_t st);
 
+// Window sums for a weight zero point other than 128 (group == 1): csum[n][h][w] = sum_c x, then
+// wsum[n][oh][ow] = sum over the window's in-image taps of (csum - izp * c).  Both int32.
+int conv_window_sum_launch(const ConvGeom &g, const uint8_t *x, int n, int32_t *csum, int32_t *wsum, cudaStream_t st);
+
 // Implicit-GEMM (tcgen05) convolution plan; defined in conv_igemm_sm100.cu.
 struct ConvIgemmPlan;
 int conv_igemm_supported(const ConvGeom &g, char *why, size_t why_len);
@@ -104,8 +113,9 @@ int conv_igemm_create(
 // status_word: device int that a bounded wait writes its code into; nullptr = the per-device word
 // that b200_device_status reads.
 // res: the second input of a fused residual add (conv_igemm_set_residual), else nullptr.
+// wsum: the window sums of conv_window_sum_launch when the plan's geometry has wzp_d != 0, else nullptr.
 int conv_igemm_launch(ConvIgemmPlan *plan, const uint8_t *x, int n, uint8_t *y, cudaStream_t st,
-                      int *status_word = nullptr, const uint8_t *res = nullptr);
+                      int *status_word = nullptr, const uint8_t *res = nullptr, const int32_t *wsum = nullptr);
 // Fuses y = eltwise_sum(conv(x), res) into the epilogue: `e` holds the eltwise constants and
 // conv_input says which of its two inputs is this conv's output.  B200_ERR_UNSUPPORTED when the
 // plan's epilogue form cannot take it (the caller then keeps the separate eltwise kernel).
@@ -127,6 +137,8 @@ struct b200_conv {
     b200::ConvGeom g_low;
     uint8_t *scratch = nullptr;     // [n][h][ow][32]
     size_t scratch_bytes = 0;
+    int32_t *sums = nullptr;        // wzp != 128 on the tensor-core path: [n][h][w] channel sums, then [n][oh][ow] window sums
+    size_t sums_images = 0;         // images the two tensors hold
     float oalpha = 0.f;             // output scale, kept for b200_conv2d_fuse_residual_add
     bool fused_residual = false;    // the plan computes eltwise_sum(conv(x), res)
 };

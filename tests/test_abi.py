@@ -57,7 +57,7 @@ def test_conv_create_refuses_cleanly(L):
     wa = (C.c_float * 1)(0.005)
     w = np.full((16, 16, 3, 3), 128, np.uint8)
     h = C.c_void_p()
-    for kw, status in ((dict(wzp=100), L.ERR_UNSUPPORTED), (dict(group=3), L.ERR_INVALID),
+    for kw, status in ((dict(ialpha=1e-12), L.ERR_UNSUPPORTED), (dict(group=3), L.ERR_INVALID),
                        (dict(obits=9), L.ERR_INVALID), (dict(n_walpha=5), L.ERR_INVALID),
                        (dict(oalpha=0.0), L.ERR_INVALID), (dict(stride_h=0), L.ERR_INVALID),
                        (dict(algo=7), L.ERR_INVALID)):

@@ -54,6 +54,28 @@ def test_plugin_fused_relu_flag(ref):
     assert_same(y, GOLD["c0_zp_relu"], "plugin conv + relu flag")
 
 
+def test_plugin_conv_asymmetric_weights(ref):
+    """Weight zero points other than 128, as the reference's calibrator writes them by default: the
+    plugin gives the bytes of the reference's own CPU module, run live on the same inputs."""
+    if not os.path.exists(PLUGIN):
+        pytest.skip("plugin not built")
+    rng = np.random.default_rng(21)
+    for wzp, (c, k, ks, st, pd, g, h, w) in ((77, (64, 32, 3, 1, 1, 1, 9, 10)), (201, (32, 64, 1, 2, 0, 1, 8, 8)),
+                                             (5, (12, 8, 3, 1, 1, 2, 7, 7)), (140, (4, 32, 7, 2, 3, 1, 20, 20))):
+        x = rng.integers(0, 256, (2, c, h, w), dtype=np.uint8)
+        wt = rng.integers(0, 256, (k, c // g, ks, ks), dtype=np.uint8)
+        bias = rng.integers(-4096, 4097, k).astype(np.int32)
+        q = (0.03, 128, 0.004, wzp, 0.03 * 0.004 * 74 * 74 * np.sqrt(c // g * ks * ks) / 40, 120)
+        want = ref.conv2d_u8(x, wt, bias, (st, st), (pd, pd), g, *q)
+        assert len(np.unique(want)) > 16
+        ref.use_module(PLUGIN, "b200_module_tp", whole_batch=True)
+        try:
+            got = ref.conv2d_u8(x, wt, bias, (st, st), (pd, pd), g, *q)
+        finally:
+            ref.use_module()
+        assert_same(got, want, "plugin wzp=%d" % wzp)
+
+
 def test_plugin_other_ops(plugin):
     rng = np.random.default_rng(7)
     a = rng.integers(0, 256, (2, 32, 14, 14), dtype=np.uint8)

@@ -123,6 +123,15 @@ def test_ip(ops, port):
     want = port.ip_u8(x, w2, None, 0.05, 7, [0.004], 128, 0.5, 9)
     ip2 = ops.InnerProduct(w2, None, in_chw=(16, 3, 3), ialpha=0.05, izp=7, walpha=0.004, oalpha=0.5, ozp=9)
     assert_same(ip2(to_dev_nhwc(x)).cpu().numpy().reshape(3, 24), want, "ip 3x3")
+    # asymmetric weights (any byte, zero point other than 128): 1x1 and spatial inputs
+    for wzp, shape in ((90, (5, 64, 1, 1)), (201, (3, 16, 3, 3))):
+        x = rng.integers(0, 256, shape, dtype=np.uint8)
+        w3 = rng.integers(0, 256, (40, int(np.prod(shape[1:]))), dtype=np.uint8)
+        b3 = rng.integers(-4096, 4097, 40).astype(np.int32)
+        want = port.ip_u8(x, w3, b3, 0.05, 131, [0.004], wzp, 0.3, 120)
+        assert len(np.unique(want)) > 16
+        ip3 = ops.InnerProduct(w3, b3, in_chw=shape[1:], ialpha=0.05, izp=131, walpha=0.004, wzp=wzp, oalpha=0.3, ozp=120)
+        assert_same(ip3(to_dev_nhwc(x)).cpu().numpy().reshape(shape[0], 40), want, "ip wzp=%d" % wzp)
 
 
 def test_layout_roundtrip(ops):
@@ -255,6 +264,42 @@ def test_conv_requantize_variants_on_both_paths(ops, port, k):
             for algo in (ops.ALGO_DIRECT, ops.ALGO_IGEMM):
                 got = run_conv(ops, x, wt, bias, 1, 1, 1, algo, walpha=walpha, relu=relu, **q)
                 assert_same(got, want, "k=%d oalpha=%g obits=%d relu=%s algo=%d" % (k, oalpha, obits, relu, algo))
+
+
+# (c, k, kernel, stride, pad, group, h, w, algo name): every kernel that forms products
+WZP_SHAPES = [(64, 64, 3, 1, 1, 1, 13, 11, "igemm"), (32, 48, 1, 1, 0, 1, 9, 9, "igemm"), (128, 32, 3, 2, 1, 1, 12, 12, "igemm"),
+              (256, 272, 1, 1, 0, 1, 7, 7, "igemm"), (4, 64, 7, 2, 3, 1, 30, 34, "igemm"), (64, 64, 3, 1, 1, 1, 13, 11, "direct"),
+              (12, 10, 3, 1, 1, 2, 8, 9, "direct"), (7, 5, 2, 1, 0, 1, 6, 6, "direct"), (32, 32, 3, 1, 1, 32, 10, 10, "direct"),
+              (16, 16, 5, 2, 2, 16, 11, 9, "direct")]
+
+
+@pytest.mark.parametrize("shape", WZP_SHAPES)
+@pytest.mark.parametrize("wzp", [0, 77, 131, 255])
+def test_conv_weight_zero_point(ops, port, shape, wzp):
+    """Asymmetric weights: any stored byte, any zero point.  The kernels multiply by (stored - 128) and
+    take (wzp - 128) times the window sum of the activations off the accumulator."""
+    c, k, ks, st, pd, g, h, w, algo_name = shape
+    rng = np.random.default_rng(1000 + c + k + wzp)
+    n = 3
+    x = rng.integers(0, 256, (n, c, h, w), dtype=np.uint8)
+    wt = rng.integers(0, 256, (k, c // g, ks, ks), dtype=np.uint8)
+    walpha = rng.uniform(0.001, 0.01, k).astype(np.float32)
+    izp = int(rng.integers(0, 256))
+    # weights with a non-zero mean push the accumulators far from 0: the bias centres every channel,
+    # and the output scale comes from the accumulators' spread, so that the bytes use the range
+    zero = np.zeros(k, np.int32)
+    _, acc = port.conv2d_u8(x, wt, zero, (st, st), (pd, pd), g, 0.03, izp, walpha, wzp, 1.0, 0, return_acc=True)
+    bias = (-acc.astype(np.float64).mean(axis=(0, 2, 3))).round().astype(np.int32) + rng.integers(-4096, 4097, k).astype(np.int32)
+    real = (acc + bias[None, :, None, None]).astype(np.float64) * 0.03 * walpha.astype(np.float64)[None, :, None, None]
+    oalpha = float(np.float32(real.std() / 45.0))
+    ozp = int(rng.integers(100, 156))
+    q = dict(ialpha=0.03, izp=izp, wzp=wzp, oalpha=oalpha, ozp=ozp, walpha=walpha)
+    want = port.conv2d_u8(x, wt, bias, (st, st), (pd, pd), g, q["ialpha"], q["izp"], walpha, wzp, q["oalpha"], q["ozp"],
+                          relu=bool(wzp & 1))
+    algo = ops.ALGO_IGEMM if algo_name == "igemm" else ops.ALGO_DIRECT
+    got = run_conv(ops, x, wt, bias, st, pd, g, algo, relu=bool(wzp & 1), **q)
+    assert_same(got, want, "wzp=%d %s" % (wzp, shape))
+    assert len(np.unique(want)) > 16
 
 
 @pytest.mark.parametrize("c,k,ks,st,hw", [(16, 96, 1, 1, 14), (48, 32, 3, 1, 9), (80, 48, 3, 2, 12), (144, 24, 1, 1, 7),

@@ -14,9 +14,9 @@ pytestmark = pytest.mark.gpu
 def test_float_net_through_max_min_to_gpu_case():
     from nart_b200.case import Case
     rng = np.random.default_rng(5)
-    w1 = rng.normal(0, 0.08, (32, 16, 3, 3)).astype(np.float32)
+    w1 = (rng.normal(0, 0.08, (32, 16, 3, 3)) + 0.05).astype(np.float32)     # off-centre: asymmetric ranges
     b1 = rng.normal(0, 0.1, 32).astype(np.float32)
-    w2 = rng.normal(0, 0.12, (16, 32, 1, 1)).astype(np.float32)
+    w2 = (rng.normal(0, 0.12, (16, 32, 1, 1)) - 0.04).astype(np.float32)
     b2 = rng.normal(0, 0.1, 16).astype(np.float32)
 
     def forward(x):
@@ -32,35 +32,26 @@ def test_float_net_through_max_min_to_gpu_case():
         for k, a in acts.items():
             ext[k]["max"].append(float(a.max()))
             ext[k]["min"].append(float(a.min()))
-    # symmetric weights: stored as value + 128 with zero point 128 (to_biased), the form the GPU path
-    # takes; activations keep their own zero points
-    param = qp.weight_entries({"conv1": w1, "conv2": w2}, symmetric=True)
+    # the calibrator's defaults: biased (asymmetric) weights and activations, each with its own zero point
+    param = qp.weight_entries({"conv1": w1, "conv2": w2})
     param.update(qp.activation_entries(ext))
     param.update(qp.bias_entries([("conv1", "data"), ("conv2", "conv1")], param))
     q = qp.convert_quant_param(param, zero_point_quotient=True)
-    for k in ("data", "conv1", "conv2"):
+    for k in ("data", "conv1", "conv2", "conv1_weight_0", "conv2_weight_0"):
         assert q[k].qtype == qp.BIASED and 0 <= q[k].zero_point <= 255 and q[k].alpha > 0
-    for k in ("conv1_weight_0", "conv2_weight_0"):
-        assert q[k].qtype == qp.SYMMETRIC and q[k].to_biased().zero_point == 128
-    # the calibrator's bias step takes 2^bit - 1 levels for both factors: it equals walpha * ialpha only
-    # up to the 127-vs-127.5 difference of the symmetric weight step
-    assert q["conv1_weight_1"].alpha == pytest.approx(q["conv1_weight_0"].alpha * q["data"].alpha, rel=0.01)
-
-    def stored(w, qw):        # symmetric int8 -> uint8 with zero point 128
-        return (qp.quantize_weight(w, qw).astype(np.int16) + 128).astype(np.uint8)
-
-    def bias_q(b, walpha, ialpha):   # the accumulator's own step, whatever the calibrator's estimate of it
-        return qp.quantize_weight(b, qp.QuantParam(walpha * ialpha, 0, 32, qp.SYMMETRIC))
+    assert q["conv1_weight_0"].zero_point != 128 and q["conv2_weight_0"].zero_point != 128
+    # the bias step of the hand-off is the product of the two step sizes it is added between
+    assert q["conv1_weight_1"].alpha == pytest.approx(q["conv1_weight_0"].alpha * q["data"].alpha, rel=1e-6)
 
     cs = Case()
     t0 = cs.input_f32(16, 12, 12, q["data"].alpha, q["data"].zero_point)
     qw1, qw2 = q["conv1_weight_0"], q["conv2_weight_0"]
-    t1 = cs.conv2d(t0, stored(w1, qw1), bias_q(b1, qw1.alpha, q["data"].alpha),
+    t1 = cs.conv2d(t0, qp.quantize_weight(w1, qw1), qp.quantize_weight(b1, q["conv1_weight_1"]),
                    pad=(1, 1), ialpha=q["data"].alpha, izp=q["data"].zero_point, walpha=qw1.alpha,
-                   wzp=qw1.to_biased().zero_point, oalpha=q["conv1"].alpha, ozp=q["conv1"].zero_point, relu=True)
-    t2 = cs.conv2d(t1, stored(w2, qw2), bias_q(b2, qw2.alpha, q["conv1"].alpha),
+                   wzp=qw1.zero_point, oalpha=q["conv1"].alpha, ozp=q["conv1"].zero_point, relu=True)
+    t2 = cs.conv2d(t1, qp.quantize_weight(w2, qw2), qp.quantize_weight(b2, q["conv2_weight_1"]),
                    ialpha=q["conv1"].alpha, izp=q["conv1"].zero_point, walpha=qw2.alpha,
-                   wzp=qw2.to_biased().zero_point, oalpha=q["conv2"].alpha, ozp=q["conv2"].zero_point)
+                   wzp=qw2.zero_point, oalpha=q["conv2"].alpha, ozp=q["conv2"].zero_point)
     cs.output_f32(t2, q["conv2"].alpha, q["conv2"].zero_point)
     cs.prepare(8)
 

@@ -119,6 +119,26 @@ def test_live_reference_random_convs(port, ref):
         assert np.array_equal(yr, yp), (t, c, k, h, w, r, s, st, pd, g)
 
 
+def test_live_reference_weight_zero_points(port, ref):
+    """Weight zero points other than 128 (asymmetric weights, any stored byte): port == reference."""
+    rng = np.random.default_rng(43)
+    for t, wzp in enumerate((0, 3, 77, 127, 131, 200, 255)):
+        g = (1, 1, 2, 1, 4, 1, 1)[t]
+        c, k = g * 6, g * 5
+        h, w = int(rng.integers(4, 12)), int(rng.integers(4, 12))
+        r, s = int(rng.integers(1, 4)), int(rng.integers(1, 4))
+        st, pd = int(rng.integers(1, 3)), int(rng.integers(0, 2))
+        x = rng.integers(0, 256, (2, c, h, w), dtype=np.uint8)
+        wt = rng.integers(0, 256, (k, c // g, r, s), dtype=np.uint8)
+        bias = rng.integers(-4096, 4097, k).astype(np.int32)
+        q = dict(ialpha=float(rng.uniform(0.01, 0.1)), izp=int(rng.integers(0, 256)), wzp=wzp,
+                 oalpha=float(rng.uniform(0.05, 2.0)), ozp=int(rng.integers(0, 256)))
+        yr = ref.conv2d_u8(x, wt, bias, (st, st), (pd, pd), g, walpha=0.004, **q)
+        yp = port.conv2d_u8(x, wt, bias, (st, st), (pd, pd), g, walpha=np.float32([0.004]), **q)
+        assert np.array_equal(yr, yp), (t, wzp, c, k, h, w, r, s, st, pd, g)
+        assert len(np.unique(yp)) > 8
+
+
 def test_live_reference_eltwise_all_byte_pairs(port, ref):
     # every (a, b) byte pair once: 65536 elements
     a = np.repeat(np.arange(256, dtype=np.uint8), 256).reshape(1, 256, 16, 16)
