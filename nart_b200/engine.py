@@ -349,10 +349,12 @@ def read_engine(path):
 
 
 # ---- builder: a read file on the GPU case runner ---------------------------------------------------
-def engine_to_case(model, max_batch, algo=0, fuse=False):
+def engine_to_case(model, max_batch, algo=0, fuse=False, input_chw=None):
     """Builds and prepares a ``Case`` from ``read_engine`` output.  Supported: one uint8 (or float32 +
     quantize) NCHW input; conv_2d, ip, pool, eltwise SUM, add, relu; outputs uint8 or dequantized
-    float32.  Returns (case, list of (is_float32, per-image shape) per output)."""
+    float32.  ``input_chw`` replaces the input's recorded (C, H, W) -- the reshape the reference applies
+    with parade_apply_reshape (art/src/parade.c:199-215); every later shape follows from the ops.
+    Returns (case, list of (is_float32, per-image shape) per output)."""
     from .case import Case
     if len(model["inputs"]) != 1:
         raise ValueError("engine_to_case: exactly one input is supported")
@@ -360,6 +362,8 @@ def engine_to_case(model, max_batch, algo=0, fuse=False):
     cs.set_fusion(fuse)
     inp = model["inputs"][0]
     _, c, h, w = inp["dims"]
+    if input_chw is not None:
+        c, h, w = (int(v) for v in input_chw)
     ids, quant = {}, {}            # file tensor index -> case tensor id / (alpha, zp) where known
     pending_f32 = inp["dtype"] == DT_FLOAT32
     if not pending_f32:

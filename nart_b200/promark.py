@@ -1,11 +1,13 @@
 """Times a serialized case on the GPU case runner, with the options and the report of the
 reference's benchmark driver (tools/promark.cpp:208-522 of ModelTC/NART):
 
-    python -m nart_b200.promark -m engine.bin [-n runs] [-b batch] [-i input.bin ...] [-s] [-d] [-y]
+    python -m nart_b200.promark -m engine.bin [-n runs] [-b batch] [-r name:n,c,h,w] [-i input.bin ...] [-s] [-d] [-y]
 
   -m  the case file (format version 2)
   -n  timed runs (default 10), after one warm-up run
   -b  batch size (default: the batch recorded in the file)
+  -r  reshape the named input to n,c,h,w before the case is prepared (the reference's
+      parade_apply_reshape path); n sets the batch unless -b is given
   -i  raw input file in the input's dtype and NCHW shape, one per model input
   -s  save the outputs as nart-out-<name>.bin (raw, NCHW)
   -d  fresh random input data before every run
@@ -30,6 +32,7 @@ def main(argv=None):
     ap.add_argument("-m", dest="model", required=True)
     ap.add_argument("-n", dest="runs", type=int, default=10)
     ap.add_argument("-b", dest="batch", type=int, default=-1)
+    ap.add_argument("-r", dest="reshape", action="append", default=[])
     ap.add_argument("-i", dest="inputs", action="append", default=[])
     ap.add_argument("-s", dest="save", action="store_true")
     ap.add_argument("-d", dest="random", action="store_true")
@@ -43,9 +46,21 @@ def main(argv=None):
     model = engine.read_engine(a.model)
     inp = model["inputs"][0]
     batch = a.batch if a.batch > 0 else int(inp["dims"][0])
-    cs, outs = engine.engine_to_case(model, batch, fuse=a.fuse)
+    chw = tuple(int(d) for d in inp["dims"][1:])
+    for spec in a.reshape:
+        name, _, dims = spec.partition(":")
+        if name != inp["name"]:
+            print("warning: -r %s names no input of the model" % name, file=sys.stderr)
+            continue
+        shape = [int(d) for d in dims.split(",")]
+        if len(shape) != 4:
+            ap.error("-r takes name:n,c,h,w")
+        chw = tuple(shape[1:])
+        if a.batch <= 0:
+            batch = shape[0]
+    cs, outs = engine.engine_to_case(model, batch, fuse=a.fuse, input_chw=chw)
     in_dtype = np.float32 if inp["dtype"] == engine.DT_FLOAT32 else np.uint8
-    in_shape = (batch,) + tuple(inp["dims"][1:])
+    in_shape = (batch,) + chw
     print("input tensors:")
     print("\t%s: %s" % (inp["name"], ", ".join(str(d) for d in in_shape)))
     print("output tensors:")

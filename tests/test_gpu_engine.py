@@ -63,3 +63,31 @@ def test_promark_cli(port, tmp_path, monkeypatch, capsys):
     want, _, _ = nets.run_cpu(spec, x, port)
     assert_same(got.view(np.uint32), want.reshape(-1).view(np.uint32), "promark -s")
     assert promark.main(["-m", path, "-n", "2", "-b", "4", "-d"]) == 0      # device-resident timing, other batch
+
+
+def test_promark_reshape(port, tmp_path, monkeypatch, capsys):
+    """-r name:n,c,h,w: the recorded input shape is replaced before the case is prepared and every later
+    shape follows (what parade_apply_reshape does in the reference's driver)."""
+    from nart_b200 import engine, nets, promark
+
+    def build(h, w):
+        b = nets.SpecBuilder(77, (3, h, w), True)
+        t = b.conv("input", 32, 3, 2, 1)
+        t = b.conv(t, 48, 3, 1, 1)
+        t = b.pool(t, nets.POOL_MAX, 2, 2, 0)
+        return b.finish("reshape-net", t)
+
+    small, large = build(16, 16), build(24, 20)
+    path = os.path.join(tmp_path, "engine.bin")
+    engine.write_engine(small, path, batch=2)
+    name = engine.read_engine(path)["inputs"][0]["name"]
+    x = np.random.default_rng(9).integers(0, 256, (3, 3, 24, 20), dtype=np.uint8)
+    x.tofile(os.path.join(tmp_path, "in.bin"))
+    monkeypatch.chdir(tmp_path)
+    assert promark.main(["-m", path, "-n", "1", "-r", "%s:3,3,24,20" % name, "-s", "-i", "in.bin"]) == 0
+    assert "%s: 3, 3, 24, 20" % name in capsys.readouterr().out
+    want, _, _ = nets.run_cpu(large, x, port)          # the file's output is the dequantized last tensor
+    out_name = engine.read_engine(path)["outputs"][0]["name"].replace("/", "_")
+    got = np.fromfile(os.path.join(tmp_path, "nart-out-%s.bin" % out_name), dtype=np.float32)
+    assert got.size == want.size == 3 * 48 * 6 * 5
+    assert_same(got.view(np.uint32), want.reshape(-1).view(np.uint32), "promark -r")
