@@ -32,6 +32,7 @@ void destroy_conv(b200_conv *cv)
     cudaFree(cv->direct.w_dev);
     cudaFree(cv->direct.w_dw_dev);
     cudaFree(cv->direct.w_dw3_dev);
+    cudaFree(cv->direct.w_dw3p_dev);
     cudaFree(cv->direct.q_dw3_dev);
     cudaFree(cv->direct.bias_fold_dev);
     cudaFree(cv->direct.mult_dev);
@@ -163,6 +164,18 @@ int b200_conv2d_create(
             }
             rc = upload(w3, &cv->direct.w_dw3_dev);
             if (rc == B200_OK) rc = upload(q3, &cv->direct.q_dw3_dev);
+            if (rc == B200_OK && g.stride_w == 1) {
+                std::vector<uint32_t> w3p((size_t)(g.c / 4) * 3 * 2 * 4, 0);
+                for (int c = 0; c < g.c; ++c)
+                    for (int rr = 0; rr < 3; ++rr) {
+                        uint32_t word = 0;
+                        for (int j = 0; j < 3; ++j)
+                            word |= (uint32_t)(uint8_t)w_s8[(size_t)c * 9 + rr * 3 + j] << (8 * j);
+                        w3p[(((size_t)(c / 4) * 3 + rr) * 2 + 0) * 4 + (c % 4)] = word;        // left pixel: inputs 0..2
+                        w3p[(((size_t)(c / 4) * 3 + rr) * 2 + 1) * 4 + (c % 4)] = word << 8;   // right pixel: inputs 1..3
+                    }
+                rc = upload(w3p, &cv->direct.w_dw3p_dev);
+            }
         }
     }
     if (rc != B200_OK) {

@@ -81,6 +81,9 @@ struct ConvDirectPlan {
     // {folded 64-bit addend, mult, shift - 32}
     uint32_t *w_dw3_dev = nullptr;
     int4 *q_dw3_dev = nullptr;
+    // the same for two output pixels side by side (stride_w == 1): [c/4][3 rows][2 pixels][4 channels]
+    // words (w0, w1, w2, 0) and (0, w0, w1, w2) of one kernel row, against four neighbouring input pixels
+    uint32_t *w_dw3p_dev = nullptr;
     int32_t *bias_fold_dev = nullptr;
     uint32_t *mult_dev = nullptr;
     int32_t *shift_dev = nullptr;
