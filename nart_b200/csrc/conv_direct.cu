@@ -292,73 +292,118 @@ __global__ void __launch_bounds__(256) conv_depthwise3x3_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------
-// Depthwise 3x3 with stride_w == 1, two output pixels side by side per thread.  The two windows
-// cover four neighbouring input pixels per kernel row; one transpose of those four words gives, per
-// channel, a word (x0, x1, x2, x3) that serves both pixels: dp4a against (w0, w1, w2, 0) is the
-// left pixel's row, against (0, w0, w1, w2) the right one's.  Per pair: 12 activation loads
-// instead of 18, 3 transposes instead of 4 plus byte extractions, and one read of the per-channel
-// requantize constants for both pixels.  Arithmetic and results equal conv_depthwise3x3_kernel.
+// Depthwise 3x3 with horizontal stride S (1 or 2): a thread computes two output pixels side by
+// side, in ROWS (1 or 2) output rows.  The two windows of a row cover 3 + S neighbouring input
+// pixels per kernel row.  One transpose of the first four of those words gives, per channel, a
+// word (x0, x1, x2, x3) that serves both pixels: dp4a against (w0, w1, w2, 0) is the left pixel's
+// kernel row; the right pixel's is (0, w0, w1, w2) for S == 1, and for S == 2 (0, 0, w0, w1) plus
+// the fifth word against w2 placed at the channel's own byte (no extraction).  With ROWS == 2 (the
+// vertical stride is S as well) the output rows share 3 - S of their input rows.  The per-channel
+// weights and requantize constants are read once per thread.  Arithmetic and results equal
+// conv_depthwise3x3_kernel.  Weight table: [c/4][3 kernel rows][2 + (S == 2)][4 channels] words.
 // ---------------------------------------------------------------------------------------------
+template <int ROWS, int S>
 __global__ void __launch_bounds__(256) conv_depthwise3x3_pair_kernel(
     ConvGeom g, const uint32_t *__restrict__ x, const uint4 *__restrict__ w3p, const int4 *__restrict__ q3,
     uint32_t *__restrict__ y, int n)
 {
+    constexpr int IN_ROWS = 3 + (ROWS - 1) * S, IN_COLS = 3 + S, NV = S == 2 ? 3 : 2;
     const uint32_t cq = (uint32_t)g.c / 4;
-    const uint32_t owp = ((uint32_t)g.ow + 1) / 2;
-    const uint32_t total = (uint32_t)n * g.oh * owp * cq;      // the launcher checks that it fits 32 bits
+    const uint32_t owp = ((uint32_t)g.ow + 1) / 2, ohp = ((uint32_t)g.oh + ROWS - 1) / ROWS;
+    const uint32_t total = (uint32_t)n * ohp * owp * cq;      // the launcher checks that it fits 32 bits
     const uint32_t izp4 = (uint32_t)g.izp * 0x01010101u;
     for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
         const uint32_t ci = idx % cq;
         const uint32_t pp = idx / cq;
         const int ox = (int)(pp % owp) * 2;
         const uint32_t rowi = pp / owp;
-        const int oy = (int)(rowi % (uint32_t)g.oh);
-        const uint32_t img = rowi / (uint32_t)g.oh;
-        const int iy0 = oy * g.stride_h - g.pad_h, ix0 = ox - g.pad_w;
+        const int oy = (int)(rowi % ohp) * ROWS;
+        const uint32_t img = rowi / ohp;
+        const int iy0 = oy * g.stride_h - g.pad_h, ix0 = ox * S - g.pad_w;   // ROWS == 2 only with stride_h == S
         const uint32_t row_pitch = (uint32_t)g.w * cq;
         const uint32_t *xc = x + (img * (uint32_t)g.h * row_pitch + ci);
-        uint32_t t[3][4];
-        if (iy0 >= 0 && iy0 + 2 < g.h && ix0 >= 0 && ix0 + 3 < g.w) {
+        uint32_t t[IN_ROWS][IN_COLS];
+        if (iy0 >= 0 && iy0 + IN_ROWS - 1 < g.h && ix0 >= 0 && ix0 + IN_COLS - 1 < g.w) {
             const uint32_t *p0 = xc + ((uint32_t)iy0 * row_pitch + (uint32_t)ix0 * cq);
 #pragma unroll
-            for (int rr = 0; rr < 3; ++rr)
+            for (int rr = 0; rr < IN_ROWS; ++rr)
 #pragma unroll
-                for (int ss = 0; ss < 4; ++ss)
+                for (int ss = 0; ss < IN_COLS; ++ss)
                     t[rr][ss] = __ldg(p0 + (rr * row_pitch + ss * cq));
         } else {
 #pragma unroll
-            for (int rr = 0; rr < 3; ++rr)
+            for (int rr = 0; rr < IN_ROWS; ++rr)
 #pragma unroll
-                for (int ss = 0; ss < 4; ++ss) {
+                for (int ss = 0; ss < IN_COLS; ++ss) {
                     const int iy = iy0 + rr, ix = ix0 + ss;
                     t[rr][ss] = (iy >= 0 && iy < g.h && ix >= 0 && ix < g.w)
                         ? __ldg(xc + ((uint32_t)iy * row_pitch + (uint32_t)ix * cq)) : izp4;
                 }
         }
-        int a0[4] = { 0, 0, 0, 0 }, a1[4] = { 0, 0, 0, 0 };
+        uint4 wv[3][NV];
 #pragma unroll
-        for (int rr = 0; rr < 3; ++rr) {
-            const uint4 wl = __ldg(w3p + ((size_t)ci * 3 + rr) * 2), wr = __ldg(w3p + ((size_t)ci * 3 + rr) * 2 + 1);
+        for (int rr = 0; rr < 3; ++rr)
+#pragma unroll
+            for (int v = 0; v < NV; ++v)
+                wv[rr][v] = __ldg(w3p + ((size_t)ci * 3 + rr) * NV + v);
+        int acc[ROWS][2][4];
+#pragma unroll
+        for (int o = 0; o < ROWS; ++o)
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                acc[o][0][j] = acc[o][1][j] = 0;
+#pragma unroll
+        for (int ir = 0; ir < IN_ROWS; ++ir) {
             uint32_t ch[4];
-            transpose4x4(t[rr][0], t[rr][1], t[rr][2], t[rr][3], ch);
-            a0[0] = dp4a_us(ch[0], wl.x, a0[0]); a0[1] = dp4a_us(ch[1], wl.y, a0[1]);
-            a0[2] = dp4a_us(ch[2], wl.z, a0[2]); a0[3] = dp4a_us(ch[3], wl.w, a0[3]);
-            a1[0] = dp4a_us(ch[0], wr.x, a1[0]); a1[1] = dp4a_us(ch[1], wr.y, a1[1]);
-            a1[2] = dp4a_us(ch[2], wr.z, a1[2]); a1[3] = dp4a_us(ch[3], wr.w, a1[3]);
+            transpose4x4(t[ir][0], t[ir][1], t[ir][2], t[ir][3], ch);
+#pragma unroll
+            for (int o = 0; o < ROWS; ++o) {
+                const int kr = ir - o * S;     // kernel row this input row meets in output row o
+                if (kr < 0 || kr > 2)
+                    continue;
+                const uint4 w0 = wv[kr][0], w1 = wv[kr][1];
+                acc[o][0][0] = dp4a_us(ch[0], w0.x, acc[o][0][0]); acc[o][0][1] = dp4a_us(ch[1], w0.y, acc[o][0][1]);
+                acc[o][0][2] = dp4a_us(ch[2], w0.z, acc[o][0][2]); acc[o][0][3] = dp4a_us(ch[3], w0.w, acc[o][0][3]);
+                acc[o][1][0] = dp4a_us(ch[0], w1.x, acc[o][1][0]); acc[o][1][1] = dp4a_us(ch[1], w1.y, acc[o][1][1]);
+                acc[o][1][2] = dp4a_us(ch[2], w1.z, acc[o][1][2]); acc[o][1][3] = dp4a_us(ch[3], w1.w, acc[o][1][3]);
+                if (S == 2) {
+                    const uint4 w2 = wv[kr][NV - 1];
+                    const uint32_t x4 = t[ir][IN_COLS - 1];
+                    acc[o][1][0] = dp4a_us(x4, w2.x, acc[o][1][0]); acc[o][1][1] = dp4a_us(x4, w2.y, acc[o][1][1]);
+                    acc[o][1][2] = dp4a_us(x4, w2.z, acc[o][1][2]); acc[o][1][3] = dp4a_us(x4, w2.w, acc[o][1][3]);
+                }
+            }
         }
-        int q0[4], q1[4];
+        int q[ROWS][2][4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int4 c4 = __ldg(q3 + (size_t)ci * 4 + j);
             const long long off = (long long)(((unsigned long long)(uint32_t)c4.y << 32) | (uint32_t)c4.x);
-            q0[j] = max((int)(((long long)a0[j] * c4.z + off) >> 32) >> c4.w, g.relu_lo);
-            q1[j] = max((int)(((long long)a1[j] * c4.z + off) >> 32) >> c4.w, g.relu_lo);
+#pragma unroll
+            for (int o = 0; o < ROWS; ++o)
+#pragma unroll
+                for (int p = 0; p < 2; ++p)
+                    q[o][p][j] = max((int)(((long long)acc[o][p][j] * c4.z + off) >> 32) >> c4.w, g.relu_lo);
         }
-        uint32_t *out = y + ((rowi * (uint32_t)g.ow + (uint32_t)ox) * cq + ci);
-        out[0] = pack_sat_u8x4(q0[0], q0[1], q0[2], q0[3]);
-        if (ox + 1 < g.ow)
-            out[cq] = pack_sat_u8x4(q1[0], q1[1], q1[2], q1[3]);
+#pragma unroll
+        for (int o = 0; o < ROWS; ++o) {
+            if (oy + o >= g.oh)
+                break;
+            uint32_t *out = y + (((img * (uint32_t)g.oh + (uint32_t)(oy + o)) * (uint32_t)g.ow + (uint32_t)ox) * cq + ci);
+            out[0] = pack_sat_u8x4(q[o][0][0], q[o][0][1], q[o][0][2], q[o][0][3]);
+            if (ox + 1 < g.ow)
+                out[cq] = pack_sat_u8x4(q[o][1][0], q[o][1][1], q[o][1][2], q[o][1][3]);
+        }
     }
+}
+
+template <int ROWS, int S>
+static void depthwise3x3_pair_launch(const ConvGeom &g, const ConvDirectPlan &p, const uint8_t *x, int n, uint8_t *y, cudaStream_t st)
+{
+    const size_t total = (size_t)n * ((g.oh + ROWS - 1) / ROWS) * ((g.ow + 1) / 2) * (g.c / 4);
+    conv_depthwise3x3_pair_kernel<ROWS, S><<<resident_grid<conv_depthwise3x3_pair_kernel<ROWS, S>, 256>((total + 255) / 256), 256, 0, st>>>(
+        g, reinterpret_cast<const uint32_t *>(x), reinterpret_cast<const uint4 *>(p.w_dw3p_dev), p.q_dw3_dev,
+        reinterpret_cast<uint32_t *>(y), n);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -493,12 +538,12 @@ int conv_direct_launch(
     const bool depthwise = p.w_dw_dev && !acc_out && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
     const bool dw3 = depthwise && p.w_dw3_dev && p.q_dw3_dev && npix * (size_t)(g.c / 4) < 0xffffffffull
         && (size_t)n * g.h * g.w * (size_t)(g.c / 4) < 0xffffffffull;
-    if (dw3 && p.w_dw3p_dev && g.stride_w == 1) {
-        const size_t total = (size_t)n * g.oh * ((g.ow + 1) / 2) * (g.c / 4);
-        const int grid = resident_grid<conv_depthwise3x3_pair_kernel, 256>((total + 255) / 256);
-        conv_depthwise3x3_pair_kernel<<<grid, 256, 0, st>>>(
-            g, reinterpret_cast<const uint32_t *>(x), reinterpret_cast<const uint4 *>(p.w_dw3p_dev), p.q_dw3_dev,
-            reinterpret_cast<uint32_t *>(y), n);
+    if (dw3 && p.w_dw3p_dev && (g.stride_w == 1 || g.stride_w == 2)) {
+        // two output rows per thread where the vertical stride equals the horizontal one
+        if (g.stride_w == 1 && g.stride_h == 1) depthwise3x3_pair_launch<2, 1>(g, p, x, n, y, st);
+        else if (g.stride_w == 1) depthwise3x3_pair_launch<1, 1>(g, p, x, n, y, st);
+        else if (g.stride_h == 2) depthwise3x3_pair_launch<2, 2>(g, p, x, n, y, st);
+        else depthwise3x3_pair_launch<1, 2>(g, p, x, n, y, st);
     } else if (dw3) {
         const size_t total = npix * (g.c / 4);
         const int grid = resident_grid<conv_depthwise3x3_kernel, 256>((total + 255) / 256);

@@ -164,15 +164,23 @@ int b200_conv2d_create(
             }
             rc = upload(w3, &cv->direct.w_dw3_dev);
             if (rc == B200_OK) rc = upload(q3, &cv->direct.q_dw3_dev);
-            if (rc == B200_OK && g.stride_w == 1) {
-                std::vector<uint32_t> w3p((size_t)(g.c / 4) * 3 * 2 * 4, 0);
+            if (rc == B200_OK && (g.stride_w == 1 || g.stride_w == 2)) {
+                // one kernel row against 3 + stride_w neighbouring input pixels (conv_depthwise3x3_pair_kernel)
+                const int nv = g.stride_w == 2 ? 3 : 2;
+                std::vector<uint32_t> w3p((size_t)(g.c / 4) * 3 * nv * 4, 0);
                 for (int c = 0; c < g.c; ++c)
                     for (int rr = 0; rr < 3; ++rr) {
-                        uint32_t word = 0;
+                        uint32_t wb[3];
                         for (int j = 0; j < 3; ++j)
-                            word |= (uint32_t)(uint8_t)w_s8[(size_t)c * 9 + rr * 3 + j] << (8 * j);
-                        w3p[(((size_t)(c / 4) * 3 + rr) * 2 + 0) * 4 + (c % 4)] = word;        // left pixel: inputs 0..2
-                        w3p[(((size_t)(c / 4) * 3 + rr) * 2 + 1) * 4 + (c % 4)] = word << 8;   // right pixel: inputs 1..3
+                            wb[j] = (uint32_t)(uint8_t)w_s8[(size_t)c * 9 + rr * 3 + j];
+                        uint32_t *dst = &w3p[((size_t)(c / 4) * 3 + rr) * nv * 4 + (c % 4)];
+                        dst[0] = wb[0] | (wb[1] << 8) | (wb[2] << 16);                   // left pixel: inputs 0..2
+                        if (g.stride_w == 1) {
+                            dst[4] = (wb[0] << 8) | (wb[1] << 16) | (wb[2] << 24);       // right pixel: inputs 1..3
+                        } else {
+                            dst[4] = (wb[0] << 16) | (wb[1] << 24);                      // right pixel: inputs 2, 3 ...
+                            dst[8] = wb[2] << (8 * (c % 4));                             // ... and 4, at the channel's byte
+                        }
                     }
                 rc = upload(w3p, &cv->direct.w_dw3p_dev);
             }

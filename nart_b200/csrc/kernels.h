@@ -81,8 +81,8 @@ struct ConvDirectPlan {
     // {folded 64-bit addend, mult, shift - 32}
     uint32_t *w_dw3_dev = nullptr;
     int4 *q_dw3_dev = nullptr;
-    // the same for two output pixels side by side (stride_w == 1): [c/4][3 rows][2 pixels][4 channels]
-    // words (w0, w1, w2, 0) and (0, w0, w1, w2) of one kernel row, against four neighbouring input pixels
+    // the same for two output pixels side by side (stride_w 1 or 2), see conv_depthwise3x3_pair_kernel:
+    // [c/4][3 kernel rows][2 or 3][4 channels] words of one kernel row against 3 + stride_w input pixels
     uint32_t *w_dw3p_dev = nullptr;
     int32_t *bias_fold_dev = nullptr;
     uint32_t *mult_dev = nullptr;

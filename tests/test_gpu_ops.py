@@ -266,10 +266,13 @@ def test_conv_requantize_variants_on_both_paths(ops, port, k):
                 assert_same(got, want, "k=%d oalpha=%g obits=%d relu=%s algo=%d" % (k, oalpha, obits, relu, algo))
 
 
-@pytest.mark.parametrize("c,h,w,sh,pd", [(32, 9, 9, 1, 1), (64, 7, 12, 1, 0), (16, 5, 3, 1, 1), (48, 11, 10, 2, 1), (16, 3, 4, 1, 0)])
-def test_depthwise3x3_two_pixels_per_thread(ops, port, c, h, w, sh, pd):
-    """Depthwise 3x3 with horizontal stride 1 (two output pixels per thread): odd and even output widths,
-    with and without padding, vertical stride 2, a width below the pair's four-pixel reach."""
+@pytest.mark.parametrize("c,h,w,sh,sw,pd", [(32, 9, 9, 1, 1, 1), (64, 7, 12, 1, 1, 0), (16, 5, 3, 1, 1, 1), (48, 11, 10, 2, 1, 1),
+                                            (16, 3, 4, 1, 1, 0), (32, 12, 12, 2, 2, 1), (48, 9, 11, 2, 2, 1), (16, 7, 7, 2, 2, 0),
+                                            (16, 8, 9, 1, 2, 1), (32, 5, 5, 2, 2, 1), (16, 3, 3, 2, 2, 1)])
+def test_depthwise3x3_two_pixels_per_thread(ops, port, c, h, w, sh, sw, pd):
+    """Depthwise 3x3 with two output pixels (and, where the strides agree, two output rows) per thread:
+    strides 1 and 2, odd and even output sizes, with and without padding, maps smaller than the
+    thread's reach."""
     rng = np.random.default_rng(c * 100 + h * 10 + w)
     n = 3
     x = rng.integers(0, 256, (n, c, h, w), dtype=np.uint8)
@@ -278,12 +281,12 @@ def test_depthwise3x3_two_pixels_per_thread(ops, port, c, h, w, sh, pd):
     walpha = rng.uniform(0.001, 0.01, c).astype(np.float32)
     q = dict(ialpha=0.04, izp=int(rng.integers(0, 256)), wzp=128, oalpha=0.12, ozp=int(rng.integers(0, 200)), walpha=walpha)
     for relu in (False, True):
-        want = port.conv2d_u8(x, wt, bias, (sh, 1), (pd, pd), c, q["ialpha"], q["izp"], walpha, 128, q["oalpha"], q["ozp"],
+        want = port.conv2d_u8(x, wt, bias, (sh, sw), (pd, pd), c, q["ialpha"], q["izp"], walpha, 128, q["oalpha"], q["ozp"],
                               relu=relu)
-        conv = ops.Conv2d(wt, bias, in_hw=(h, w), stride=(sh, 1), pad=(pd, pd), group=c, algo=ops.ALGO_DIRECT, relu=relu, **q)
+        conv = ops.Conv2d(wt, bias, in_hw=(h, w), stride=(sh, sw), pad=(pd, pd), group=c, algo=ops.ALGO_DIRECT, relu=relu, **q)
         got = to_host_nchw(conv(to_dev_nhwc(x)))
         assert ops.device_status() == 0
-        assert_same(got, want, "dw pair c=%d %dx%d sh=%d pad=%d relu=%d" % (c, h, w, sh, pd, relu))
+        assert_same(got, want, "dw pair c=%d %dx%d stride %dx%d pad=%d relu=%d" % (c, h, w, sh, sw, pd, relu))
     assert len(np.unique(want)) > 16
 
 
