@@ -45,7 +45,9 @@ namespace {
 
 constexpr int kMaxAccStages = 4;              // accumulator stages in tensor memory = epilogue groups: 2 or 4
 constexpr int kEpiWarps = 16;                 // split into 2 groups of 8 warps or 4 groups of 4
+constexpr int kMma2Warp = 2 + kEpiWarps;        // the second MMA-issuing warp, behind the epilogue warps
 constexpr int kThreads = 64 + kEpiWarps * 32;
+constexpr int kThreads2 = kThreads + 32;         // with the second MMA-issuing warp
 constexpr int kTileM = 128;
 constexpr int kMaxStages = 8;
 constexpr int kGroupBytes = 32 * 1024;        // target size of one pipeline stage (a group of k-blocks)
@@ -457,8 +459,9 @@ __host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int 
 
 // HAS_RES: the instantiation whose epilogue can add a residual tensor; plans without a fused add run the
 // other one, which carries none of that code.
-template <bool HAS_RES, bool HAS_WZP = false>
-__global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const IgemmArgs g)
+// MMA2: the instantiation with a second MMA-issuing warp (one more warp in the block).
+template <bool HAS_RES, bool HAS_WZP = false, bool MMA2 = false>
+__global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const IgemmArgs g)
 {
     extern __shared__ uint8_t smem_raw[];
     // the swizzle patterns are functions of the absolute shared address: align the base to 1024
@@ -521,9 +524,16 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
         // `slots` k-blocks.  The first lane of a group posts the group's byte count; a load of another
         // lane may complete before that (the transaction count is signed), the phase cannot, because
         // the arrival is still pending.
+        //
+        // With two MMA-issuing warps the ring is split in two halves, one per warp: the lanes of half
+        // r load the k-blocks of the CTA's tiles r, r + 2, ... only, so that every stage barrier has
+        // one consumer that meets its phases in order.
         const int slots = g.stages * g.kgroup;
+        constexpr int rings = MMA2 ? 2 : 1;
+        const int ring_slots = slots / rings;
         if (lane < slots && blockIdx.x < total_tiles) {
             const int stage = lane / g.kgroup;
+            const int ring = lane / ring_slots, rl = lane - ring * ring_slots;
             const bool first = lane == stage * g.kgroup;
             const uint32_t fb = full_bar(stage), eb = empty_bar(stage);
             const uint32_t a_dst = base + L.a + lane * a_tile_bytes, b_dst = base + L.b + lane * b_tile_bytes;
@@ -536,11 +546,11 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
             }
             const int sh_h = g.stride_h - 1, sh_w = g.stride_w - 1;   // strides are 1 or 2
             // this lane's first k-block
-            int kb = lane % kblocks;
+            int kb = rl % kblocks;
             int tile = blockIdx.x;
             TileWalker tw;
             tw.init(g, tile);
-            for (int i = lane / kblocks; i > 0; --i) {
+            for (int i = (rl / kblocks) * rings + ring; i > 0; --i) {
                 tile += gridDim.x;
                 tw.advance(g);
             }
@@ -579,11 +589,13 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                         if (!g.b_resident)
                             tma_load_2d(b_dst, &maps.b, fb, kb * g.bk, tw.nt * g.bn);
                         phase ^= 1;
-                        kb += slots;
+                        kb += ring_slots;
                         while (kb >= kblocks) {
                             kb -= kblocks;
-                            tile += gridDim.x;
-                            tw.advance(g);
+                            for (int i = 0; i < rings; ++i) {
+                                tile += gridDim.x;
+                                tw.advance(g);
+                            }
                         }
                         active = tile < total_tiles;
                         t0 = clock64();
@@ -596,15 +608,20 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || (MMA2 && warp == kMma2Warp)) {
         // ================= MMA issuer =================
         // The whole warp walks the loop (uniform control flow); lane 0 alone issues.  Descriptors of
         // one operand differ only in the start-address field, so only their low words are computed.
         {
             const uint32_t lead = lane == 0 ? 1u : 0u;
-            int stage = 0;
+            // warp r of `rings` issuing warps takes the CTA's tiles r, r + rings, ... and the stages
+            // [r * ring_stages, (r + 1) * ring_stages); accumulator stages advance by `rings` as well
+            constexpr int rings = MMA2 ? 2 : 1;
+            const int ring = warp == 1 ? 0 : 1;
+            const int ring_stages = g.stages / rings, stage0 = ring * ring_stages;
+            int stage = stage0;
             uint32_t phase = 0;
-            int as = 0;
+            int as = ring;
             uint32_t aphase = 0;
             bool ok = true;
             const uint64_t adesc0 = make_smem_desc(base + L.a, g.bk);
@@ -622,7 +639,7 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                 *abort_flag = 1;
                 ok = false;
             }
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            for (int tile = blockIdx.x + ring * gridDim.x; tile < total_tiles && ok; tile += rings * gridDim.x) {
                 if (!mbar_wait(tempty_bar(as), aphase ^ 1, abort_flag)) {
                     if (lead)
                         atomicCAS(g.status, 0, kErrMmaTmemWait);
@@ -655,21 +672,22 @@ __global__ void __launch_bounds__(kThreads, 1) conv_igemm_i8_kernel(const __grid
                         }
                     }
                     mma_commit(empty_bar(stage), lead);   // frees the smem stage when the group's MMAs are done
-                    if (++stage == g.stages) {
-                        stage = 0;
+                    if (++stage == stage0 + ring_stages) {
+                        stage = stage0;
                         phase ^= 1;
                     }
                 }
                 if (!ok)
                     break;
                 mma_commit(tfull_bar(as), lead);          // accumulator complete
-                if (++as == g.acc_stages) {
-                    as = 0;
+                as += rings;
+                if (as >= g.acc_stages) {
+                    as -= g.acc_stages;
                     aphase ^= 1;
                 }
             }
         }
-    } else {
+    } else if (warp < kMma2Warp) {
         // ================= epilogue (warps 2..17) =================
         // Two independent groups of 8 warps; group i owns accumulator stage i, i.e. every second
         // tile of this CTA, with its own staging buffer, tables and named barriers, so that one
@@ -931,7 +949,7 @@ struct ConvIgemmPlan {
     ConvGeom g;
     int groups = 2, acc_stages = 2;
     int cpad = 0;                   // input channels rounded up to a multiple of 32
-    int bk = 0, bn = 0, stages = 0, kgroup = 1, ob = 0, kpad = 0, b_resident = 0, a_wide = 0;
+    int bk = 0, bn = 0, stages = 0, kgroup = 1, ob = 0, kpad = 0, b_resident = 0, a_wide = 0, mma_warps = 1;
     int n_row_cls = 0, n_col_cls = 0;
     int generic_requant = 0;
     int8_t *w_dev = nullptr;        // [kpad][r][s][c]
@@ -1127,6 +1145,18 @@ int conv_igemm_create(
         while (stages > 2 && (!fits(stages, kgroup) || stages * kgroup > 32))
             --stages;
         // a deep ring lets the producer run several tiles ahead when a tile has few k-blocks
+        // Narrow channel tiles make short MMAs, and one thread issues those no faster than one per
+        // ~100 cycles whatever their size: two issuing warps, each on its own half of the ring and on
+        // every second tile, keep the tensor pipe fed (3x3 64-channel layer: 0.082 -> 0.061 ms; 256-wide
+        // tiles gain nothing).
+        p->mma_warps = (p->bn <= 128 && stages >= 4) ? 2 : 1;
+        if (const char *e = getenv("B200_IGEMM_MMA_WARPS")) {   // tuning aid: 1, or 2 when the ring has four stages or more
+            int v = atoi(e);
+            if (v == 1 || (v == 2 && stages >= 4))
+                p->mma_warps = v;
+        }
+        if (p->mma_warps == 2)
+            stages &= ~1;
         p->stages = stages;
         p->kgroup = kgroup;
     }
@@ -1368,6 +1398,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
+        B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
         p->attr_set = true;
     }
     p->last_x = x;
@@ -1423,6 +1454,8 @@ int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cud
         conv_igemm_i8_kernel<true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
     else if (wsum != nullptr)
         conv_igemm_i8_kernel<false, true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
+    else if (p->mma_warps == 2)
+        conv_igemm_i8_kernel<false, false, true><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args);
     else
         conv_igemm_i8_kernel<false><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
     B200_CUDA_TRY(cudaGetLastError());
