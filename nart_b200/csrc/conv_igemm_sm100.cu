@@ -459,9 +459,12 @@ __host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int 
 
 // HAS_RES: the instantiation whose epilogue can add a residual tensor; plans without a fused add run the
 // other one, which carries none of that code.
-// MMA2: the instantiation with a second MMA-issuing warp (one more warp in the block).
-template <bool HAS_RES, bool HAS_WZP = false, bool MMA2 = false>
-__global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const IgemmArgs g)
+// MODE 0: one MMA-issuing warp.  MODE 1 and 2 add a second one (one more warp in the block):
+//   1: the CTA's tiles alternate between the two warps, each on its own half of the stage ring;
+//   2: the CTA's tiles go in pairs that share every weight k-block: a stage holds the activation
+//      tiles of both and ONE weight tile, each warp issues the MMAs of its own tile of the pair.
+template <bool HAS_RES, bool HAS_WZP = false, int MODE = 0>
+__global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const IgemmArgs g)
 {
     extern __shared__ uint8_t smem_raw[];
     // the swizzle patterns are functions of the absolute shared address: align the base to 1024
@@ -470,7 +473,7 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
     uint8_t *smem = smem_raw + (base - raw_addr);
     const int kblocks_all = g.r * g.s * (g.c / g.bk);
     const int slots = g.stages * g.kgroup;
-    const SmemLayout L = smem_layout(slots, g.b_resident ? kblocks_all : slots, g.bk, g.bn, g.groups);
+    const SmemLayout L = smem_layout(MODE == 2 ? 2 * slots : slots, g.b_resident ? kblocks_all : slots, g.bk, g.bn, g.groups);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -488,7 +491,7 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
     if (threadIdx.x == 0) {
         for (int s = 0; s < g.stages; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(empty_bar(s), MODE == 2 ? 2 : 1);   // pair mode: both issuing warps release a stage
         }
         mbar_init(bres_bar, 1);
         for (int s = 0; s < g.acc_stages; ++s) {
@@ -529,14 +532,19 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
         // r load the k-blocks of the CTA's tiles r, r + 2, ... only, so that every stage barrier has
         // one consumer that meets its phases in order.
         const int slots = g.stages * g.kgroup;
-        constexpr int rings = MMA2 ? 2 : 1;
+        //
+        // Pair mode: one ring; slot l holds, for k-block q of the PAIR sequence, the activation tiles of
+        // the pair's two tiles and the one weight tile both use (the host has checked that the two
+        // tiles share their channel tile).
+        constexpr int rings = MODE == 1 ? 2 : 1;
+        constexpr int tiles_per_step = MODE == 0 ? 1 : 2;   // tiles a lane moves on by when its k-block wraps
         const int ring_slots = slots / rings;
         if (lane < slots && blockIdx.x < total_tiles) {
             const int stage = lane / g.kgroup;
             const int ring = lane / ring_slots, rl = lane - ring * ring_slots;
             const bool first = lane == stage * g.kgroup;
             const uint32_t fb = full_bar(stage), eb = empty_bar(stage);
-            const uint32_t a_dst = base + L.a + lane * a_tile_bytes, b_dst = base + L.b + lane * b_tile_bytes;
+            const uint32_t a_dst = base + L.a + lane * a_tile_bytes * (MODE == 2 ? 2 : 1), b_dst = base + L.b + lane * b_tile_bytes;
             const uint32_t tx_bytes = (a_tile_bytes + (g.b_resident ? 0u : (uint32_t)g.bn * g.bk)) * (uint32_t)g.kgroup;
             if (g.b_resident && lane == 0) {
                 // one channel tile and weights that fit: every k-block of B is loaded once and stays
@@ -550,7 +558,7 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
             int tile = blockIdx.x;
             TileWalker tw;
             tw.init(g, tile);
-            for (int i = (rl / kblocks) * rings + ring; i > 0; --i) {
+            for (int i = (rl / kblocks) * tiles_per_step + ring; i > 0; --i) {
                 tile += gridDim.x;
                 tw.advance(g);
             }
@@ -580,19 +588,32 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
                         const int xw = (tw.twi << g.tw_sh) + ((dw - pw) >> sh_w);
                         const int n0 = tw.tni * g.tn;
                         const CUtensorMap *amap = &maps.a[ph * 2 + pw];
+                        if (MODE == 2) {
+                            // the pair's second tile (absent behind an odd number of tiles): same tap, its own pixels
+                            const bool second = tile + (int)gridDim.x < total_tiles;
+                            mbar_expect_tx(fb, tx_bytes + (second ? a_tile_bytes : 0u));
+                            tma_load_4d(a_dst, amap, fb, cc, xw, yh, n0);
+                            if (second) {
+                                TileWalker t2 = tw;
+                                t2.advance(g);
+                                tma_load_4d(a_dst + a_tile_bytes, amap, fb, cc, (t2.twi << g.tw_sh) + ((dw - pw) >> sh_w),
+                                            (t2.thi << g.th_sh) + ((dh - ph) >> sh_h), t2.tni * g.tn);
+                            }
+                        } else {
                         if (first)
                             mbar_expect_tx(fb, tx_bytes);
                         if (g.a_wide)   // rows of tw pixels x 32 bytes, in 8-byte elements
                             tma_load_3d(a_dst, amap, fb, xw << 2, yh, n0);
                         else
                             tma_load_4d(a_dst, amap, fb, cc, xw, yh, n0);
+                        }
                         if (!g.b_resident)
                             tma_load_2d(b_dst, &maps.b, fb, kb * g.bk, tw.nt * g.bn);
                         phase ^= 1;
                         kb += ring_slots;
                         while (kb >= kblocks) {
                             kb -= kblocks;
-                            for (int i = 0; i < rings; ++i) {
+                            for (int i = 0; i < tiles_per_step; ++i) {
                                 tile += gridDim.x;
                                 tw.advance(g);
                             }
@@ -608,7 +629,7 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
                 }
             }
         }
-    } else if (warp == 1 || (MMA2 && warp == kMma2Warp)) {
+    } else if (warp == 1 || (MODE != 0 && warp == kMma2Warp)) {
         // ================= MMA issuer =================
         // The whole warp walks the loop (uniform control flow); lane 0 alone issues.  Descriptors of
         // one operand differ only in the start-address field, so only their low words are computed.
@@ -616,9 +637,12 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
             const uint32_t lead = lane == 0 ? 1u : 0u;
             // warp r of `rings` issuing warps takes the CTA's tiles r, r + rings, ... and the stages
             // [r * ring_stages, (r + 1) * ring_stages); accumulator stages advance by `rings` as well
-            constexpr int rings = MMA2 ? 2 : 1;
+            // In pair mode both warps walk the whole ring, stage by stage together: warp r issues for the
+            // r-th tile of each pair, on the r-th activation tile of the stage and the shared weight tile.
+            constexpr int rings = MODE == 1 ? 2 : 1;
+            constexpr int tile_step = MODE == 0 ? 1 : 2;
             const int ring = warp == 1 ? 0 : 1;
-            const int ring_stages = g.stages / rings, stage0 = ring * ring_stages;
+            const int ring_stages = g.stages / rings, stage0 = MODE == 1 ? ring * ring_stages : 0;
             int stage = stage0;
             uint32_t phase = 0;
             int as = ring;
@@ -629,7 +653,7 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
             const uint32_t desc_hi = (uint32_t)(adesc0 >> 32);        // the same for A and B
             const uint32_t a_lo0 = (uint32_t)adesc0, b_lo0 = (uint32_t)bdesc0;
             const uint32_t a_step = a_tile_bytes >> 4, b_step = b_tile_bytes >> 4;   // descriptor address units
-            const uint32_t a_grp = a_step * g.kgroup, b_grp = b_step * g.kgroup;
+            const uint32_t a_grp = a_step * g.kgroup * (MODE == 2 ? 2 : 1), b_grp = b_step * g.kgroup;
             const int ksteps = g.bk / 32;
             const int groups = kblocks / g.kgroup;
             const uint32_t idesc = g.idesc;
@@ -639,8 +663,13 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
                 *abort_flag = 1;
                 ok = false;
             }
-            for (int tile = blockIdx.x + ring * gridDim.x; tile < total_tiles && ok; tile += rings * gridDim.x) {
-                if (!mbar_wait(tempty_bar(as), aphase ^ 1, abort_flag)) {
+            for (int tile = blockIdx.x + ring * gridDim.x; (MODE == 2 ? tile - ring * (int)gridDim.x : tile) < total_tiles && ok;
+                 tile += tile_step * gridDim.x) {
+                // pair mode: the second warp of a pair without a second tile still takes part in the
+                // stage hand-over (its commits arrive at once), it just issues nothing
+                const bool have_tile = MODE != 2 || tile < total_tiles;
+                const uint32_t issue = have_tile ? lead : 0u;
+                if (have_tile && !mbar_wait(tempty_bar(as), aphase ^ 1, abort_flag)) {
                     if (lead)
                         atomicCAS(g.status, 0, kErrMmaTmemWait);
                     *abort_flag = 1;
@@ -658,17 +687,17 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
                         break;
                     }
                     tc_fence_after();
-                    uint32_t a_lo = a_lo0 + stage * a_grp;
+                    uint32_t a_lo = a_lo0 + stage * a_grp + (MODE == 2 ? ring * a_step : 0u);
                     uint32_t b_lo = b_lo0 + (g.b_resident ? grp : stage) * b_grp;
                     for (int j = 0; j < g.kgroup; ++j, a_lo += a_step, b_lo += b_step) {
                         // a k-block is 1, 2 or 4 MMAs of K = 32 bytes: +2 (16-byte units) inside the swizzle atom
-                        mma_i8(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate, lead);
+                        mma_i8(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate, issue);
                         accumulate = 1;
                         if (ksteps >= 2)
-                            mma_i8(d_tmem, a_lo + 2, b_lo + 2, desc_hi, idesc, 1, lead);
+                            mma_i8(d_tmem, a_lo + 2, b_lo + 2, desc_hi, idesc, 1, issue);
                         if (ksteps == 4) {
-                            mma_i8(d_tmem, a_lo + 4, b_lo + 4, desc_hi, idesc, 1, lead);
-                            mma_i8(d_tmem, a_lo + 6, b_lo + 6, desc_hi, idesc, 1, lead);
+                            mma_i8(d_tmem, a_lo + 4, b_lo + 4, desc_hi, idesc, 1, issue);
+                            mma_i8(d_tmem, a_lo + 6, b_lo + 6, desc_hi, idesc, 1, issue);
                         }
                     }
                     mma_commit(empty_bar(stage), lead);   // frees the smem stage when the group's MMAs are done
@@ -679,8 +708,8 @@ __global__ void __launch_bounds__(MMA2 ? kThreads2 : kThreads, 1) conv_igemm_i8_
                 }
                 if (!ok)
                     break;
-                mma_commit(tfull_bar(as), lead);          // accumulator complete
-                as += rings;
+                mma_commit(tfull_bar(as), issue);         // accumulator complete
+                as += tile_step;
                 if (as >= g.acc_stages) {
                     as -= g.acc_stages;
                     aphase ^= 1;
@@ -949,7 +978,7 @@ struct ConvIgemmPlan {
     ConvGeom g;
     int groups = 2, acc_stages = 2;
     int cpad = 0;                   // input channels rounded up to a multiple of 32
-    int bk = 0, bn = 0, stages = 0, kgroup = 1, ob = 0, kpad = 0, b_resident = 0, a_wide = 0, mma_warps = 1;
+    int bk = 0, bn = 0, stages = 0, kgroup = 1, ob = 0, kpad = 0, b_resident = 0, a_wide = 0, mma_warps = 1, pair = 0;
     int n_row_cls = 0, n_col_cls = 0;
     int generic_requant = 0;
     int8_t *w_dev = nullptr;        // [kpad][r][s][c]
@@ -1157,10 +1186,26 @@ int conv_igemm_create(
         }
         if (p->mma_warps == 2)
             stages &= ~1;
+        // Pair mode (see the kernel's MODE 2): wide k-blocks of a layer with one channel tile, where the
+        // operand loads from L2 set the pace: two tiles per stage share one weight tile.
+        // (3x3 128-channel layer 0.047 -> 0.043 ms.  256-wide tiles lose: their two accumulators fill the
+        // tensor memory, so the next pair's mainloop cannot overlap this pair's epilogue: 0.039 -> 0.044 ms.)
+        const bool pair_off = getenv("B200_IGEMM_PAIR") && atoi(getenv("B200_IGEMM_PAIR")) == 0;   // tuning aid
+        if (!pair_off && !p->b_resident && kgroup == 1 && !p->a_wide && n_tiles_n == 1 && p->bn <= 128) {
+            int st = kMaxStages;
+            auto fits2 = [&](int n) { return smem_layout(2 * n, n, p->bk, p->bn, p->groups).total + 1024 <= 227 * 1024; };
+            while (st > 2 && !fits2(st))
+                --st;
+            if (fits2(st)) {
+                p->pair = 1;
+                p->mma_warps = 2;
+                stages = st;
+            }
+        }
         p->stages = stages;
         p->kgroup = kgroup;
     }
-    if (smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (p->cpad / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024 > 227 * 1024) {
+    if (smem_layout((p->pair ? 2 : 1) * p->stages * p->kgroup, p->b_resident ? g.r * g.s * (p->cpad / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024 > 227 * 1024) {
         delete p;
         return fail(B200_ERR_UNSUPPORTED, "conv(igemm): tile does not fit shared memory");
     }
@@ -1393,12 +1438,13 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
         a.step_h = gsz % a.tiles_h;
         a.step_n = gsz / a.tiles_h;
     }
-    p->smem = smem_layout(p->stages * p->kgroup, p->b_resident ? g.r * g.s * (p->cpad / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024;
+    p->smem = smem_layout((p->pair ? 2 : 1) * p->stages * p->kgroup, p->b_resident ? g.r * g.s * (p->cpad / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024;
     if (!p->attr_set) {
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
         B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
-        B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
+        B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
+        B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
         p->attr_set = true;
     }
     p->last_x = x;
@@ -1454,8 +1500,10 @@ int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cud
         conv_igemm_i8_kernel<true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
     else if (wsum != nullptr)
         conv_igemm_i8_kernel<false, true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
+    else if (p->pair)
+        conv_igemm_i8_kernel<false, false, 2><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args);
     else if (p->mma_warps == 2)
-        conv_igemm_i8_kernel<false, false, true><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args);
+        conv_igemm_i8_kernel<false, false, 1><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args);
     else
         conv_igemm_i8_kernel<false><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
     B200_CUDA_TRY(cudaGetLastError());
