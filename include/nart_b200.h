@@ -312,7 +312,7 @@ B200_API int b200_case_wait(b200_case_t *cs);
 B200_API int b200_case_launch_count(const b200_case_t *cs, int32_t *launches);
 /* Folds residual adds into the convs that feed them (default: off; call before b200_case_prepare).
  * Off by default because on B200 the conv epilogue is bound by instruction issue, not by memory:
- * ResNet-50 at batch 256 runs 3.62 ms per step fused against 3.39 ms with the adds as kernels of
+ * ResNet-50 at batch 256 runs 3.43 ms per step fused against 3.23 ms with the adds as kernels of
  * their own, although the fused form moves 2.7 GB less.
  * A two-input eltwise SUM whose later-produced input is the output of a tensor-core conv that
  * nothing else reads then runs in that conv's epilogue (b200_conv2d_fuse_residual_add) and its own
