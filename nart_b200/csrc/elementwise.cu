@@ -175,22 +175,24 @@ __device__ __forceinline__ int elt_finish(int t, const EltwiseArgs &a)
 
 // FAST: obits == 8 and the final rounding term 2^(s0-1) << b[0] fits into add[0] (folded there by
 // the host, exact because it is a multiple of 2^b[0]); then y = sat_u8(max((t >> s0) + ozp, relu_lo))
-// and the saturation comes with the pack.  32 bytes per input per thread and iteration.
+// and the saturation comes with the pack.  64 bytes per input per thread and iteration.
 // PLAIN (with FAST): ozp == 0 and no floor above 0, so y = sat_u8(t >> s0) and the pack does the rest.
 template <int N_IN, bool FAST, bool PLAIN = false>
 __global__ void __launch_bounds__(256) eltwise_sum_kernel(EltwiseArgs a, uint8_t *__restrict__ y, size_t count)
 {
-    constexpr int VPT = 2;   // 16-byte vectors per input per thread
+    constexpr int VPT = 4;   // 16-byte vectors per input per thread (2: 0.80 ms, 4: 0.78 ms, 8: 0.79 ms for the 16 adds of ResNet-50)
     const size_t nvec = count / 16;
-    const size_t nchunk = nvec / VPT;
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t ck = (size_t)blockIdx.x * blockDim.x + threadIdx.x; ck < nchunk; ck += stride) {
+    // a block works on tiles of 256 * VPT vectors; vector u of a thread lies 256 vectors after vector
+    // u - 1, so that every load and store instruction of a warp covers 512 contiguous bytes
+    const size_t ntile = nvec / (256 * VPT);
+    for (size_t tile = blockIdx.x; tile < ntile; tile += gridDim.x) {
+        const size_t v0 = tile * (256 * VPT) + threadIdx.x;
         uint32_t xin[N_IN][4 * VPT];
 #pragma unroll
         for (int i = 0; i < N_IN; ++i)
 #pragma unroll
             for (int u = 0; u < VPT; ++u) {
-                uint4 q = __ldg(reinterpret_cast<const uint4 *>(a.x[i]) + ck * VPT + u);
+                uint4 q = __ldg(reinterpret_cast<const uint4 *>(a.x[i]) + v0 + u * 256);
                 xin[i][4 * u + 0] = q.x; xin[i][4 * u + 1] = q.y; xin[i][4 * u + 2] = q.z; xin[i][4 * u + 3] = q.w;
             }
         uint32_t o[4 * VPT];
@@ -211,11 +213,11 @@ __global__ void __launch_bounds__(256) eltwise_sum_kernel(EltwiseArgs a, uint8_t
         }
 #pragma unroll
         for (int u = 0; u < VPT; ++u)
-            reinterpret_cast<uint4 *>(y)[ck * VPT + u] = make_uint4(o[4 * u], o[4 * u + 1], o[4 * u + 2], o[4 * u + 3]);
+            reinterpret_cast<uint4 *>(y)[v0 + u * 256] = make_uint4(o[4 * u], o[4 * u + 1], o[4 * u + 2], o[4 * u + 3]);
     }
-    // tail (what is left after whole 32-byte chunks)
+    // tail (what is left after whole tiles: less than 256 * VPT * 16 bytes)
     if (blockIdx.x == 0) {
-        for (size_t e = nchunk * VPT * 16 + threadIdx.x; e < count; e += blockDim.x) {
+        for (size_t e = ntile * (256 * VPT * 16) + threadIdx.x; e < count; e += blockDim.x) {
             int t = 0;
 #pragma unroll
             for (int i = 0; i < N_IN; ++i)
@@ -495,7 +497,7 @@ int b200_eltwise_sum_u8(
         return fail(B200_ERR_INVALID, "eltwise: output is not 16-byte aligned");
     if (count == 0)
         return B200_OK;
-    const size_t want = (count / 32 + 1 + 255) / 256;
+    const size_t want = count / (256 * 64) + 1;   // tiles of 256 threads x 64 bytes
     cudaStream_t st = as_stream(stream);
 #define B200_ELT_LAUNCH(...) \
     eltwise_sum_kernel<__VA_ARGS__><<<resident_grid<eltwise_sum_kernel<__VA_ARGS__>, 256>(want), 256, 0, st>>>(a, y, count)
