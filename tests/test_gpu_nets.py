@@ -91,6 +91,25 @@ def test_graph_replay_matches_eager(port):
     cs.close()
 
 
+def test_graphs_of_several_batch_sizes_keep_their_scratch(port):
+    """Graphs captured at a small batch are replayed after a larger batch has run: the convs' scratch
+    tensors (the row-lowered stem) are sized once at prepare (b200_conv2d_reserve), so the addresses
+    a captured graph holds stay valid."""
+    import torch
+    from nart_b200 import nets
+    spec = nets.resnet(18, seed=14, hw=64, width_div=2, spread=True, num_classes=32)
+    rng = np.random.default_rng(10)
+    cs, ids = nets.to_case(spec, 6)
+    cs.use_graph(True)
+    side = torch.cuda.Stream()
+    xs = {b: rng.integers(0, 256, (b, 3, 64, 64), dtype=np.uint8) for b in (2, 6, 3)}
+    want = {b: nets.run_cpu(spec, x, port)[0] for b, x in xs.items()}
+    for b in (2, 2, 2, 6, 6, 6, 2, 3, 3, 3, 6, 2):     # eager, capture, replay per size; then replays interleaved
+        (got,) = cs.run_host([xs[b]], [(np.float32, (32, 1, 1))], side.cuda_stream)
+        assert_same(got.reshape(want[b].shape).view(np.uint32), want[b].view(np.uint32), "batch %d" % b)
+    cs.close()
+
+
 def test_pipelined_submit_matches_reference(port):
     """b200_case_submit_host / b200_case_wait: three batches in flight back to back."""
     import torch
