@@ -36,7 +36,7 @@ BATCH = 256
 # DRAM bytes per launch of the conv kernel, averaged over the 54 launches of one batch-256 step:
 # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of this script (3.850 GB per step)
 IGEMM_DRAM_BYTES_PER_LAUNCH = 3.850e9 / 54
-WORKLOAD = "BASELINE configs[3]: ResNet-50 v1.5 int8, batch 256 per GPU, 3x224x224 uint8 input"
+WORKLOAD = "ResNet-50 v1.5 int8, batch 256 per GPU, 3x224x224 uint8 input, synthetic per-layer quantization"
 SEED = 3
 
 
@@ -121,12 +121,12 @@ def _cpu_init(kind):
 
 def _cpu_worker(args):
     seed, n_images = args
-    from nart_b200 import nets
+    from oracle.net_walk import run_net
     if n_images == 0:          # warm-up call: the worker exists and is initialised
         return 0.0
     x = np.random.default_rng(seed).integers(0, 256, (n_images, 3, 224, 224), dtype=np.uint8)
     t = time.perf_counter()
-    nets.run_cpu(_CPU_STATE["spec"], x, _CPU_STATE["be"], per_channel=(_CPU_STATE["kind"] != "reference"))
+    run_net(_CPU_STATE["spec"], x, _CPU_STATE["be"], per_channel=(_CPU_STATE["kind"] != "reference"))
     return time.perf_counter() - t
 
 
@@ -182,6 +182,58 @@ def run_reference_arm(a):
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
+def pin_to_gpu_numa_node(local: int):
+    """Best effort: run this rank's host threads on the cores of the NUMA node its GPU hangs off, so
+    that the pinned batch buffers (first touch) and the copy engine's reads stay on that node.
+    Returns a short description for the JSON line."""
+    try:
+        import torch
+        bus = torch.cuda.get_device_properties(local).pci_bus_id, torch.cuda.get_device_properties(local).pci_device_id
+        dom = torch.cuda.get_device_properties(local).pci_domain_id
+        path = "/sys/bus/pci/devices/%04x:%02x:%02x.0" % (dom, bus[0], bus[1])
+        node = int(open(path + "/numa_node").read().strip())
+        if node < 0:
+            return "gpu reports no NUMA node"
+        cpus = []
+        for part in open("/sys/devices/system/node/node%d/cpulist" % node).read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.extend(range(int(lo), int(hi or lo) + 1))
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if not allowed:
+            return "node %d has no core this process may use" % node
+        os.sched_setaffinity(0, allowed)
+        return "node %d, %d cores" % (node, len(allowed))
+    except Exception as e:          # containers without /sys, restricted affinity: leave the process where it is
+        return "not pinned (%s)" % type(e).__name__
+
+
+def verify_ranks(cs, batch, stream, rank, world, device):
+    """Every rank pushes the SAME seeded batch through its replica once, outside any timed region;
+    the logits' bytes are hashed per rank, gathered, and must agree with rank 0's; rank 0 compares
+    three images of them with the CPU restatement.  Returns (ranks_identical, images_checked)."""
+    import hashlib
+    import torch
+    x = torch.from_numpy(np.random.default_rng(4242).integers(0, 256, (batch, 3, 224, 224), dtype=np.uint8)).pin_memory()
+    y = torch.zeros((batch, 1000), dtype=torch.float32).pin_memory()
+    cs.run_host_ptrs(batch, [x.data_ptr()], [y.data_ptr()], stream)
+    digest = hashlib.sha256(y.numpy().tobytes()).digest()[:8]
+    from nart_b200 import replicas
+    identical = replicas.all_ranks_hold(digest, device)
+    checked = 0
+    if rank == 0:
+        import oracle
+        from oracle.net_walk import run_net
+        from nart_b200 import nets
+        pick = [0, batch // 2, batch - 1] if batch >= 3 else list(range(batch))
+        want, _, _ = run_net(nets.resnet(50, seed=SEED), x.numpy()[pick], oracle.port())
+        if not np.array_equal(y.numpy()[pick].view(np.uint32), want.reshape(len(pick), -1).view(np.uint32)):
+            raise SystemExit("bench: the logits of the verification batch differ from the CPU restatement")
+        checked = len(pick)
+    if not identical:
+        raise SystemExit("bench: ranks disagree on the logits of the same batch")
+    return identical, checked
+
+
 def fused_residual_convs(spec):
     """Names of the conv outputs whose residual add the case runner folds into the conv: the later
     produced input of a two-input eltwise op, when a conv makes it and nothing else reads it."""
@@ -229,6 +281,7 @@ def run_gpu_arm(a):
 
     rank, world, local = replicas.env_rank_world()
     torch.cuda.set_device(local)
+    numa = pin_to_gpu_numa_node(local)
     replicas.init("nccl", torch.device("cuda", local))
 
     batch = a.batch
@@ -252,6 +305,11 @@ def run_gpu_arm(a):
     def barrier():
         replicas.barrier()
         torch.cuda.synchronize()
+
+    # ---- every replica computes the same thing ---------------------------------------------------
+    ranks_identical, oracle_images = verify_ranks(cs, batch, stream, rank, world, torch.device("cuda", local))
+    check(lib.b200_memcpy_h2d(cs.io_device_ptr(False, 0), x_host.data_ptr(), in_bytes, stream))
+    torch.cuda.synchronize()
 
     # ---- device-resident throughput -----------------------------------------------------------
     # The case replays its launches as one CUDA graph (eager first run, captured second run).
@@ -365,7 +423,9 @@ def run_gpu_arm(a):
                         kernel_times="CUDA events around every launch, a second pass of the same K steps",
                         fused_residual_adds=len(fused),
                         conv_tops=igemm_ops / sec / 1e12, ms_per_step_by_kernel=breakdown,
-                        conv_gop_per_image=nets.conv_ops_per_image(spec) / 1e9, logits_checksum=logits_checksum),
+                        conv_gop_per_image=nets.conv_ops_per_image(spec) / 1e9, logits_checksum=logits_checksum,
+                        ranks_identical=ranks_identical, images_checked_against_cpu_restatement=oracle_images,
+                        host_numa="rank 0: " + numa),
             roofline=dict(bound="hbm", achieved=hbm_ach, peak=peaks["hbm_gbs"], unit="GB/s", frac=hbm_ach / peaks["hbm_gbs"],
                           traffic=IGEMM_DRAM_BYTES_PER_LAUNCH if batch == BATCH else None,
                           traffic_source="ncu dram__bytes_read.sum + dram__bytes_write.sum over the 54 launches of one "

@@ -82,6 +82,15 @@ B200_API int b200_stream_synchronize(b200_stream_t stream);
  * runs out (0 = none did).  Synchronizes `stream` first. */
 B200_API int b200_device_status(b200_stream_t stream, int *status_word);
 
+/* Exercises the give-up path of the bounded device-side waits without a fault: launches a one-warp
+ * kernel that waits, through the very wait routine the convolution kernel's roles use, on a barrier
+ * nothing arrives at.  After `limit_cycles` SM clock cycles (1 .. 2e9, i.e. at most about a second)
+ * the wait gives up, the kernel records code 0x1ff in the device status word and returns normally;
+ * the next b200_device_status then reads 0x1ff, and b200_case_run_host / b200_case_wait report
+ * B200_ERR_DEVICE_WAIT.  The context stays usable.  The reference has no counterpart: its GPU
+ * modules have no device-side waits (art/modules/cuda_quant/src/cuda_quant_workspace.c). */
+B200_API int b200_selftest_wait_expiry(uint64_t limit_cycles, b200_stream_t stream);
+
 /* ---- scale decomposition -------------------------------------------------------------------
  * get_quant_scale_int32 / get_quant_scale_int16 / get_quant_scale
  * (art/modules/quant/include/art/quant/quant_helper.h:60-118): `bits` 32, -16 (the uint16
@@ -97,6 +106,14 @@ B200_API void b200_get_quant_scale(float x, int bits, uint32_t *mult, int8_t *sh
  * decomposed by the same function).  relu follows the fused flag of the reference GPU module
  * (SETTING_CONV_2D_RELU_FLAG, art/modules/cuda_quant/src/op/conv_2d_quant.cu:793-794) with the
  * CPU module's relu arithmetic (art/modules/quant/src/op/relu.c:76-115, equal in/out scale). */
+/* Tuning switches of the tensor-core plan, read from the environment by b200_conv2d_create (all
+ * optional; a value a plan cannot honour is ignored; results never change, only speed):
+ *   B200_IGEMM_BN=<16..256, multiple of 16>  output channels per tile
+ *   B200_IGEMM_GROUPS=<2|4>                  epilogue groups (4 needs four accumulators in tensor memory)
+ *   B200_IGEMM_ACC=<2|4>                     accumulator stages in tensor memory
+ *   B200_IGEMM_KGROUP=<1..10>                k-blocks per pipeline stage (must divide a tile's k-blocks)
+ *   B200_IGEMM_MMA_WARPS=<1|2>               MMA-issuing warps
+ *   B200_IGEMM_PAIR=0                        never pair tiles on one weight tile */
 #define B200_CONV_ALGO_AUTO 0
 #define B200_CONV_ALGO_DIRECT 1 /* CUDA-core dp4a kernel: any group, any channel count   */
 #define B200_CONV_ALGO_IGEMM 2  /* tcgen05 kind::i8 implicit GEMM: group 1, c % 16 == 0, k % 16 == 0 */
@@ -151,15 +168,25 @@ B200_API int b200_conv2d_destroy(b200_conv_t *conv);
  * refused with B200_ERR_INVALID) -- and keeps that tensor in a fixed 32 MiB device array inside
  * the library instead of growing one with cudaMalloc.  The call fails with B200_ERR_UNSUPPORTED
  * when n * h * ow * 32 bytes exceed 32 MiB (41 images of a 224x224 stride-2 stem).  It makes no
- * cudaMalloc / cudaFree and calls no allocating routine.
- * - The first call on a device looks up the array's device address; make that call outside any
- *   stream capture.  Every GPU the library is used on holds the 32 MiB until the process exits.
+ * cudaMalloc / cudaFree, calls no allocating library routine and, once a given (x, y, n) has been
+ * seen, touches no host heap either (the first call with a new (x, y, n) encodes tensor maps into
+ * storage the plan reserved at creation).
+ * - b200_conv2d_create of such a plan resolves the array's device address and does the kernels'
+ *   one-time set-up on the device that is current then, so that this entry point has nothing left to
+ *   set up there.  On any other device the first call does it: make that call during preparation,
+ *   outside any stream capture.  Every GPU the array is resolved on holds the 32 MiB until the process exits.
  * - All calls on a device share the one array: two calls whose kernels overlap on the GPU (different
  *   streams, no dependency between them) race on it.  Calls on one stream are safe.
- * - A bounded device-side wait that runs out is recorded in the array's own status word, which each
- *   call clears first; b200_device_status does not report it. */
+ * - A bounded device-side wait that runs out is recorded in the array's own status word, not in the
+ *   one b200_device_status reads: check it with b200_static_scratch_status, which allocates nothing. */
 B200_API int b200_conv2d_run_static_scratch(
     b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, b200_stream_t stream);
+
+/* No counterpart in the reference.  Synchronizes `stream`, copies the static scratch array's status
+ * word (4 bytes) into *status_word and, if it is not zero, clears it and returns
+ * B200_ERR_DEVICE_WAIT: some b200_conv2d_run_static_scratch call since the last check had a device-side
+ * wait run out and its output is not valid.  B200_OK with *status_word == 0 otherwise. */
+B200_API int b200_static_scratch_status(b200_stream_t stream, int *status_word);
 
 /* Residual add fused into the conv (no such op in the reference's CPU module; its GPU module
  * fuses ReLU into conv and eltwise the same way, python/nart/modules/cuda_quant.py:300-330).

@@ -50,6 +50,7 @@ SIGNATURES = {
     "b200_stream_destroy": (C.c_int, [vp]),
     "b200_stream_synchronize": (C.c_int, [vp]),
     "b200_device_status": (C.c_int, [vp, C.POINTER(C.c_int)]),
+    "b200_selftest_wait_expiry": (C.c_int, [C.c_uint64, vp]),
     "b200_get_quant_scale": (None, [f32, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int8)]),
     "b200_conv2d_create": (C.c_int, [C.POINTER(ConvParams), vp, vp, C.POINTER(vp)]),
     "b200_conv2d_out_dims": (C.c_int, [vp, pi32, pi32]),
@@ -59,6 +60,7 @@ SIGNATURES = {
     "b200_conv2d_reserve": (C.c_int, [vp, i32]),
     "b200_conv2d_destroy": (C.c_int, [vp]),
     "b200_conv2d_run_static_scratch": (C.c_int, [vp, vp, i32, vp, vp]),
+    "b200_static_scratch_status": (C.c_int, [vp, C.POINTER(C.c_int)]),
     "b200_conv2d_fuse_residual_add": (C.c_int, [vp, i32, C.POINTER(f32), C.POINTER(u8), C.POINTER(f32), f32, u8, u8,
                                                i32]),
     "b200_conv2d_run_residual": (C.c_int, [vp, vp, i32, vp, vp, vp]),

@@ -82,8 +82,10 @@ def build_library(force: bool = False) -> str:
 
 def art_include_dirs() -> list[str] | None:
     """Include directories of the art runtime (the plugin's ABI headers).  They belong to the
-    reference project and are used where they lie; ``NART_ART_ROOT`` names its ``art`` folder."""
-    root = os.environ.get("NART_ART_ROOT", "/root/reference/art")
+    reference project and are used where they lie; ``NART_ART_ROOT`` names its ``art`` folder (default:
+    a checkout called ``reference`` beside this repository).  None when there is no such folder: the
+    plugin is then not rebuilt."""
+    root = os.environ.get("NART_ART_ROOT") or os.path.join(os.path.dirname(ROOT), "reference", "art")
     inc = os.path.join(root, "include")
     if not os.path.exists(os.path.join(inc, "art", "module.h")):
         return None

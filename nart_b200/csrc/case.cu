@@ -514,8 +514,14 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         return B200_OK;
     // the legacy default stream cannot be captured: graph mode needs a stream of its own
     if (!cs->use_graph || cs->profiling || stream == nullptr) {
-        if (cs->profiling || !cs->after_inputs)
-            return run_eager(cs, batch, stream);
+        if (cs->profiling || !cs->after_inputs) {
+            // one whole pass (the event pairs of the profiler bracket every launch in order); a pipelined
+            // caller may refill the input staging buffer once this pass is through
+            const int rc = run_eager(cs, batch, stream);
+            if (rc == B200_OK && cs->after_inputs)
+                B200_CUDA_TRY(cudaEventRecord(cs->after_inputs, as_stream(stream)));
+            return rc;
+        }
         B200_TRY(run_eager(cs, batch, stream, 1));
         B200_CUDA_TRY(cudaEventRecord(cs->after_inputs, as_stream(stream)));
         return run_eager(cs, batch, stream, 2);

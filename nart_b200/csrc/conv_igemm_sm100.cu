@@ -59,6 +59,7 @@ constexpr int kErrProducerWait = 0x101;
 constexpr int kErrMmaFullWait = 0x102;
 constexpr int kErrMmaTmemWait = 0x103;
 constexpr int kErrEpilogueWait = 0x104;
+constexpr int kErrSelfTestWait = 0x1ff;   // wait_expiry_probe_kernel
 
 struct alignas(64) IgemmMaps {
     CUtensorMap a[4];   // activations, one per (row parity, column parity) of a strided conv
@@ -183,7 +184,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
 }
 // Bounded wait: returns false when the barrier did not flip within kWaitCycles or another role
 // has already given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, long long limit = kWaitCycles)
 {
     if (mbar_try_wait(bar, parity))
         return true;
@@ -191,7 +192,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     int spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 255) == 0) {
-            if (*abort_flag != 0 || clock64() - t0 > kWaitCycles)
+            if (*abort_flag != 0 || clock64() - t0 > limit)
                 return false;
         }
     }
@@ -929,6 +930,27 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
     }
 }
 
+// The give-up path of the bounded waits, on its own: one warp waits, through the same mbar_wait the
+// convolution's roles use, on a barrier that nothing will ever arrive at, with the caller's (short)
+// limit.  When the limit is reached the wait returns false, the code goes to the status word and the
+// kernel ends normally -- no trap, nothing left waiting.
+__global__ void __launch_bounds__(32) wait_expiry_probe_kernel(int *status, long long limit_cycles)
+{
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, limit_cycles);
+    if (!__all_sync(0xffffffffu, ok) && threadIdx.x == 0) {
+        atomicCAS(status, 0, kErrSelfTestWait);
+        abort_flag = 1;
+    }
+}
+
 // ---- host side -------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(
     CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -1012,6 +1034,7 @@ struct ConvIgemmPlan {
         IgemmArgs args;
         dim3 grid;
     };
+    static constexpr size_t kMaxSaved = 8;
     std::vector<Saved> saved;
     size_t next_saved = 0;
 };
@@ -1083,6 +1106,7 @@ int conv_igemm_create(
     }
     ConvIgemmPlan *p = new ConvIgemmPlan();
     p->g = g;
+    p->saved.reserve(ConvIgemmPlan::kMaxSaved);   // launches never grow it: a later run touches no heap
     p->a_wide = a_row_swizzled ? 1 : 0;
     // K of an 8-bit MMA is 32 bytes: the channel count is rounded up to a multiple of 32 in the
     // repacked weights (zero weights); on the activation side the TMA box runs past the tensor's
@@ -1440,11 +1464,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     }
     p->smem = smem_layout((p->pair ? 2 : 1) * p->stages * p->kgroup, p->b_resident ? g.r * g.s * (p->cpad / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024;
     if (!p->attr_set) {
-        B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
-        B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
-        B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
+        B200_TRY(conv_igemm_warm());
         p->attr_set = true;
     }
     p->last_x = x;
@@ -1484,12 +1504,11 @@ int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cud
         if (!hit) {
             B200_TRY(build_launch(p, x, n, y, status_word, res));
             ConvIgemmPlan::Saved sv = { x, res, y, n, status_word, p->maps, p->args, p->grid };
-            constexpr size_t kMaxSaved = 8;
-            if (p->saved.size() < kMaxSaved) {
+            if (p->saved.size() < ConvIgemmPlan::kMaxSaved) {
                 p->saved.push_back(sv);
             } else {
                 p->saved[p->next_saved] = sv;
-                p->next_saved = (p->next_saved + 1) % kMaxSaved;
+                p->next_saved = (p->next_saved + 1) % ConvIgemmPlan::kMaxSaved;
             }
         }
     }
@@ -1506,6 +1525,30 @@ int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cud
         conv_igemm_i8_kernel<false, false, 1><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args);
     else
         conv_igemm_i8_kernel<false><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+// Everything the first launch of any plan would otherwise do once per process or device: the driver
+// entry point of the tensor-map encoder and the kernels' shared-memory attribute (which also loads
+// this module's code onto the current device).  Called at plan creation, while allocation is allowed.
+int conv_igemm_warm()
+{
+    if (!encode_fn())
+        return fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    B200_CUDA_TRY(cudaFuncSetAttribute(conv_igemm_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
+    B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
+    B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
+    return B200_OK;
+}
+
+int wait_expiry_probe_launch(long long limit_cycles, cudaStream_t st)
+{
+    int *status = nullptr;
+    B200_TRY(status_word_ptr(&status));
+    wait_expiry_probe_kernel<<<1, 32, 0, st>>>(status, limit_cycles);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

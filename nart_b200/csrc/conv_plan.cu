@@ -220,6 +220,11 @@ int b200_conv2d_create(
             cv->algo = B200_CONV_ALGO_IGEMM;
             cv->lowered = true;
             cv->g_low = gl;
+            // for callers of b200_conv2d_run_static_scratch: everything that entry point would otherwise do
+            // once per device (kernel set-up, the static array's address) happens here, where allocation is
+            // allowed; a failure only matters to that entry point, which reports it itself
+            if (conv_igemm_warm() != B200_OK || conv_static_scratch_prepare() != B200_OK)
+                cudaGetLastError();
         } else if (rc != B200_ERR_UNSUPPORTED || p->algo == B200_CONV_ALGO_IGEMM) {
             destroy_conv(cv);
             return rc;

@@ -327,7 +327,13 @@ int eltwise_prepare(
             return fail(B200_ERR_UNSUPPORTED, "eltwise: per-input shift %d outside 1..30", b);
         a.m[i] = (int)m[i];
         a.b[i] = b;
-        a.add[i] = (int)((1ll << (b - 1)) - (long long)izp[i] * (long long)m[i]);
+        const long long add = (1ll << (b - 1)) - (long long)izp[i] * (long long)m[i];
+        // the kernels form x * m + add in int32 where the reference's rshift_rn works on int64
+        // (quant_helper.h:55-58): decline what would not fit (shifts of 25 and more with a small zero point)
+        const long long hi = 255ll * (long long)m[i] + add, lo = add;
+        if (hi >= (1ll << 31) || lo < -(1ll << 31))
+            return fail(B200_ERR_UNSUPPORTED, "eltwise: input %d needs more than 32 bits before its shift of %d (scale ratio too extreme)", i, b);
+        a.add[i] = (int)add;
     }
     {
         long long worst = 1ll << (s0 - 1);

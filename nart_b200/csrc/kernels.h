@@ -124,6 +124,13 @@ int conv_igemm_launch(ConvIgemmPlan *plan, const uint8_t *x, int n, uint8_t *y, 
 // plan's epilogue form cannot take it (the caller then keeps the separate eltwise kernel).
 int conv_igemm_set_residual(ConvIgemmPlan *plan, const EltwiseArgs &e, int conv_input);
 void conv_igemm_destroy(ConvIgemmPlan *plan);
+// Per-process / per-device set-up of the tensor-core kernels (driver entry point, shared-memory
+// attribute): done by the first launch otherwise; plan creation calls it so that runs do not.
+int conv_igemm_warm();
+// Launches the one-warp kernel whose bounded wait cannot be satisfied (see b200_selftest_wait_expiry).
+int wait_expiry_probe_launch(long long limit_cycles, cudaStream_t st);
+// Resolves the device address of the static scratch array for the current device (conv_static_scratch.cu).
+int conv_static_scratch_prepare();
 
 }  // namespace b200
 

@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "kernels.h"
 
 namespace b200 {
 
@@ -239,6 +240,13 @@ int b200_device_status(b200_stream_t stream, int *status_word)
     if (*status_word != 0)
         B200_CUDA_TRY(cudaMemset(p, 0, sizeof(int)));
     return B200_OK;
+}
+
+int b200_selftest_wait_expiry(uint64_t limit_cycles, b200_stream_t stream)
+{
+    if (limit_cycles == 0 || limit_cycles > 2000000000ull)
+        return fail(B200_ERR_INVALID, "selftest: limit of %llu cycles outside 1..2e9 (about one second)", (unsigned long long)limit_cycles);
+    return wait_expiry_probe_launch((long long)limit_cycles, as_stream(stream));
 }
 
 void b200_get_quant_scale(float x, int bits, uint32_t *mult, int8_t *shift)

@@ -2,9 +2,9 @@
 stride on the 3x3) and MobileNetV2-1.0, as flat op lists ("specs") with seeded random int8
 weights and per-tensor activation scales / zero points.
 
-A spec is backend-neutral: ``to_case`` turns it into a GPU case through the C-ABI, ``run_cpu`` walks
-it op by op over any object that offers the quant ops on NCHW numpy arrays (the tests pass the CPU
-checkers in).  BatchNorm is assumed folded into the convs, the way the reference's exporter emits
+A spec is backend-neutral and building one loads no native library: ``to_case`` turns it into a
+GPU case through the C-ABI (and loads ``libnart_b200.so`` when called); the tests walk the same spec
+op by op over their CPU checkers.  BatchNorm is assumed folded into the convs, the way the reference's exporter emits
 quantized cases (python/nart/modules/quant.py of ModelTC/NART); ReLU after a conv or a residual
 add is the fused clamp at the output zero point.
 """
@@ -14,7 +14,10 @@ import math
 
 import numpy as np
 
-from ._lib import ALGO_AUTO, POOL_AVE, POOL_MAX
+# SETTING_POOL_MAX / SETTING_POOL_AVE (art/include/art/op_settings.h:62-63) and B200_CONV_ALGO_AUTO; the
+# same values as in ._lib, repeated here so that importing this module loads no shared library
+POOL_MAX, POOL_AVE = 0, 1
+ALGO_AUTO = 0
 
 
 class SpecBuilder:
@@ -39,7 +42,7 @@ class SpecBuilder:
         return "%s%d" % (kind, self._n)
 
     def _out_quant(self, real_std, relu):
-        """Output scale / zero point / spread estimate.  BASELINE: alpha ~ U(0.01, 0.1),
+        """Output scale / zero point / spread estimate.  Benchmark form: alpha ~ U(0.01, 0.1),
         zp ~ U{0..255}.  With random weights that saturates most outputs, so the parity nets use
         ``spread``: a scale matched to the estimated spread of the real values, which keeps the
         quantized values distributed over the range layer after layer."""
@@ -232,53 +235,3 @@ def to_case(spec, max_batch: int, algo: int = ALGO_AUTO, output_f32: bool = True
         cs.output_u8(ids[name])
     cs.prepare(max_batch)
     return cs, ids
-
-
-def run_cpu(spec, x, backend, per_channel: bool = True, keep=()):
-    """Walks the spec with ``backend`` (an object offering conv2d_u8 / ip_u8 / pool_u8 /
-    eltwise_sum_u8 / relu_u8 / dequantize_u8 on NCHW numpy arrays).  ``per_channel`` False passes
-    only walpha[0], which is all the reference module reads.  Returns (float32 logits, uint8 output,
-    {name: tensor} for the names in ``keep``)."""
-    T = spec["tensors"]
-    vals = {"input": np.ascontiguousarray(x, dtype=np.uint8)}
-    kept = {}
-    last_use = {}
-    for i, op in enumerate(spec["ops"]):
-        for n in op["ins"]:
-            last_use[n] = i
-    for i, op in enumerate(spec["ops"]):
-        ti, to = T[op["ins"][0]], T[op["out"]]
-        xin = vals[op["ins"][0]]
-        if op["op"] in ("conv", "ip"):
-            wa = op["walpha"] if per_channel else op["walpha"][:1]
-            if op["op"] == "conv":
-                kw = dict(relu=op["relu"]) if per_channel else {}
-                y = backend.conv2d_u8(xin, op["w"], op["bias"], (op["stride"],) * 2, (op["pad"],) * 2, op["group"],
-                                      ialpha=ti["alpha"], izp=ti["zp"], walpha=wa if per_channel else float(wa[0]),
-                                      wzp=128, oalpha=to["alpha"], ozp=to["zp"], **kw)
-                if not per_channel and op["relu"]:
-                    y = backend.relu_u8(y, to["alpha"], to["zp"], to["alpha"], to["zp"])
-            else:
-                y = backend.ip_u8(xin.reshape(xin.shape[0], -1), op["w"], op["bias"], ti["alpha"], ti["zp"],
-                                  wa if per_channel else float(wa[0]), 128, to["alpha"], to["zp"])
-                y = y.reshape(y.shape[0], -1, 1, 1)
-        elif op["op"] == "pool":
-            y = backend.pool_u8(xin, op["method"], (op["ksize"],) * 2, (op["pad"],) * 2, (op["stride"],) * 2,
-                                op["ceil_mode"], ti["alpha"], ti["zp"], to["alpha"], to["zp"])
-        elif op["op"] == "eltwise":
-            ins = [T[n] for n in op["ins"]]
-            y = backend.eltwise_sum_u8([vals[n] for n in op["ins"]], [t["alpha"] for t in ins],
-                                       [t["zp"] for t in ins], to["alpha"], to["zp"])
-            if op["relu"]:
-                y = backend.relu_u8(y, to["alpha"], to["zp"], to["alpha"], to["zp"])
-        else:
-            raise ValueError(op["op"])
-        vals[op["out"]] = y
-        if op["out"] in keep:
-            kept[op["out"]] = y
-        for n in op["ins"]:
-            if last_use.get(n) == i and n != spec["output"] and n in vals:
-                del vals[n]
-    out = T[spec["output"]]
-    q = vals[spec["output"]]
-    return backend.dequantize_u8(q, out["alpha"], out["zp"]), q, kept

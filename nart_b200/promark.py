@@ -16,7 +16,7 @@ reference's benchmark driver (tools/promark.cpp:208-522 of ModelTC/NART):
 
 promark's `-c` (runtime JSON choosing the modules) has no meaning here: this driver always runs the
 b200 case runner.  To run the same file through the reference's own parade, list "b200" in the
-runtime JSON of the reference's promark (see INTEGRATION.md).
+runtime JSON of the reference's promark.
 """
 from __future__ import annotations
 

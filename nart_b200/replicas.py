@@ -59,6 +59,22 @@ def sum_over_ranks(value: float, device="cpu") -> float:
     return float(t.item())
 
 
+def all_ranks_hold(payload: bytes, device="cpu") -> bool:
+    """True when every rank passed the same bytes (at most 64; a digest): the check that batch-sharded
+    replicas given the same images produce the same result.  A single process trivially agrees."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return True
+    if len(payload) > 64:
+        raise ValueError("pass a digest, not the data")
+    buf = bytes(payload).ljust(64, b"\0")
+    mine = torch.tensor(list(buf), dtype=torch.uint8, device=device)
+    gathered = [torch.empty_like(mine) for _ in range(dist.get_world_size())]
+    dist.all_gather(gathered, mine)
+    return all(bool(torch.equal(g, gathered[0])) for g in gathered)
+
+
 def images_per_sec(images_this_rank: int, steps: int, elapsed_ms_this_rank: float, device="cpu") -> float:
     """Whole-job throughput: all ranks' images over the slowest rank's time."""
     total = sum_over_ranks(images_this_rank * steps, device)

@@ -31,10 +31,21 @@ _i32p = C.POINTER(C.c_int32)
 _f32p = C.POINTER(C.c_float)
 
 
+def reference_root() -> str | None:
+    """Folder of the reference project's checkout when it is present on this machine: ``$NART_REF_ROOT``,
+    else a folder called ``reference`` beside this repository.  None elsewhere (the GPU boxes)."""
+    cand = os.environ.get("NART_REF_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return cand if os.path.exists(os.path.join(cand, "art", "src", "op.c")) else None
+
+
 def build(ref: bool | None = None) -> None:
     """Compile the restatement, and the reference when its sources are present."""
     target = "all" if ref is None else ("all" if ref else "port")
-    subprocess.check_call(["make", "-s", "-C", _HERE, target])
+    cmd = ["make", "-s", "-C", _HERE, target]
+    root = reference_root()
+    if root is not None:
+        cmd.append("REF=" + root)
+    subprocess.check_call(cmd)
 
 
 def _p(a, tp):

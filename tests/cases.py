@@ -1,11 +1,11 @@
-"""Seeded synthetic inputs shared by the CPU and GPU tests (BASELINE configs 0 and 1 and the small
+"""Seeded synthetic inputs shared by the CPU and GPU tests (the single 3x3 conv on 56x56, the conv shape sweep and the small
 edge-case shapes).  Everything is drawn from numpy's default_rng(seed)."""
 import numpy as np
 
 
 def conv_inputs(seed, n, c, h, w, k, r, s, group=1, per_channel=True):
     """uint8 activations U[0,255]; int8 weights U[-127,127] stored +128; int32 bias U[-4096,4096];
-    per-channel weight scales U(0.001, 0.01) (BASELINE config 0)."""
+    per-channel weight scales U(0.001, 0.01)."""
     rng = np.random.default_rng(seed)
     x = rng.integers(0, 256, (n, c, h, w), dtype=np.uint8)
     wt = (rng.integers(-127, 128, (k, c // group, r, s)) + 128).astype(np.uint8)
@@ -19,7 +19,7 @@ def conv_inputs(seed, n, c, h, w, k, r, s, group=1, per_channel=True):
 # (n, c, h, w, k, r, s, stride, pad, group) -- edge shapes: odd sizes, ragged channel counts,
 # grouped, depthwise, stem, tiny maps, asymmetric kernels
 EDGE_SHAPES = [
-    (1, 64, 56, 56, 64, 3, 3, 1, 1, 1),      # BASELINE config 0
+    (1, 64, 56, 56, 64, 3, 3, 1, 1, 1),      # the single-conv benchmark case
     (2, 32, 9, 9, 32, 3, 3, 1, 1, 1),
     (3, 16, 7, 5, 48, 1, 1, 1, 0, 1),
     (2, 32, 11, 13, 16, 3, 3, 2, 1, 1),
@@ -33,6 +33,6 @@ EDGE_SHAPES = [
     (5, 64, 7, 7, 64, 3, 3, 2, 1, 1),
 ]
 
-# BASELINE config 1 shapes: (c, k, h) x kernel {1,3} x stride {1,2}
+# conv shape sweep: (c, k, h) x kernel {1,3} x stride {1,2}
 SWEEP = [(c, k, h, ks, st) for (c, k, h) in [(64, 64, 56), (128, 128, 28), (256, 256, 14), (512, 512, 7)]
          for ks in (1, 3) for st in (1, 2)]

@@ -24,7 +24,7 @@ def port():
 def ref():
     import oracle
     if not oracle.have_ref():
-        if os.path.exists("/root/reference/art/src/op.c"):
+        if oracle.reference_root() is not None:
             oracle.build(ref=True)
         else:
             pytest.skip("the compiled reference (oracle/_ref) is not available on this machine")

@@ -44,7 +44,7 @@ def main():
     out["rshift_x"], out["rshift_b"] = xs, bs
     out["rshift_y"] = np.array([R.rshift_rn(int(a), int(b)) for a, b in zip(xs, bs)], dtype=np.int64)
 
-    # ---- conv: BASELINE config 0, per-tensor / per-channel / fused relu ------------------------
+    # ---- conv: 64 -> 64 channels, 3x3 on 56x56, per-tensor / per-channel / fused relu ------------------------
     n, c, h, w, k, r, s, st, pd, g = EDGE_SHAPES[0]
     x, wt, bias, walpha = conv_inputs(0, n, c, h, w, k, r, s, g)
     q = dict(ialpha=0.02, izp=128, wzp=128, oalpha=0.05, ozp=0)

@@ -78,3 +78,21 @@ def test_pool_out_dims_follow_reference_shape_rule(L):
     assert (oh.value, ow.value) == (56, 56)
     assert L.lib.b200_pool_out_dims(14, 14, 3, 3, 1, 1, 2, 2, 1, C.byref(oh), C.byref(ow)) == 0
     assert (oh.value, ow.value) == tuple(GOLD["pool_max_ceil"].shape[2:])
+
+
+def test_eltwise_refuses_terms_that_would_not_fit_32_bits(L):
+    """Argument checks that precede any CUDA call (count == 0: nothing is launched).  The kernels form
+    x * m + add in int32; a scale ratio of 2^27 between the inputs would need more (the reference's
+    rshift_rn works on int64), so such an op is declined instead of computed differently."""
+    x = (C.c_void_p * 2)(256, 512)          # aligned dummies; never dereferenced with count == 0
+    izp = (C.c_uint8 * 2)(0, 0)
+    ok = (C.c_float * 2)(0.02, 0.02 * 1024)
+    assert L.lib.b200_eltwise_sum_u8(x, 2, 0, ok, izp, None, 0.05, 3, 8, 0, 1024, None) == L.OK
+    extreme = (C.c_float * 2)(0.02, 0.02 * 2.0 ** 27)
+    rc = L.lib.b200_eltwise_sum_u8(x, 2, 0, extreme, izp, None, 0.05, 3, 8, 0, 1024, None)
+    assert rc == L.ERR_UNSUPPORTED, L.lib.b200_last_error()
+
+
+def test_selftest_argument_check(L):
+    assert L.lib.b200_selftest_wait_expiry(0, None) == L.ERR_INVALID
+    assert L.lib.b200_selftest_wait_expiry(3_000_000_000, None) == L.ERR_INVALID

@@ -1,5 +1,6 @@
 """CPU, world_size 2 over gloo: the replica plumbing bench.py uses at N > 1 -- shard ownership, the
-max-over-ranks clock and the aggregate throughput."""
+max-over-ranks clock, the aggregate throughput and the check that every replica produced the same
+logits for the same batch."""
 import os
 import socket
 
@@ -38,7 +39,9 @@ def _worker(rank, world, port, out):
     elapsed_ms = 100.0 * (rank + 1)            # rank 1 is the slow one
     slowest = replicas.max_over_ranks(elapsed_ms)
     ips = replicas.images_per_sec(256, 10, elapsed_ms)
-    out.put((rank, slowest, ips))
+    same = replicas.all_ranks_hold(b"digest-of-the-logits")
+    differ = replicas.all_ranks_hold(b"rank %d" % rank)
+    out.put((rank, slowest, ips, same, differ))
     import torch.distributed as dist
     dist.destroy_process_group()
 
@@ -54,6 +57,7 @@ def test_two_ranks_agree_on_the_slowest_clock_and_the_aggregate():
     for p in procs:
         p.join(60)
         assert p.exitcode == 0
-    for rank, slowest, ips in got:
+    for rank, slowest, ips, same, differ in got:
         assert slowest == 200.0
         assert abs(ips - 2 * 256 * 10 / 0.2) < 1e-6
+        assert same is True and differ is False      # every rank learns whether the replicas agree

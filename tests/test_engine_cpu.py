@@ -7,6 +7,7 @@ import numpy as np
 import pytest
 
 from nart_b200 import engine, nets
+from oracle.net_walk import run_net
 
 
 def test_constants_match_the_reference_headers(ref):
@@ -41,5 +42,5 @@ def test_written_case_runs_on_the_reference_parade(ref, tmp_path):
     x = np.random.default_rng(3).integers(0, 256, (1, 3, 96, 96), dtype=np.uint8)
     ref.use_module()
     (got,) = ref.run_engine(path, [x], [np.float32])
-    want, _, _ = nets.run_cpu(spec, x, ref, per_channel=False)
+    want, _, _ = run_net(spec, x, ref, per_channel=False)
     np.testing.assert_array_equal(got.view(np.uint32), want.reshape(-1).view(np.uint32))

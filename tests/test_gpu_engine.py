@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 
 from gpu_util import assert_same
+from oracle.net_walk import run_net
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -21,7 +22,7 @@ def test_engine_file_on_the_case_runner(port, tmp_path, depth, relu_flag):
     path = os.path.join(tmp_path, "engine.bin")
     engine.write_engine(spec, path, batch=3, per_channel=True, conv_relu_flag=relu_flag)
     x = np.random.default_rng(depth).integers(0, 256, (3, 3, 64, 64), dtype=np.uint8)
-    want, _, _ = nets.run_cpu(spec, x, port)
+    want, _, _ = run_net(spec, x, port)
     cs, outs = engine.engine_to_case(engine.read_engine(path), 4)
     assert outs == [(True, (40, 1, 1))]
     (got,) = cs.run_host([x], [(np.float32, (40, 1, 1))])
@@ -37,7 +38,7 @@ def test_engine_file_through_the_reference_parade_on_the_plugin(ref, port, tmp_p
     path = os.path.join(tmp_path, "engine.bin")
     engine.write_engine(spec, path, batch=2, per_channel=True, conv_relu_flag=True)
     x = np.random.default_rng(8).integers(0, 256, (2, 3, 64, 64), dtype=np.uint8)
-    want, _, _ = nets.run_cpu(spec, x, port)
+    want, _, _ = run_net(spec, x, port)
     ref.use_module(PLUGIN, "b200_module_tp", whole_batch=True)
     try:
         (got,) = ref.run_engine(path, [x], [np.float32])
@@ -60,7 +61,7 @@ def test_promark_cli(port, tmp_path, monkeypatch, capsys):
     text = capsys.readouterr().out
     assert "input tensors:" in text and "Process 1 : cost" in text and "average cost" in text
     got = np.fromfile(os.path.join(tmp_path, "nart-out-logits.bin"), dtype=np.float32)
-    want, _, _ = nets.run_cpu(spec, x, port)
+    want, _, _ = run_net(spec, x, port)
     assert_same(got.view(np.uint32), want.reshape(-1).view(np.uint32), "promark -s")
     assert promark.main(["-m", path, "-n", "2", "-b", "4", "-d"]) == 0      # device-resident timing, other batch
 
@@ -86,7 +87,7 @@ def test_promark_reshape(port, tmp_path, monkeypatch, capsys):
     monkeypatch.chdir(tmp_path)
     assert promark.main(["-m", path, "-n", "1", "-r", "%s:3,3,24,20" % name, "-s", "-i", "in.bin"]) == 0
     assert "%s: 3, 3, 24, 20" % name in capsys.readouterr().out
-    want, _, _ = nets.run_cpu(large, x, port)          # the file's output is the dequantized last tensor
+    want, _, _ = run_net(large, x, port)          # the file's output is the dequantized last tensor
     out_name = engine.read_engine(path)["outputs"][0]["name"].replace("/", "_")
     got = np.fromfile(os.path.join(tmp_path, "nart-out-%s.bin" % out_name), dtype=np.float32)
     assert got.size == want.size == 3 * 48 * 6 * 5

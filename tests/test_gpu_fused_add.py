@@ -6,6 +6,7 @@ import pytest
 
 from cases import conv_inputs
 from gpu_util import assert_same, to_dev_nhwc, to_host_nchw
+from oracle.net_walk import run_net
 
 pytestmark = pytest.mark.gpu
 
@@ -88,7 +89,7 @@ def test_case_fusion_on_and_off_agree(port):
     from nart_b200 import nets
     spec = nets.resnet(50, seed=12, hw=64, width_div=2, spread=True, num_classes=64)
     x = np.random.default_rng(9).integers(0, 256, (3, 3, 64, 64), dtype=np.uint8)
-    want_logits, _, _ = nets.run_cpu(spec, x, port)
+    want_logits, _, _ = run_net(spec, x, port)
     outs, launches = [], []
     for fuse in (True, False):
         cs, ids = nets.to_case(spec, 4, fuse=fuse)

@@ -22,8 +22,6 @@ def ops():
 
 def algos_for(ops, c, k, group):
     a = [ops.ALGO_DIRECT]
-    if os.environ.get("B200_TEST_ALGOS") == "direct":   # debugging aid: CUDA-core path only
-        return a
     if group == 1 and c % 16 == 0 and k % 16 == 0:
         a.append(ops.ALGO_IGEMM)
     return a
@@ -78,13 +76,37 @@ def test_conv_accumulators(ops, port):
 @pytest.mark.parametrize("c,k,h,ks,st", SWEEP)
 @pytest.mark.parametrize("batch", [1, 3])
 def test_conv_sweep_shapes(ops, port, c, k, h, ks, st, batch):
-    """BASELINE config 1 shapes at small batch (the restatement finishes in seconds)."""
+    """The single-conv sweep shapes at small batch (the restatement finishes in seconds)."""
     x, wt, bias, walpha = conv_inputs(c + h + ks + st, batch, c, h, h, k, ks, ks)
     q = dict(ialpha=0.02, izp=128, wzp=128, oalpha=0.05 * np.sqrt(c * ks * ks) / 8, ozp=0)
     want = port.conv2d_u8(x, wt, bias, (st, st), (ks // 2, ks // 2), 1, walpha=walpha, relu=True, **q)
     for algo in algos_for(ops, c, k, 1):
         y = run_conv(ops, x, wt, bias, st, ks // 2, 1, algo, walpha=walpha, relu=True, **q)
         assert_same(y, want, "sweep algo%d" % algo)
+
+
+@pytest.mark.parametrize("c,k,h,ks,st", SWEEP)
+@pytest.mark.parametrize("batch", [32, 256])
+def test_conv_sweep_shapes_at_bench_batches(ops, port, c, k, h, ks, st, batch):
+    """The same 16 shapes at the batches the throughput figures are quoted on.  Batch changes the
+    M-tile box, the grid and the number of tiles a CTA walks, so these are kernel configurations of
+    their own.  The whole output goes through the tensor-core path; images from both ends, the middle
+    and either side of a tile boundary are compared with the restatement (every image of a conv is
+    independent of the others), and the full tensor must equal a second run."""
+    x, wt, bias, walpha = conv_inputs(1000 + c + h + ks + st + batch, batch, c, h, h, k, ks, ks)
+    q = dict(ialpha=0.02, izp=128, wzp=128, oalpha=0.05 * np.sqrt(c * ks * ks) / 8, ozp=0)
+    conv = ops.Conv2d(wt, bias, in_hw=(h, h), stride=(st, st), pad=(ks // 2, ks // 2), group=1, algo=ops.ALGO_IGEMM,
+                      walpha=walpha, relu=True, **q)
+    xd = to_dev_nhwc(x)
+    y1 = conv(xd)
+    y2 = conv(xd)
+    assert ops.device_status() == 0
+    assert bool((y1 == y2).all())
+    pick = sorted({0, 1, batch // 2 - 1, batch // 2, batch - 2, batch - 1})
+    want = port.conv2d_u8(x[pick], wt, bias, (st, st), (ks // 2, ks // 2), 1, walpha=walpha, relu=True, **q)
+    got = to_host_nchw(y1[pick])
+    assert_same(got, want, "sweep c%d h%d k%dx%d s%d batch %d" % (c, h, ks, ks, st, batch))
+    assert len(np.unique(want)) > 16
 
 
 def test_conv_large_scale_generic_requant_path(ops, port):
@@ -338,3 +360,43 @@ def test_conv_channels_not_multiple_of_32_on_tensor_cores(ops, port, c, k, ks, s
                           relu=True)
     got = run_conv(ops, x, wt, bias, st, pd, 1, ops.ALGO_IGEMM, relu=True, **q)
     assert_same(got, want, "c=%d k=%d %dx%d s%d" % (c, k, ks, ks, st))
+
+
+def test_bounded_wait_expiry_is_reported_and_the_context_survives(ops, port):
+    """The give-up path of the kernels' bounded waits, exercised the harmless way: a one-warp kernel
+    waits on a barrier nothing arrives at, with a limit of about a millisecond; it gives up, writes its
+    code to the device status word and ends normally.  The status call reports the code once, a case run
+    that follows such a kernel returns B200_ERR_DEVICE_WAIT, and ordinary work is correct afterwards."""
+    import ctypes as C
+    import time
+    import torch
+    from nart_b200 import nets
+    from nart_b200._lib import B200Error, ERR_DEVICE_WAIT, ERR_INVALID, check, lib
+    from oracle.net_walk import run_net
+    side = torch.cuda.Stream()
+    stream = side.cuda_stream
+    assert ops.device_status() == 0
+    assert lib.b200_selftest_wait_expiry(0, stream) == ERR_INVALID
+    t = time.perf_counter()
+    check(lib.b200_selftest_wait_expiry(2_000_000, stream))
+    word = C.c_int(0)
+    check(lib.b200_device_status(stream, C.byref(word)))
+    assert time.perf_counter() - t < 5.0           # about a millisecond of waiting, not the kernels' two seconds
+    assert word.value == 0x1FF
+    check(lib.b200_device_status(stream, C.byref(word)))
+    assert word.value == 0                          # reading clears it
+
+    # the host-buffer entry point of a case maps the word to the error status
+    spec = nets.resnet(18, seed=31, hw=32, width_div=4, spread=True, num_classes=10)
+    x = np.random.default_rng(12).integers(0, 256, (2, 3, 32, 32), dtype=np.uint8)
+    want, _, _ = run_net(spec, x, port)
+    cs, _ = nets.to_case(spec, 2)
+    check(lib.b200_selftest_wait_expiry(1_000_000, stream))
+    with pytest.raises(B200Error) as ei:
+        cs.run_host([x], [(np.float32, (10, 1, 1))], stream)
+    assert ei.value.status == ERR_DEVICE_WAIT
+    # ... and the same case, same context, right after: correct results, clean status
+    (got,) = cs.run_host([x], [(np.float32, (10, 1, 1))], stream)
+    assert_same(got.reshape(want.shape).view(np.uint32), want.view(np.uint32), "after an expired wait")
+    assert ops.device_status() == 0
+    cs.close()

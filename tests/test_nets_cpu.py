@@ -4,6 +4,7 @@ generators are deterministic."""
 import numpy as np
 
 from nart_b200 import nets
+from oracle.net_walk import run_net
 
 
 def test_spec_is_seeded():
@@ -26,8 +27,8 @@ def test_small_resnet_port_equals_reference(port, ref):
     for depth in (18, 50):
         spec = nets.resnet(depth, seed=11, hw=96, width_div=4, spread=True, num_classes=10)
         x = rng.integers(0, 256, (2, 3, 96, 96), dtype=np.uint8)  # maps stay >= 3x3: the reference mis-handles maps smaller than the kernel
-        lp, qp, _ = nets.run_cpu(spec, x, port, per_channel=False)
-        lr, qr, _ = nets.run_cpu(spec, x, ref, per_channel=False)
+        lp, qp, _ = run_net(spec, x, port, per_channel=False)
+        lr, qr, _ = run_net(spec, x, ref, per_channel=False)
         assert np.array_equal(qp, qr)
         assert np.array_equal(lp.view(np.uint32), lr.view(np.uint32))
         assert len(np.unique(qp)) > 4   # the outputs are spread, not saturated
