@@ -113,7 +113,11 @@ B200_API void b200_get_quant_scale(float x, int bits, uint32_t *mult, int8_t *sh
  *   B200_IGEMM_ACC=<2|4>                     accumulator stages in tensor memory
  *   B200_IGEMM_KGROUP=<1..10>                k-blocks per pipeline stage (must divide a tile's k-blocks)
  *   B200_IGEMM_MMA_WARPS=<1|2>               MMA-issuing warps
- *   B200_IGEMM_PAIR=0                        never pair tiles on one weight tile */
+ *   B200_IGEMM_PAIR=0                        never pair tiles on one weight tile
+ *   B200_IGEMM_EPI_CONST=0                   never use the uniform-shift epilogue (per-channel constants as kernel parameters)
+ * and by b200_case_prepare:
+ *   B200_CASE_ZIGZAG=0                       every op walks its tiles first to last (default: each op walks against the
+ *                                            direction of the op that wrote its input, to start on what is still in L2) */
 #define B200_CONV_ALGO_AUTO 0
 #define B200_CONV_ALGO_DIRECT 1 /* CUDA-core dp4a kernel: any group, any channel count   */
 #define B200_CONV_ALGO_IGEMM 2  /* tcgen05 kind::i8 implicit GEMM: group 1, c % 16 == 0, k % 16 == 0 */

@@ -39,6 +39,11 @@ struct CaseOp {
     float oalpha = 1.f;
     uint8_t ozp = 0, obits = 8;
     int relu = 0;
+    // eltwise: the prepared constants (built once in b200_case_prepare)
+    b200::EltwiseArgs elt;
+    bool elt_fast = false;
+    // direction in which the op's kernel walks its tiles: 1 = last to first (see b200_case_prepare)
+    int reverse = 0;
     // relu / max-pool lookup table
     uint8_t lut[256];
     uint8_t *lut_dev = nullptr;
@@ -447,6 +452,42 @@ int b200_case_prepare(b200_case_t *cs, int32_t max_batch)
             B200_CUDA_TRY(cudaMemcpy(op.lut_dev, op.lut, 256, cudaMemcpyHostToDevice));
         }
     }
+    // Zig-zag traversal.  A tensor of this path is larger than what stays in L2 behind its producer, but
+    // the part written last is still there: every op walks its tiles in the direction opposite to the op
+    // that produced its (most recently written) input, so that it starts on that part.  The pools and
+    // the layout kernels always run first to last.  Results do not depend on the direction.
+    {
+        const char *e = getenv("B200_CASE_ZIGZAG");
+        const bool zigzag = !(e && atoi(e) == 0);
+        std::vector<int> dir(cs->tensors.size(), 0);     // direction in which each tensor was written
+        for (auto &op : cs->ops) {
+            if (op.kind == OpKind::Eltwise) {
+                B200_TRY(eltwise_prepare((int)op.ins.size(), op.ialpha.data(), op.izp.data(), op.has_coeff ? op.coeff.data() : nullptr,
+                                         op.oalpha, op.ozp, op.obits, op.relu, &op.elt, &op.elt_fast));
+            }
+            if (op.skipped)
+                continue;
+            int latest = op.ins[0];
+            for (int t : op.ins)
+                latest = t > latest ? t : latest;           // tensor ids grow in creation order
+            if (op.residual >= 0 && op.residual > latest)
+                latest = op.residual;
+            int rev = zigzag ? !dir[latest] : 0;
+            if (op.kind == OpKind::Conv) {
+                // a row-lowered conv reads the scratch tensor its own lowering kernel has just written, first to last
+                if (op.conv->lowered)
+                    rev = zigzag ? 1 : 0;
+                if (op.conv->igemm)
+                    conv_igemm_set_reverse(op.conv->igemm, rev);
+                else
+                    rev = 0;
+            } else if (op.kind != OpKind::Eltwise) {
+                rev = 0;
+            }
+            op.reverse = rev;
+            dir[op.out] = rev;
+        }
+    }
     cs->prepared = true;
     return B200_OK;
 }
@@ -628,9 +669,7 @@ static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream, int p
             const uint8_t *xs[4];
             for (size_t i = 0; i < op.ins.size(); ++i)
                 xs[i] = cs->tensors[op.ins[i]].dev;
-            B200_TRY(b200_eltwise_sum_u8(
-                xs, (int)op.ins.size(), to.bytes_per_image() * batch, op.ialpha.data(), op.izp.data(),
-                op.has_coeff ? op.coeff.data() : nullptr, op.oalpha, op.ozp, op.obits, op.relu, to.dev, stream));
+            B200_TRY(eltwise_launch(op.elt, op.elt_fast, xs, to.dev, to.bytes_per_image() * batch, op.reverse, as_stream(stream)));
             kind = 3;
             break;
         }

@@ -44,7 +44,10 @@ namespace b200 {
 namespace {
 
 constexpr int kMaxAccStages = 4;              // accumulator stages in tensor memory = epilogue groups: 2 or 4
-constexpr int kEpiWarps = 16;                 // split into 2 groups of 8 warps or 4 groups of 4
+#ifndef B200_EPI_WARPS
+#define B200_EPI_WARPS 16
+#endif
+constexpr int kEpiWarps = B200_EPI_WARPS;     // split into 2 groups of 8 warps or 4 groups of 4
 constexpr int kMma2Warp = 2 + kEpiWarps;        // the second MMA-issuing warp, behind the epilogue warps
 constexpr int kThreads = 64 + kEpiWarps * 32;
 constexpr int kThreads2 = kThreads + 32;         // with the second MMA-issuing warp
@@ -110,6 +113,24 @@ struct IgemmArgs {
     // sums of (x - izp) per output pixel [n][oh][ow] (conv_window_sum_launch); nullptr: off
     const int32_t *wsum;
     int wzp_d;
+    // Uniform-shift epilogue (epi_const != 0): every channel's shift was brought to the layer's smallest
+    // one, S, by dropping low zero bits of its multiplier, so that
+    //   y = ((acc + off32[class][k]) * mult_u[k] + rnd) >> S,   rnd = 2^(S-1) + (ozp << S)
+    // needs two 32-bit constants per channel.  With one channel tile they are kernel parameters (EpiTab),
+    // read as immediate constant-bank operands by the unrolled epilogue: no loads, no registers.
+    int epi_const;           // 0: off; else one byte per warp of a lane quarter: (first 32-column chunk << 4) | chunk count
+    int ushift;              // S - 32: the shift of the product's high word
+    int rnd_lo, rnd_hi;      // rnd
+    const int32_t *off32;    // [n_cls][kpad] accumulator offsets (layers with several border classes read them from here)
+    // 1: the M tiles are visited from the last image / row / column tile down to the first, so that a layer
+    // starts on the part of its input that the layer before wrote last (and that still sits in L2)
+    int rev;
+};
+
+// Per-channel constants of the uniform-shift epilogue for layers with one channel tile (<= 256 channels).
+struct EpiTab {
+    int32_t off32[256];      // the single border class's offsets (unused otherwise)
+    int32_t mult[256];
 };
 
 // Tile index -> (Cout tile, ow tile, oh tile, image tile), Cout tile fastest.  A persistent CTA
@@ -139,6 +160,10 @@ struct TileWalker {
         if (thi >= g.tiles_h) { thi -= g.tiles_h; carry = 1; }
         tni += g.step_n + carry;
     }
+    // tile coordinates as the roles use them (reversed traversal mirrors every M digit)
+    __device__ __forceinline__ int wi(const IgemmArgs &g) const { return g.rev ? g.tiles_w - 1 - twi : twi; }
+    __device__ __forceinline__ int hi(const IgemmArgs &g) const { return g.rev ? g.tiles_h - 1 - thi : thi; }
+    __device__ __forceinline__ int ni(const IgemmArgs &g) const { return g.rev ? g.tiles_n - 1 - tni : tni; }
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -300,6 +325,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[32])
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // Named barriers of one epilogue group (ids 1 + 2g and 2 + 2g for group g).
 __device__ __forceinline__ void epi_bar_sync(int group, int group_threads)
@@ -425,6 +460,83 @@ __device__ __forceinline__ void epi_chunk(const uint32_t (&v)[32], int c0, const
     }
 }
 
+// The uniform-shift form of one 16-column half chunk (see IgemmArgs::epi_const).  `c0` is a compile-time
+// constant after unrolling, so tab.mult[c0 + i] and tab.off32[c0 + i] are constant-bank operands of
+// the add and the multiply-add; the 16 chains share nothing but the two uniform registers of `rnd`.
+template <bool SINGLE, bool FLOOR, bool WZP>
+__device__ __forceinline__ void epi_half_const(const uint32_t (&v)[16], const EpiTab &tab, const int c0, const int32_t *off_row32,
+                                               const long long rnd, const int ush, const int relu_lo, const int wz_t,
+                                               uint8_t *s_out, const int ob, const int ob_sh, const int sw, const int row)
+{
+    uint32_t packed[4];
+#pragma unroll
+    for (int q4 = 0; q4 < 4; ++q4) {
+        int o0, o1, o2, o3;
+        if (SINGLE) {
+            o0 = tab.off32[c0 + q4 * 4 + 0]; o1 = tab.off32[c0 + q4 * 4 + 1];
+            o2 = tab.off32[c0 + q4 * 4 + 2]; o3 = tab.off32[c0 + q4 * 4 + 3];
+        } else {
+            const int4 o = __ldg(reinterpret_cast<const int4 *>(off_row32 + c0 + q4 * 4));
+            o0 = o.x; o1 = o.y; o2 = o.z; o3 = o.w;
+        }
+        if (WZP) {
+            o0 += wz_t; o1 += wz_t; o2 += wz_t; o3 += wz_t;
+        }
+        const long long p0 = (long long)((int)v[q4 * 4 + 0] + o0) * tab.mult[c0 + q4 * 4 + 0] + rnd;
+        const long long p1 = (long long)((int)v[q4 * 4 + 1] + o1) * tab.mult[c0 + q4 * 4 + 1] + rnd;
+        const long long p2 = (long long)((int)v[q4 * 4 + 2] + o2) * tab.mult[c0 + q4 * 4 + 2] + rnd;
+        const long long p3 = (long long)((int)v[q4 * 4 + 3] + o3) * tab.mult[c0 + q4 * 4 + 3] + rnd;
+        const int q0 = (int)(p0 >> 32) >> ush, q1 = (int)(p1 >> 32) >> ush;
+        const int q2 = (int)(p2 >> 32) >> ush, q3 = (int)(p3 >> 32) >> ush;
+        if (FLOOR)
+            packed[q4] = pack_sat_u8x4(max(q0, relu_lo), max(q1, relu_lo), max(q2, relu_lo), max(q3, relu_lo));
+        else
+            packed[q4] = pack_sat_u8x4(q0, q1, q2, q3);
+    }
+    const int sub = c0 >> ob_sh;
+    const int chunk = (c0 & (ob - 1)) >> 4;
+    uint8_t *srow = s_out + (((size_t)sub * kTileM + row) << ob_sh);
+    *reinterpret_cast<uint4 *>(srow + ((chunk ^ sw) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
+
+// The 32-column chunks [CH0, CH1) of a tile's accumulator rows for one warp, uniform-shift form, in
+// halves of 16 columns: the tensor-memory read of the next half is in flight while this one is
+// requantized (two register sets of 16).  The accumulator stage goes back to the MMA warp as soon as
+// the last read has landed, before the last half's arithmetic.
+template <int CH0, int CH1, bool SINGLE, bool FLOOR, bool WZP>
+__device__ __forceinline__ void epi_tile_const(const uint32_t t_row, const int bn, const EpiTab &tab, const int32_t *off_row32,
+                                               const long long rnd, const int ush, const int relu_lo, const int wz_t,
+                                               uint8_t *s_out, const int ob, const int ob_sh, const int sw, const int row,
+                                               const uint32_t tempty, const int lane)
+{
+    // the caller guarantees that the range is exact (CH1 * 32 <= bn): everything here is compile-time
+    uint32_t va[16], vb[16];
+    tmem_ld16(t_row + CH0 * 32, va);
+#pragma unroll
+    for (int h = CH0 * 2; h < CH1 * 2; ++h) {
+        const int c0 = h * 16;
+        tmem_ld_wait();
+        const bool more = h + 1 < CH1 * 2;
+        if (((h - CH0 * 2) & 1) == 0) {
+            if (more)
+                tmem_ld16(t_row + c0 + 16, vb);
+        } else {
+            if (more)
+                tmem_ld16(t_row + c0 + 16, va);
+        }
+        if (!more) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0)
+                mbar_arrive(tempty);
+        }
+        if (((h - CH0 * 2) & 1) == 0)
+            epi_half_const<SINGLE, FLOOR, WZP>(va, tab, c0, off_row32, rnd, ush, relu_lo, wz_t, s_out, ob, ob_sh, sw, row);
+        else
+            epi_half_const<SINGLE, FLOOR, WZP>(vb, tab, c0, off_row32, rnd, ush, relu_lo, wz_t, s_out, ob, ob_sh, sw, row);
+    }
+}
+
 // ---- shared memory layout (dynamic, base aligned to 1024) ---------------------------------------
 //   [stages x A tile (128 x bk)] [stages x B tile (bn x bk)] [2 x output staging 128 x bn]
 //   [2 x (mult bn x 4, shift bn x 4, offsets bn x 8)] [barriers][tmem address][abort flag]
@@ -465,7 +577,7 @@ __host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int 
 //   2: the CTA's tiles go in pairs that share every weight k-block: a stage holds the activation
 //      tiles of both and ONE weight tile, each warp issues the MMAs of its own tile of the pair.
 template <bool HAS_RES, bool HAS_WZP = false, int MODE = 0>
-__global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const IgemmArgs g)
+__global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const __grid_constant__ IgemmArgs g, const __grid_constant__ EpiTab tab)
 {
     extern __shared__ uint8_t smem_raw[];
     // the swizzle patterns are functions of the absolute shared address: align the base to 1024
@@ -585,9 +697,9 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
                         //   = stride * (oh + (d - p) / stride) + p with p = d mod stride (0 <= p < stride)
                         const int dh = rr - g.pad_h, ph = dh & sh_h;
                         const int dw = ss - g.pad_w, pw = dw & sh_w;
-                        const int yh = (tw.thi << g.th_sh) + ((dh - ph) >> sh_h);
-                        const int xw = (tw.twi << g.tw_sh) + ((dw - pw) >> sh_w);
-                        const int n0 = tw.tni * g.tn;
+                        const int yh = (tw.hi(g) << g.th_sh) + ((dh - ph) >> sh_h);
+                        const int xw = (tw.wi(g) << g.tw_sh) + ((dw - pw) >> sh_w);
+                        const int n0 = tw.ni(g) * g.tn;
                         const CUtensorMap *amap = &maps.a[ph * 2 + pw];
                         if (MODE == 2) {
                             // the pair's second tile (absent behind an odd number of tiles): same tap, its own pixels
@@ -597,8 +709,8 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
                             if (second) {
                                 TileWalker t2 = tw;
                                 t2.advance(g);
-                                tma_load_4d(a_dst + a_tile_bytes, amap, fb, cc, (t2.twi << g.tw_sh) + ((dw - pw) >> sh_w),
-                                            (t2.thi << g.th_sh) + ((dh - ph) >> sh_h), t2.tni * g.tn);
+                                tma_load_4d(a_dst + a_tile_bytes, amap, fb, cc, (t2.wi(g) << g.tw_sh) + ((dw - pw) >> sh_w),
+                                            (t2.hi(g) << g.th_sh) + ((dh - ph) >> sh_h), t2.ni(g) * g.tn);
                             }
                         } else {
                         if (first)
@@ -769,7 +881,7 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
             tw.advance(g);
         for (int tile = blockIdx.x + group * gridDim.x; tile < total_tiles; tile += g.groups * gridDim.x) {
             const int nt = tw.nt;
-            const int ow0 = tw.twi << g.tw_sh, oh0 = tw.thi << g.th_sh, n0 = tw.tni * g.tn;
+            const int ow0 = tw.wi(g) << g.tw_sh, oh0 = tw.hi(g) << g.th_sh, n0 = tw.ni(g) * g.tn;
             const int k0 = nt * g.bn;
             const int ow = ow0 + lw, oh = oh0 + lh, img = n0 + ln;
             const bool pix_valid = ow < g.ow && oh < g.oh && img < g.n;
@@ -786,7 +898,7 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
 
             // per-channel tables change with the channel tile: the group meets before (everyone is
             // past the previous tile's reads) and after the reload
-            if (nt != cur_nt) {
+            if (nt != cur_nt && (HAS_RES || !g.epi_const)) {
                 epi_bar_sync(group, group_threads);
                 for (int j = et; j < g.bn; j += group_threads) {
                     const int sft = g.shift[k0 + j];
@@ -816,6 +928,37 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
             if (!failed) {
                 tc_fence_after();
                 const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(as * g.bn);
+                if (!HAS_RES && g.epi_const) {
+                const long long rnd = ((long long)g.rnd_hi << 32) | (unsigned long long)(uint32_t)g.rnd_lo;
+                const int32_t *off_row32 = g.off32;
+                if (!single_class)
+                    off_row32 += (size_t)((int)g.row_cls[min(oh, g.oh - 1)] * g.n_col_cls + (int)g.col_cls[min(ow, g.ow - 1)]) * g.kpad;
+#define B200_EPI_TILE(CH0, CH1)                                                                                                   \
+    do {                                                                                                                          \
+        if (single_class) {                                                                                                       \
+            if (no_floor)                                                                                                         \
+                epi_tile_const<CH0, CH1, true, false, HAS_WZP>(t_row, g.bn, tab, off_row32, rnd, g.ushift, g.relu_lo, wz_t, s_out, g.ob, g.ob_sh, sw, row, tempty_bar(as), lane); \
+            else                                                                                                                  \
+                epi_tile_const<CH0, CH1, true, true, HAS_WZP>(t_row, g.bn, tab, off_row32, rnd, g.ushift, g.relu_lo, wz_t, s_out, g.ob, g.ob_sh, sw, row, tempty_bar(as), lane);  \
+        } else {                                                                                                                  \
+            if (no_floor)                                                                                                         \
+                epi_tile_const<CH0, CH1, false, false, HAS_WZP>(t_row, g.bn, tab, off_row32, rnd, g.ushift, g.relu_lo, wz_t, s_out, g.ob, g.ob_sh, sw, row, tempty_bar(as), lane); \
+            else                                                                                                                  \
+                epi_tile_const<CH0, CH1, false, true, HAS_WZP>(t_row, g.bn, tab, off_row32, rnd, g.ushift, g.relu_lo, wz_t, s_out, g.ob, g.ob_sh, sw, row, tempty_bar(as), lane);  \
+        }                                                                                                                         \
+    } while (0)
+                // epi_const = (first chunk << 4) | chunk count of this warp's column range, per sub-warp
+                switch ((g.epi_const >> (8 * sub_warp)) & 0xff) {
+                case 0x01: B200_EPI_TILE(0, 1); break;
+                case 0x02: B200_EPI_TILE(0, 2); break;
+                case 0x03: B200_EPI_TILE(0, 3); break;
+                case 0x04: B200_EPI_TILE(0, 4); break;
+                case 0x22: B200_EPI_TILE(2, 4); break;
+                case 0x08: B200_EPI_TILE(0, 8); break;
+                default: B200_EPI_TILE(4, 8); break;   // 0x44
+                }
+#undef B200_EPI_TILE
+                } else
                 for (int c0 = 0; c0 < g.bn; c0 += 32) {
                     if (((c0 >> own_sh) & (wpq - 1)) != sub_warp)
                         continue;
@@ -871,11 +1014,14 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
                         epi_chunk<false, false, 16>(v, c0, off_row, ec, rv);
                     }
                 }
-                // accumulator stage drained: hand it back to the MMA warp
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0)
-                    mbar_arrive(tempty_bar(as));
+                // accumulator stage drained: hand it back to the MMA warp (the uniform-shift form has
+                // done so already, after its last tensor-memory read)
+                if (HAS_RES || !g.epi_const) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0)
+                        mbar_arrive(tempty_bar(as));
+                }
 
                 if (g.use_tma_store) {
                     fence_async_smem();
@@ -1008,6 +1154,12 @@ struct ConvIgemmPlan {
     uint32_t *mult_dev = nullptr;   // [kpad]
     int32_t *shift_dev = nullptr;   // [kpad]
     uint8_t *row_cls_dev = nullptr, *col_cls_dev = nullptr;
+    // uniform-shift epilogue (IgemmArgs::epi_const)
+    int rev = 0;                    // reversed tile traversal (conv_igemm_set_reverse)
+    int epi_const = 0, ushift = 0;
+    long long rnd = 0;
+    int32_t *off32_dev = nullptr;   // [n_cls][kpad]
+    EpiTab tab;
     // fused residual add (conv_igemm_set_residual)
     bool has_res = false;
     int r_m[2] = { 0, 0 }, r_add[2] = { 0, 0 }, r_b[2] = { 1, 1 };
@@ -1258,6 +1410,7 @@ int conv_igemm_create(
             for (int t = 0; t < taps; ++t)
                 wtap[(size_t)k * taps + t] += w_s8[((size_t)k * g.c + c) * taps + t];
     std::vector<long long> off((size_t)p->n_row_cls * p->n_col_cls * p->kpad, 0);
+    std::vector<int32_t> off32_all(off.size(), 0);   // the same offsets as plain int32 (uniform-shift epilogue)
     for (int rc = 0; rc < p->n_row_cls; ++rc)
         for (int cc = 0; cc < p->n_col_cls; ++cc)
             for (int k = 0; k < g.k; ++k) {
@@ -1271,6 +1424,7 @@ int conv_igemm_create(
                 // the int32 accumulator offset, folded with the multiplier, the rounding term and the
                 // output zero point into the 64-bit addend of the epilogue's multiply-add
                 const long long off32 = (long long)(int32_t)(uint32_t)(unsigned long long)v;
+                off32_all[((size_t)rc * p->n_col_cls + cc) * p->kpad + k] = (int32_t)off32;
                 off[((size_t)rc * p->n_col_cls + cc) * p->kpad + k]
                     = off32 * (long long)mult[k] + (1ll << (shift[k] - 1)) + ((long long)g.ozp << shift[k]);
             }
@@ -1282,6 +1436,44 @@ int conv_igemm_create(
         if (shift[k] < 32)
             p->generic_requant = 1;
     }
+    // Uniform shift: the multipliers come from an fp32 scale, so their low 7 bits are zero; a channel
+    // whose shift lies d above the layer's smallest one, S, is served exactly by (mult >> d, S) when those
+    // d bits are zero:  (t * mult + 2^(shift-1)) / 2^shift == (t * (mult >> d) + 2^(S-1)) / 2^S.
+    memset(&p->tab, 0, sizeof(p->tab));
+    {
+        int smin = 127;
+        for (int k = 0; k < g.k; ++k)
+            smin = shift[k] < smin ? shift[k] : smin;
+        bool uni = smin >= 33 && g.qmax == 255 && g.k % 16 == 0 && n_tiles_n == 1 && p->bn % 32 == 0 && !p->a_wide;
+        for (int k = 0; k < g.k && uni; ++k) {
+            const int d = shift[k] - smin;
+            uni = d <= 7 && (mult[k] & ((1u << d) - 1u)) == 0;
+        }
+        // each warp of a lane quarter takes a contiguous range of 32-column chunks: (first << 4) | count,
+        // one byte per warp of the quarter; only the ranges the kernel has code for qualify
+        const int wpq = (kEpiWarps / p->groups) / 4;
+        const int chunks = p->bn / 32;
+        int ranges = 0;
+        if (wpq == 1 && (chunks <= 4 || chunks == 8))
+            ranges = chunks;
+        else if (wpq == 2 && p->bn == 256 && p->ob == 128)
+            ranges = 0x04 | (0x44 << 8);
+        else if (wpq == 2 && p->bn == 128 && p->ob == 64)
+            ranges = 0x02 | (0x22 << 8);
+        if (ranges == 0)
+            uni = false;
+        if (getenv("B200_IGEMM_EPI_CONST") && atoi(getenv("B200_IGEMM_EPI_CONST")) == 0)   // tuning aid
+            uni = false;
+        if (uni) {
+            p->epi_const = ranges;
+            p->ushift = smin - 32;
+            p->rnd = (1ll << (smin - 1)) + ((long long)g.ozp << smin);
+            for (int k = 0; k < g.k; ++k)
+                p->tab.mult[k] = (int32_t)(mult[k] >> (shift[k] - smin));
+            for (int k = 0; k < g.k; ++k)
+                p->tab.off32[k] = off32_all[k];          // class 0: all there is when the layer has one class
+        }
+    }
     auto up = [](const void *src, size_t bytes, void **dst) -> int {
         B200_CUDA_TRY(cudaMalloc(dst, bytes));
         B200_CUDA_TRY(cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice));
@@ -1289,6 +1481,7 @@ int conv_igemm_create(
     };
     int rc = up(wp.data(), wp.size(), (void **)&p->w_dev);
     if (rc == B200_OK) rc = up(off.data(), off.size() * 8, (void **)&p->off_dev);
+    if (rc == B200_OK) rc = up(off32_all.data(), off32_all.size() * 4, (void **)&p->off32_dev);
     if (rc == B200_OK) rc = up(multp.data(), multp.size() * 4, (void **)&p->mult_dev);
     if (rc == B200_OK) rc = up(shiftp.data(), shiftp.size() * 4, (void **)&p->shift_dev);
     if (rc == B200_OK) rc = up(row_cls.data(), row_cls.size(), (void **)&p->row_cls_dev);
@@ -1307,6 +1500,7 @@ void conv_igemm_destroy(ConvIgemmPlan *p)
         return;
     cudaFree(p->w_dev);
     cudaFree(p->off_dev);
+    cudaFree(p->off32_dev);
     cudaFree(p->mult_dev);
     cudaFree(p->shift_dev);
     cudaFree(p->row_cls_dev);
@@ -1330,6 +1524,15 @@ static void choose_tile(int ow, int oh, int n, int *tw, int *th, int *tn, int mi
                 *tn = nn;
             }
         }
+}
+
+void conv_igemm_set_reverse(ConvIgemmPlan *p, int reverse)
+{
+    if (p->rev != (reverse ? 1 : 0)) {
+        p->rev = reverse ? 1 : 0;
+        p->last_n = -1;        // cached launch configurations carry the old direction
+        p->saved.clear();
+    }
 }
 
 int conv_igemm_set_residual(ConvIgemmPlan *p, const EltwiseArgs &e, int conv_input)
@@ -1386,6 +1589,10 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.n_col_cls = p->n_col_cls; a.n_cls = p->n_row_cls * p->n_col_cls; a.kpad = p->kpad;
     a.ozp = g.ozp; a.qmax = g.qmax; a.relu_lo = g.relu_lo;
     a.generic_requant = p->generic_requant;
+    a.epi_const = p->epi_const; a.ushift = p->ushift;
+    a.rnd_lo = (int)(uint32_t)(unsigned long long)p->rnd; a.rnd_hi = (int)(p->rnd >> 32);
+    a.off32 = p->off32_dev;
+    a.rev = p->rev;
     a.use_tma_store = (g.k % 16 == 0) ? 1 : 0;
     a.y = y;
     a.res = res;
@@ -1516,15 +1723,15 @@ int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cud
     p->args.wsum = wsum;
     p->args.wzp_d = p->g.wzp_d;
     if (res != nullptr)
-        conv_igemm_i8_kernel<true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
+        conv_igemm_i8_kernel<true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args, p->tab);
     else if (wsum != nullptr)
-        conv_igemm_i8_kernel<false, true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
+        conv_igemm_i8_kernel<false, true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args, p->tab);
     else if (p->pair)
-        conv_igemm_i8_kernel<false, false, 2><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args);
+        conv_igemm_i8_kernel<false, false, 2><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args, p->tab);
     else if (p->mma_warps == 2)
-        conv_igemm_i8_kernel<false, false, 1><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args);
+        conv_igemm_i8_kernel<false, false, 1><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args, p->tab);
     else
-        conv_igemm_i8_kernel<false><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args);
+        conv_igemm_i8_kernel<false><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args, p->tab);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }

@@ -177,7 +177,7 @@ __device__ __forceinline__ int elt_finish(int t, const EltwiseArgs &a)
 // the host, exact because it is a multiple of 2^b[0]); then y = sat_u8(max((t >> s0) + ozp, relu_lo))
 // and the saturation comes with the pack.  64 bytes per input per thread and iteration.
 // PLAIN (with FAST): ozp == 0 and no floor above 0, so y = sat_u8(t >> s0) and the pack does the rest.
-template <int N_IN, bool FAST, bool PLAIN = false>
+template <int N_IN, bool FAST, bool PLAIN = false, bool REV = false>
 __global__ void __launch_bounds__(256) eltwise_sum_kernel(EltwiseArgs a, uint8_t *__restrict__ y, size_t count)
 {
     constexpr int VPT = 4;   // 16-byte vectors per input per thread (2: 0.80 ms, 4: 0.78 ms, 8: 0.79 ms for the 16 adds of ResNet-50)
@@ -185,7 +185,8 @@ __global__ void __launch_bounds__(256) eltwise_sum_kernel(EltwiseArgs a, uint8_t
     // a block works on tiles of 256 * VPT vectors; vector u of a thread lies 256 vectors after vector
     // u - 1, so that every load and store instruction of a warp covers 512 contiguous bytes
     const size_t ntile = nvec / (256 * VPT);
-    for (size_t tile = blockIdx.x; tile < ntile; tile += gridDim.x) {
+    for (size_t tile_i = blockIdx.x; tile_i < ntile; tile_i += gridDim.x) {
+        const size_t tile = REV ? ntile - 1 - tile_i : tile_i;   // REV: from the last tile to the first
         const size_t v0 = tile * (256 * VPT) + threadIdx.x;
         uint32_t xin[N_IN][4 * VPT];
 #pragma unroll
@@ -343,6 +344,7 @@ int eltwise_prepare(
             return fail(B200_ERR_UNSUPPORTED, "eltwise: the int32 sum could overflow");
     }
     a.n_in = n_in;
+    a.rev = 0;
     a.s0 = s0;
     a.round0 = 1 << (s0 - 1);
     a.ozp = ozp;
@@ -494,6 +496,19 @@ int b200_eltwise_sum_u8(
     EltwiseArgs a;
     bool fast = false;
     B200_TRY(eltwise_prepare(n_in, ialpha, izp, coeff, oalpha, ozp, obits, relu, &a, &fast));
+    return eltwise_launch(a, fast, xs, y, count, 0, as_stream(stream));
+}
+
+}  // extern "C"
+
+namespace b200 {
+
+int eltwise_launch(const EltwiseArgs &prepared, bool fast, const uint8_t *const *xs, uint8_t *y, size_t count, int reverse,
+                   cudaStream_t st)
+{
+    EltwiseArgs a = prepared;
+    const int n_in = a.n_in;
+    a.rev = reverse ? 1 : 0;
     for (int i = 0; i < n_in; ++i) {
         if (((uintptr_t)xs[i] & 15) != 0)
             return fail(B200_ERR_INVALID, "eltwise: input %d is not 16-byte aligned", i);
@@ -504,7 +519,6 @@ int b200_eltwise_sum_u8(
     if (count == 0)
         return B200_OK;
     const size_t want = count / (256 * 64) + 1;   // tiles of 256 threads x 64 bytes
-    cudaStream_t st = as_stream(stream);
 #define B200_ELT_LAUNCH(...) \
     eltwise_sum_kernel<__VA_ARGS__><<<resident_grid<eltwise_sum_kernel<__VA_ARGS__>, 256>(want), 256, 0, st>>>(a, y, count)
     if (fast) {
@@ -513,6 +527,8 @@ int b200_eltwise_sum_u8(
         case 2:
             if (a.ozp == 0 && a.relu_lo <= 0)
                 B200_ELT_LAUNCH(2, true, true);
+            else if (a.rev)
+                B200_ELT_LAUNCH(2, true, false, true);
             else
                 B200_ELT_LAUNCH(2, true);
             break;
@@ -531,6 +547,12 @@ int b200_eltwise_sum_u8(
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
 
 int b200_relu_u8(
     const uint8_t *x, size_t count, float ialpha, uint8_t izp, float oalpha, uint8_t ozp,

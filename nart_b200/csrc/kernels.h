@@ -48,6 +48,7 @@ struct EltwiseArgs {
     int add[kMaxEltIn];
     int b[kMaxEltIn];
     int n_in;
+    int rev;       // 1: tiles from the last to the first (see conv_igemm_set_reverse)
     int s0;        // final shift (>= 1)
     int round0;    // 2^(s0-1)
     int ozp, qmax, relu_lo;
@@ -55,6 +56,9 @@ struct EltwiseArgs {
 int eltwise_prepare(
     int n_in, const float *ialpha, const uint8_t *izp, const float *coeff, float oalpha, uint8_t ozp,
     uint8_t obits, int relu, EltwiseArgs *out, bool *fast_out);
+// Launches the prepared op on `count` bytes per input; reverse != 0 walks the tiles from the last to the first.
+int eltwise_launch(const EltwiseArgs &prepared, bool fast, const uint8_t *const *xs, uint8_t *y, size_t count, int reverse,
+                   cudaStream_t st);
 
 // ---- conv -----------------------------------------------------------------------------------
 // Geometry and quantization of one prepared convolution, shared by both kernels.
@@ -124,6 +128,9 @@ int conv_igemm_launch(ConvIgemmPlan *plan, const uint8_t *x, int n, uint8_t *y, 
 // plan's epilogue form cannot take it (the caller then keeps the separate eltwise kernel).
 int conv_igemm_set_residual(ConvIgemmPlan *plan, const EltwiseArgs &e, int conv_input);
 void conv_igemm_destroy(ConvIgemmPlan *plan);
+// Direction in which a launch walks its output tiles: 0 first to last, 1 last to first.  Results do not
+// depend on it; a consumer that walks against its producer's direction starts on data still in L2.
+void conv_igemm_set_reverse(ConvIgemmPlan *plan, int reverse);
 // Per-process / per-device set-up of the tensor-core kernels (driver entry point, shared-memory
 // attribute): done by the first launch otherwise; plan creation calls it so that runs do not.
 int conv_igemm_warm();
