@@ -118,6 +118,19 @@ B200_API void b200_get_quant_scale(float x, int bits, uint32_t *mult, int8_t *sh
  * and by b200_case_prepare:
  *   B200_CASE_ZIGZAG=0                       every op walks its tiles first to last (default: each op walks against the
  *                                            direction of the op that wrote its input, to start on what is still in L2) */
+/* Activation type.  B200_ACT_S8 is the reference's dtINT8 path -- op_conv_2d_i8xi8_run
+ * (art/modules/quant/src/op/conv_2d_int8_impl.c:34-174), dispatched on the dtype of input 0
+ * (conv_2d.c:114-142): activations, weights and outputs are int8, there are no zero points
+ * (izp / wzp / ozp are ignored), `weights` points at int8 values, and
+ *   y = ssaturate_int_by_bits(rshift_rn(acc * mult_k, shift_k), obits)     (quant_helper.h:43-47)
+ * which clips to +-(2^obits - 1) and then narrows to int8.  For obits <= 7 that is a plain clip.  For
+ * obits == 8 -- what the reference's exporter writes for 8-bit tensors (python/nart/modules/
+ * quant.py:47,200) -- the bound is +-255 and the narrowing wraps (200 becomes -56): such a plan is
+ * refused unless s8_wrap is set, in which case it reproduces the wrap bit for bit on the CUDA-core
+ * path.  relu != 0 floors the output at 0.  x and y of the run calls are then int8 NHWC tensors. */
+#define B200_ACT_U8 0
+#define B200_ACT_S8 1
+
 #define B200_CONV_ALGO_AUTO 0
 #define B200_CONV_ALGO_DIRECT 1 /* CUDA-core dp4a kernel: any group, any channel count   */
 #define B200_CONV_ALGO_IGEMM 2  /* tcgen05 kind::i8 implicit GEMM: group 1, c % 16 == 0, k % 16 == 0 */
@@ -138,6 +151,8 @@ typedef struct b200_conv_params {
     int32_t n_walpha;       /* 1 or k                                                         */
     int32_t relu;           /* non-zero: clamp at ozp after requantize                        */
     int32_t algo;           /* B200_CONV_ALGO_*                                               */
+    int32_t act_type;       /* B200_ACT_U8 (0, the default of a zeroed struct) or B200_ACT_S8 */
+    int32_t s8_wrap;        /* B200_ACT_S8 only: accept obits == 8 with the reference's wrapping cast */
 } b200_conv_params;
 
 typedef struct b200_conv b200_conv_t;
@@ -221,6 +236,13 @@ B200_API int b200_ip_create(
     int32_t n_walpha, uint8_t wzp, float oalpha, uint8_t ozp, uint8_t obits,
     const uint8_t *weights, const int32_t *bias, b200_conv_t **conv);
 
+/* op_quant_ip_i8xi8_run (art/modules/quant/src/op/ip.cpp:210-274): the inner product on int8
+ * activations and weights (see B200_ACT_S8).  weights: host int8 [k][c*h*w]. */
+B200_API int b200_ip_create_s8(
+    int32_t c, int32_t h, int32_t w, int32_t k, float ialpha, const float *walpha, int32_t n_walpha,
+    float oalpha, uint8_t obits, int32_t s8_wrap, const int8_t *weights, const int32_t *bias,
+    b200_conv_t **conv);
+
 /* ---- quantize / dequantize ------------------------------------------------------------------
  * op_quantize_run_u8 (art/modules/quant/src/op/quantize.c:145-157) and op_dequantize_run_u8
  * (dequantize.c:111-123).  The float side is always NCHW (the reference's layout); the uint8
@@ -232,6 +254,16 @@ B200_API int b200_quantize_u8(
 B200_API int b200_dequantize_u8(
     const uint8_t *x, float *y, int32_t n, int32_t c, int32_t h, int32_t w, float ialpha,
     uint8_t izp, int32_t nhwc, b200_stream_t stream);
+
+/* op_quantize_run_i8 (quantize.c:159-185, qtype SYMMETRIC): y = clip(round(x * (float)(1. / oalpha)),
+ * +-(2^(obits-1) - 1)), round half away from zero; and op_dequantize_run_i8 (dequantize.c:124-136):
+ * y = (float)q * ialpha.  Layout arguments as for the uint8 pair. */
+B200_API int b200_quantize_s8(
+    const float *x, int8_t *y, int32_t n, int32_t c, int32_t h, int32_t w, float oalpha,
+    uint8_t obits, int32_t nhwc, b200_stream_t stream);
+B200_API int b200_dequantize_s8(
+    const int8_t *x, float *y, int32_t n, int32_t c, int32_t h, int32_t w, float ialpha,
+    int32_t nhwc, b200_stream_t stream);
 
 /* ---- layout ---------------------------------------------------------------------------------
  * uint8 NCHW <-> NHWC, for tensors that cross the module boundary in the reference's layout.

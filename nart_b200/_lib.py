@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libnart_b200.so")
 OK = 0
 ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_NOMEM, ERR_DEVICE_WAIT = -1, -2, -3, -4, -5
 ALGO_AUTO, ALGO_DIRECT, ALGO_IGEMM = 0, 1, 2
+ACT_U8, ACT_S8 = 0, 1
 POOL_MAX, POOL_AVE = 0, 1
 
 i32, u8, f32 = C.c_int32, C.c_uint8, C.c_float
@@ -27,6 +28,7 @@ class ConvParams(C.Structure):
         ("pad_h", i32), ("pad_w", i32), ("stride_h", i32), ("stride_w", i32), ("group", i32),
         ("ialpha", f32), ("izp", u8), ("wzp", u8), ("ozp", u8), ("obits", u8), ("oalpha", f32),
         ("walpha", C.POINTER(f32)), ("n_walpha", i32), ("relu", i32), ("algo", i32),
+        ("act_type", i32), ("s8_wrap", i32),
     ]
 
 
@@ -66,6 +68,9 @@ SIGNATURES = {
     "b200_conv2d_run_residual": (C.c_int, [vp, vp, i32, vp, vp, vp]),
     "b200_ip_create": (C.c_int, [i32, i32, i32, i32, f32, u8, C.POINTER(f32), i32, u8, f32, u8, u8,
                                  vp, vp, C.POINTER(vp)]),
+    "b200_ip_create_s8": (C.c_int, [i32, i32, i32, i32, f32, C.POINTER(f32), i32, f32, u8, i32, vp, vp, C.POINTER(vp)]),
+    "b200_quantize_s8": (C.c_int, [vp, vp, i32, i32, i32, i32, f32, u8, i32, vp]),
+    "b200_dequantize_s8": (C.c_int, [vp, vp, i32, i32, i32, i32, f32, i32, vp]),
     "b200_quantize_u8": (C.c_int, [vp, vp, i32, i32, i32, i32, f32, u8, u8, i32, vp]),
     "b200_dequantize_u8": (C.c_int, [vp, vp, i32, i32, i32, i32, f32, u8, i32, vp]),
     "b200_nchw_to_nhwc_u8": (C.c_int, [vp, vp, i32, i32, i32, i32, i32, u8, vp]),

@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
     const int cwords = cg4 / 4;
     const int items = g.r * g.s * cwords;
     const uint32_t izp4 = (uint32_t)g.izp * 0x01010101u;
+    const uint32_t x_flip = g.act_signed ? 0x80808080u : 0u;   // int8 bytes seen as uint8 with zero point 128
     const uint8_t *ximg = x + (size_t)img * g.h * g.w * g.c + (size_t)grp * cg;
 
     int acc[4] = { 0, 0, 0, 0 };
@@ -94,6 +95,7 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
                             if (cw * 4 + b < cg)
                                 xv |= (uint32_t)__ldg(px + b) << (8 * b);
                     }
+                    xv ^= x_flip;   // (bytes past the group's last channel meet zero weights)
                 }
                 uint4 wv = *reinterpret_cast<const uint4 *>(&wsm[it][kq * 4]);
                 acc[0] = dp4a_us(xv, wv.x, acc[0]);
@@ -122,7 +124,13 @@ __global__ void __launch_bounds__(256) conv_direct_kernel(
             a -= g.wzp_d * (xsum - g.izp * g.r * g.s * cg);
         if (acc_out)
             acc_out[pix * g.k + k] = a;
-        q[j] = sat_relu(requant_raw(a, mult[k], shift[k], g.ozp), g.qmax, g.relu_lo);
+        if (g.s8_wrap) {
+            // ssaturate_int_by_bits(v, 8): clip at +-255, then the int8 return type keeps the low byte
+            const int v = requant_raw(a, mult[k], shift[k], 0);
+            q[j] = max(min(v, 255), g.relu_lo) & 0xff;
+        } else {
+            q[j] = sat_relu(requant_raw(a, mult[k], shift[k], g.ozp), g.qmax, g.relu_lo) ^ (g.act_signed ? 0x80 : 0);
+        }
     }
     uint8_t *py = y + pix * g.k + k0 + kq * 4;
     if (nk == 4 && (((size_t)g.k | (size_t)k0) & 3) == 0) {
@@ -535,7 +543,7 @@ int conv_direct_launch(
         return B200_OK;
     const size_t npix = (size_t)n * g.oh * g.ow;
     const int kg = g.k / g.group, cg = g.c / g.group;
-    const bool depthwise = p.w_dw_dev && !acc_out && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
+    const bool depthwise = p.w_dw_dev && !acc_out && !g.act_signed && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0);
     const bool dw3 = depthwise && p.w_dw3_dev && p.q_dw3_dev && npix * (size_t)(g.c / 4) < 0xffffffffull
         && (size_t)n * g.h * g.w * (size_t)(g.c / 4) < 0xffffffffull;
     if (dw3 && p.w_dw3p_dev && (g.stride_w == 1 || g.stride_w == 2)) {

@@ -118,6 +118,7 @@ struct IgemmArgs {
     //   y = ((acc + off32[class][k]) * mult_u[k] + rnd) >> S,   rnd = 2^(S-1) + (ozp << S)
     // needs two 32-bit constants per channel.  With one channel tile they are kernel parameters (EpiTab),
     // read as immediate constant-bank operands by the unrolled epilogue: no loads, no registers.
+    uint32_t out_flip;       // int8 outputs: 0x80808080 (the generic requantize form flips bit 7 of every byte), else 0
     int epi_const;           // 0: off; else one byte per warp of a lane quarter: (first 32-column chunk << 4) | chunk count
     int ushift;              // S - 32: the shift of the product's high word
     int rnd_lo, rnd_hi;      // rnd
@@ -380,6 +381,7 @@ struct EpiConsts {
     uint8_t *s_out;            // staging buffer of this epilogue group
     int ob, ob_sh, sw, row;
     int qmax, relu_lo;
+    uint32_t out_flip;         // 0x80808080 for int8 outputs (generic form only), else 0
     int r_m0, r_add0, r_b0, r_m1, r_add1, r_b1, r_s0, r_ozp, r_lo;   // fused residual add
 };
 
@@ -446,6 +448,8 @@ __device__ __forceinline__ void epi_chunk(const uint32_t (&v)[32], int c0, const
             packed[q4] = pack_sat_u8x4(max(q0, ec.relu_lo), max(q1, ec.relu_lo), max(q2, ec.relu_lo), max(q3, ec.relu_lo));
         else
             packed[q4] = pack_sat_u8x4(q0, q1, q2, q3);
+        if (!FAST)
+            packed[q4] ^= ec.out_flip;
     }
     // staging: sub-tile (col / ob), row-major rows of `ob` bytes, 16-byte chunks XOR-swizzled with the
     // row index exactly as the TMA store's swizzle mode expects
@@ -860,7 +864,7 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
         bool store_pending = false;
         uint8_t *s_out = smem + L.out + (size_t)group * out_bytes;
 
-        const EpiConsts ec = { s_mult, s_shift, s_off, s_out, g.ob, g.ob_sh, sw, row, g.qmax, g.relu_lo,
+        const EpiConsts ec = { s_mult, s_shift, s_off, s_out, g.ob, g.ob_sh, sw, row, g.qmax, g.relu_lo, g.out_flip,
                                g.r_m[0], g.r_add[0], g.r_b[0], g.r_m[1], g.r_add[1], g.r_b[1], g.r_s0, g.r_ozp, g.r_lo };
         const bool fast_epi = !g.generic_requant && g.qmax == 255;
         const bool no_floor = g.relu_lo <= 0;
@@ -1420,7 +1424,8 @@ int conv_igemm_create(
                         for (int ss = 0; ss < g.s; ++ss)
                             if (col_valid[cc][ss])
                                 sum += wtap[(size_t)k * taps + rr * g.s + ss];
-                long long v = (long long)(bias ? bias[k] : 0) - (long long)g.izp * sum;
+                // int8 activations reach the tensor cores as signed bytes and TMA pads with a true zero: no correction
+                long long v = (long long)(bias ? bias[k] : 0) - (long long)(g.act_signed ? 0 : g.izp) * sum;
                 // the int32 accumulator offset, folded with the multiplier, the rounding term and the
                 // output zero point into the 64-bit addend of the epilogue's multiply-add
                 const long long off32 = (long long)(int32_t)(uint32_t)(unsigned long long)v;
@@ -1436,6 +1441,8 @@ int conv_igemm_create(
         if (shift[k] < 32)
             p->generic_requant = 1;
     }
+    if (g.act_signed)
+        p->generic_requant = 1;     // the generic form carries the ceiling below 255 and the output's bit flip
     // Uniform shift: the multipliers come from an fp32 scale, so their low 7 bits are zero; a channel
     // whose shift lies d above the layer's smallest one, S, is served exactly by (mult >> d, S) when those
     // d bits are zero:  (t * mult + 2^(shift-1)) / 2^shift == (t * (mult >> d) + 2^(S-1)) / 2^S.
@@ -1444,7 +1451,7 @@ int conv_igemm_create(
         int smin = 127;
         for (int k = 0; k < g.k; ++k)
             smin = shift[k] < smin ? shift[k] : smin;
-        bool uni = smin >= 33 && g.qmax == 255 && g.k % 16 == 0 && n_tiles_n == 1 && p->bn % 32 == 0 && !p->a_wide;
+        bool uni = smin >= 33 && !p->generic_requant && g.qmax == 255 && g.k % 16 == 0 && n_tiles_n == 1 && p->bn % 32 == 0 && !p->a_wide;
         for (int k = 0; k < g.k && uni; ++k) {
             const int d = shift[k] - smin;
             uni = d <= 7 && (mult[k] & ((1u << d) - 1u)) == 0;
@@ -1579,7 +1586,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     for (a.ob_sh = 0; (1 << a.ob_sh) < a.ob; ++a.ob_sh) {}
     // instruction descriptor: D = S32 (2 at bit 4), A = unsigned 8-bit (0 at bit 7), B = signed 8-bit
     // (1 at bit 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-    a.idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((uint32_t)(p->bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+    a.idesc = (2u << 4) | ((g.act_signed ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(p->bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
     uint32_t cols = 32;
     while (cols < (uint32_t)(p->acc_stages * p->bn))
         cols <<= 1;
@@ -1589,6 +1596,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.n_col_cls = p->n_col_cls; a.n_cls = p->n_row_cls * p->n_col_cls; a.kpad = p->kpad;
     a.ozp = g.ozp; a.qmax = g.qmax; a.relu_lo = g.relu_lo;
     a.generic_requant = p->generic_requant;
+    a.out_flip = g.act_signed ? 0x80808080u : 0u;
     a.epi_const = p->epi_const; a.ushift = p->ushift;
     a.rnd_lo = (int)(uint32_t)(unsigned long long)p->rnd; a.rnd_hi = (int)(p->rnd >> 32);
     a.off32 = p->off32_dev;

@@ -69,6 +69,16 @@ int b200_conv2d_create(
         return fail(B200_ERR_INVALID, "conv: ialpha and oalpha must be positive");
     if (p->algo != B200_CONV_ALGO_AUTO && p->algo != B200_CONV_ALGO_DIRECT && p->algo != B200_CONV_ALGO_IGEMM)
         return fail(B200_ERR_INVALID, "conv: unknown algo %d", p->algo);
+    if (p->act_type != B200_ACT_U8 && p->act_type != B200_ACT_S8)
+        return fail(B200_ERR_INVALID, "conv: unknown act_type %d", p->act_type);
+    const bool s8 = p->act_type == B200_ACT_S8;
+    if (s8 && p->obits == 8 && !p->s8_wrap)
+        return fail(
+            B200_ERR_UNSUPPORTED,
+            "conv: int8 activations with obits = 8 clip at +-255 and then wrap into int8 in the reference "
+            "(quant_helper.h:43-47); set s8_wrap to reproduce that, or use obits <= 7");
+    if (s8 && p->obits == 8 && p->algo == B200_CONV_ALGO_IGEMM)
+        return fail(B200_ERR_UNSUPPORTED, "conv: the wrapping int8 output exists on the CUDA-core path only");
 
     b200_conv *cv = new b200_conv();
     ConvGeom &g = cv->g;
@@ -80,6 +90,17 @@ int b200_conv2d_create(
     g.izp = p->izp; g.ozp = p->ozp; g.qmax = (1 << p->obits) - 1;
     g.relu_lo = p->relu ? p->ozp : 0;
     g.wzp_d = (int)p->wzp - 128;
+    g.act_signed = 0;
+    g.s8_wrap = 0;
+    if (s8) {
+        const int m = (1 << p->obits) - 1;     // ssaturate_int_by_bits: +-(2^obits - 1)
+        g.act_signed = 1;
+        g.s8_wrap = p->obits == 8 ? 1 : 0;
+        g.izp = 128; g.ozp = 128; g.wzp_d = 0;
+        g.qmax = g.s8_wrap ? 255 : 128 + m;
+        // the wrapping form works on the signed value itself (floor 0 or -255), the clipping one on value + 128
+        g.relu_lo = g.s8_wrap ? (p->relu ? 0 : -255) : (p->relu ? 128 : 128 - m);
+    }
     cv->oalpha = p->oalpha;
     cudaGetDevice(&cv->device);
 
@@ -91,7 +112,7 @@ int b200_conv2d_create(
     // wzp_d = wzp - 128 and applied through the sum of the activations (ConvGeom::wzp_d).
     std::vector<int8_t> w_s8(wcount);   // [k][cg][r][s], value = stored - 128
     for (size_t i = 0; i < wcount; ++i)
-        w_s8[i] = (int8_t)((int)weights[i] - 128);
+        w_s8[i] = s8 ? (int8_t)weights[i] : (int8_t)((int)weights[i] - 128);
 
     std::vector<uint32_t> mult(g.k);
     std::vector<int32_t> shift(g.k);
@@ -193,7 +214,7 @@ int b200_conv2d_create(
 
     // ---- tensor-core plan ---------------------------------------------------------------------
     char why[256] = "";
-    const bool ig_ok = conv_igemm_supported(g, why, sizeof(why)) != 0;
+    const bool ig_ok = conv_igemm_supported(g, why, sizeof(why)) != 0 && !g.s8_wrap;
     // A 4-channel image with a short kernel row is no contraction the tensor cores can take as it
     // is (4 bytes per tap).  Gathering, for every input row and output column, the 8-pixel window
     // the kernel row slides over gives a 32-channel tensor [n][h][ow][8 pixels x 4 channels] on
@@ -201,7 +222,7 @@ int b200_conv2d_create(
     // Window cells outside the image hold the byte izp, whose contribution the epilogue's
     // zero-point term removes exactly; cells past the kernel width get zero weights.
     const bool low_ok = g.group == 1 && g.c == 4 && g.s <= kLowerWindow && g.k >= 16 && g.stride_h <= 2
-        && g.h >= g.stride_h;
+        && g.h >= g.stride_h && !g.act_signed;
     if (!ig_ok && low_ok && p->algo != B200_CONV_ALGO_DIRECT) {
         ConvGeom gl = g;
         gl.c = kLowerWindow * 4;
@@ -260,6 +281,21 @@ int b200_ip_create(
     p.ialpha = ialpha; p.izp = izp; p.wzp = wzp; p.ozp = ozp; p.obits = obits; p.oalpha = oalpha;
     p.walpha = walpha; p.n_walpha = n_walpha; p.relu = 0; p.algo = B200_CONV_ALGO_AUTO;
     return b200_conv2d_create(&p, weights, bias, conv);
+}
+
+int b200_ip_create_s8(
+    int32_t c, int32_t h, int32_t w, int32_t k, float ialpha, const float *walpha, int32_t n_walpha,
+    float oalpha, uint8_t obits, int32_t s8_wrap, const int8_t *weights, const int32_t *bias,
+    b200_conv_t **conv)
+{
+    b200_conv_params p;
+    memset(&p, 0, sizeof(p));
+    p.c = c; p.h = h; p.w = w; p.k = k; p.r = h; p.s = w;
+    p.pad_h = p.pad_w = 0; p.stride_h = p.stride_w = 1; p.group = 1;
+    p.ialpha = ialpha; p.obits = obits; p.oalpha = oalpha;
+    p.walpha = walpha; p.n_walpha = n_walpha; p.relu = 0; p.algo = B200_CONV_ALGO_AUTO;
+    p.act_type = B200_ACT_S8; p.s8_wrap = s8_wrap;
+    return b200_conv2d_create(&p, reinterpret_cast<const uint8_t *>(weights), bias, conv);
 }
 
 int b200_conv2d_out_dims(const b200_conv_t *conv, int32_t *oh, int32_t *ow)
@@ -333,6 +369,8 @@ int b200_conv2d_fuse_residual_add(
         return fail(B200_ERR_UNSUPPORTED, "conv(fuse): only plans on the tensor-core path take a residual add");
     if (conv->g.wzp_d != 0)
         return fail(B200_ERR_UNSUPPORTED, "conv(fuse): a weight zero point other than 128 and a fused residual add do not combine");
+    if (conv->g.act_signed)
+        return fail(B200_ERR_UNSUPPORTED, "conv(fuse): the residual add is a uint8 op (eltwise.c reads uint8 only)");
     if (conv->fused_residual)
         return fail(B200_ERR_INVALID, "conv(fuse): the plan already has a residual add");
     if (izp[conv_input] != (uint8_t)conv->g.ozp || ialpha[conv_input] != conv->oalpha)

@@ -48,6 +48,28 @@ struct DequantizeFn {
     }
 };
 
+struct QuantizeS8Fn {
+    // op_quantize_run_i8 (quantize.c:159-185): clip(round(x * alpha), -l, l) with alpha = (float)(1. / oalpha)
+    // (formed on the host), the float product rounded half away from zero -- roundf of the float equals the
+    // reference's round() of the same value widened to double -- and the clip done on the rounded value.
+    float alpha;
+    int l;
+    __device__ __forceinline__ uint8_t operator()(float x) const
+    {
+        const float r = roundf(__fmul_rn(x, alpha));
+        if (!(r == r))
+            return 0;  // NaN: undefined in the reference
+        const int v = (int)fminf(fmaxf(r, (float)-l), (float)l);
+        return (uint8_t)(int8_t)v;
+    }
+};
+
+struct DequantizeS8Fn {
+    // op_dequantize_run_i8 (dequantize.c:124-136): the int8 value as float, times alpha
+    float alpha;
+    __device__ __forceinline__ float operator()(uint8_t q) const { return __fmul_rn((float)(int)(int8_t)q, alpha); }
+};
+
 struct IdentityFn {
     __device__ __forceinline__ uint8_t operator()(uint8_t q) const { return q; }
 };
@@ -439,6 +461,57 @@ int b200_dequantize_u8(
     if (nhwc && !(c == 1 || P == 1)) {
         dim3 grid((P + TP - 1) / TP, (c + TC - 1) / TC, n);
         nhwc_to_nchw_kernel<float, DequantizeFn><<<grid, TP, 0, as_stream(stream)>>>(x, y, c, P, c, fn);
+    } else {
+        size_t count = (size_t)n * c * P;
+        size_t threads = (count + 3) / 4;
+        dequantize_flat_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, as_stream(stream)>>>(x, y, count, fn);
+    }
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_quantize_s8(
+    const float *x, int8_t *y8, int32_t n, int32_t c, int32_t h, int32_t w, float oalpha, uint8_t obits,
+    int32_t nhwc, b200_stream_t stream)
+{
+    if (!x || !y8 || n < 0 || c <= 0 || h <= 0 || w <= 0 || obits < 2 || obits > 8)
+        return fail(B200_ERR_INVALID, "quantize(int8): bad argument (obits 2..8)");
+    if (!(oalpha > 0.f))
+        return fail(B200_ERR_INVALID, "quantize(int8): oalpha must be positive");
+    if (n == 0)
+        return B200_OK;
+    uint8_t *y = reinterpret_cast<uint8_t *>(y8);
+    QuantizeS8Fn fn;
+    fn.alpha = (float)(1. / (double)oalpha);
+    fn.l = (1 << (obits - 1)) - 1;
+    const int P = h * w;
+    if (nhwc && !(c == 1 || P == 1)) {
+        dim3 grid((P + TP - 1) / TP, (c + TC - 1) / TC, n);
+        nchw_to_nhwc_kernel<float, QuantizeS8Fn><<<grid, TP, 0, as_stream(stream)>>>(x, y, c, P, c, 0, fn);
+    } else {
+        size_t count = (size_t)n * c * P;
+        size_t threads = (count + 3) / 4;
+        quantize_flat_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, as_stream(stream)>>>(x, y, count, fn);
+    }
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+int b200_dequantize_s8(
+    const int8_t *x8, float *y, int32_t n, int32_t c, int32_t h, int32_t w, float ialpha, int32_t nhwc,
+    b200_stream_t stream)
+{
+    if (!x8 || !y || n < 0 || c <= 0 || h <= 0 || w <= 0)
+        return fail(B200_ERR_INVALID, "dequantize(int8): bad argument");
+    if (n == 0)
+        return B200_OK;
+    const uint8_t *x = reinterpret_cast<const uint8_t *>(x8);
+    DequantizeS8Fn fn;
+    fn.alpha = ialpha;
+    const int P = h * w;
+    if (nhwc && !(c == 1 || P == 1)) {
+        dim3 grid((P + TP - 1) / TP, (c + TC - 1) / TC, n);
+        nhwc_to_nchw_kernel<float, DequantizeS8Fn><<<grid, TP, 0, as_stream(stream)>>>(x, y, c, P, c, fn);
     } else {
         size_t count = (size_t)n * c * P;
         size_t threads = (count + 3) / 4;

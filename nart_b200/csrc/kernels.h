@@ -72,6 +72,13 @@ struct ConvGeom {
     // and the second sum (over the window's in-image taps and the group's channels) is formed beside
     // the products (CUDA-core kernels) or read from a window-sum tensor (tensor-core kernel).
     int wzp_d;
+    // int8 activations (the reference's dtINT8 path).  An int8 value v and the byte v ^ 0x80 = v + 128
+    // are the same number seen with zero point 128, so the plan is the uint8 one with izp = 128,
+    // int8 weights (wzp_d = 0), ozp = 128, floor 128 - m and ceiling qmax = 128 + m for the symmetric
+    // clip at +-m; the kernels flip bit 7 of every input byte they load (or let the tensor cores read the
+    // bytes as signed) and of every output byte they store.
+    int act_signed;
+    int s8_wrap;    // obits == 8 on that path: clip at +-255, then keep the low byte (CUDA-core kernel only)
 };
 
 // Direct (CUDA-core) convolution: weights [k][r][s][cg4] int8 (cg4 = c/group rounded up to 4,

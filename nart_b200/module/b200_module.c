@@ -237,6 +237,15 @@ static void *output_dev(tensor_t *t, bool nhwc)
     return m->dev;
 }
 
+/* The int8 path of the reference clips 8-bit outputs at +-255 and then wraps them into int8
+ * (quant_helper.h:43-47).  That is reproduced only when NART_B200_S8_WRAP=1 is set in the environment;
+ * otherwise an int8 conv_2d / ip with obits = 8 is refused with the library's explanation. */
+static int s8_wrap_allowed(void)
+{
+    const char *e = getenv("NART_B200_S8_WRAP");
+    return e && atoi(e) != 0;
+}
+
 static void alloc_io(op_t *op)
 {
     size_t i;
@@ -363,8 +372,9 @@ void op_b200_conv_2d_tp_prepare(op_t *op)
     op_b200_conv_2d_t *c = (op_b200_conv_2d_t *)op;
     int n, ch, h, w;
     alloc_io(op);
-    if (op->input_tensors[0]->dtype != dtUINT8)
-        LOG_error("b200: conv_2d takes uint8 activations (int8 weights travel as uint8 with wzp 128)\n");
+    /* dispatch on the dtype of input 0, as the reference does (conv_2d.c:114-142) */
+    if (op->input_tensors[0]->dtype != dtUINT8 && op->input_tensors[0]->dtype != dtINT8)
+        LOG_error("b200: conv_2d takes uint8 or int8 activations\n");
     dims_of(op->input_tensors[0], &n, &ch, &h, &w);
     /* prepare runs again after a reshape (art/src/parade.c:199-215): rebuild only if the geometry changed */
     if (c->plan && c->plan_c == ch && c->plan_h == h && c->plan_w == w) {
@@ -388,6 +398,10 @@ void op_b200_conv_2d_tp_prepare(op_t *op)
     p.n_walpha = (c->q.n_walpha == (size_t)c->num_output && c->num_output > 1) ? (int32_t)c->num_output : 1;
     p.relu = c->relu_flag ? 1 : 0;
     p.algo = B200_CONV_ALGO_AUTO;
+    if (op->input_tensors[0]->dtype == dtINT8) {
+        p.act_type = B200_ACT_S8;
+        p.s8_wrap = s8_wrap_allowed();
+    }
     const uint8_t *wt = (const uint8_t *)mem_cpu_data(op->input_tensors[1]->mem);
     const int32_t *bias = op->input_size == 3 ? (const int32_t *)mem_cpu_data(op->input_tensors[2]->mem) : NULL;
     B200_CALL(b200_conv2d_create(&p, wt, bias, &c->plan));
@@ -454,8 +468,8 @@ void op_b200_ip_tp_prepare(op_t *op)
     op_b200_ip_t *c = (op_b200_ip_t *)op;
     int n, ch, h, w;
     alloc_io(op);
-    if (op->input_tensors[0]->dtype != dtUINT8)
-        LOG_error("b200: ip takes uint8 activations\n");
+    if (op->input_tensors[0]->dtype != dtUINT8 && op->input_tensors[0]->dtype != dtINT8)
+        LOG_error("b200: ip takes uint8 or int8 activations\n");
     dims_of(op->input_tensors[0], &n, &ch, &h, &w);
     if (c->plan && c->plan_c == ch && c->plan_h == h && c->plan_w == w) {
         op->run_func = op_b200_ip_run;
@@ -465,10 +479,15 @@ void op_b200_ip_tp_prepare(op_t *op)
         B200_CALL(b200_conv2d_destroy(c->plan));
     const uint8_t *wt = (const uint8_t *)mem_cpu_data(op->input_tensors[1]->mem);
     const int32_t *bias = op->input_size == 3 ? (const int32_t *)mem_cpu_data(op->input_tensors[2]->mem) : NULL;
-    B200_CALL(b200_ip_create(
-        ch, h, w, (int32_t)c->num_output, c->q.ialpha[0], c->q.izp[0], c->q.walpha,
-        (c->q.n_walpha == (size_t)c->num_output && c->num_output > 1) ? (int32_t)c->num_output : 1, c->q.wzp[0],
-        c->q.oalpha[0], c->q.ozp[0], c->q.obits[0], wt, bias, &c->plan));
+    const int32_t n_wa = (c->q.n_walpha == (size_t)c->num_output && c->num_output > 1) ? (int32_t)c->num_output : 1;
+    if (op->input_tensors[0]->dtype == dtINT8)   /* ip.cpp:313-331 */
+        B200_CALL(b200_ip_create_s8(
+            ch, h, w, (int32_t)c->num_output, c->q.ialpha[0], c->q.walpha, n_wa, c->q.oalpha[0], c->q.obits[0],
+            s8_wrap_allowed(), (const int8_t *)wt, bias, &c->plan));
+    else
+        B200_CALL(b200_ip_create(
+            ch, h, w, (int32_t)c->num_output, c->q.ialpha[0], c->q.izp[0], c->q.walpha, n_wa, c->q.wzp[0],
+            c->q.oalpha[0], c->q.ozp[0], c->q.obits[0], wt, bias, &c->plan));
     c->plan_c = ch; c->plan_h = h; c->plan_w = w;
     op->run_func = op_b200_ip_run;
 }
@@ -686,7 +705,8 @@ static bool infer_shape_b200_quantize(op_t *op)
         op->output_tensors = (tensor_t *)malloc(sizeof(tensor_t));
         memset(op->output_tensors, 0, sizeof(tensor_t));
         op->output_tensors[0].mem = mem_new(op->input_tensors[0]->mem->tp);
-        op->output_tensors[0].dtype = dtUINT8;
+        /* quantize.c:51-65: SYMMETRIC gives int8, DEFAULT / BIASED uint8 (config has run: op.c:46-53) */
+        op->output_tensors[0].dtype = ((op_b200_qdq_t *)op)->qtype == SETTING_QUANT_SYMMETRIC ? dtINT8 : dtUINT8;
     }
     op->output_tensors[0].shape = op->input_tensors[0]->shape;
     return true;
@@ -780,6 +800,17 @@ static const void *float_or_bytes_dev(tensor_t *t, scratch_t *scratch, size_t by
     return scratch->buf;
 }
 
+static bool qdq_key_built(int32_t key)
+{
+    switch (key) {
+    case 0x0008: case 0x0108:
+    case 0x0202: case 0x0203: case 0x0204: case 0x0206: case 0x0207: case 0x0208:
+        return true;
+    default:
+        return false;
+    }
+}
+
 static void op_b200_quantize_run(op_t *op)
 {
     op_b200_qdq_t *q = (op_b200_qdq_t *)op;
@@ -788,7 +819,10 @@ static void op_b200_quantize_run(op_t *op)
     const float *x = (const float *)float_or_bytes_dev(
         op->input_tensors[0], &q->in_scratch, sizeof(float) * shape_count(&op->input_tensors[0]->shape));
     uint8_t *y = (uint8_t *)output_dev(&op->output_tensors[0], true);
-    B200_CALL(b200_quantize_u8(x, y, n, c, h, w, q->alpha[0], q->zp[0], q->bits[0], 1, NULL));
+    if (q->qtype == SETTING_QUANT_SYMMETRIC)
+        B200_CALL(b200_quantize_s8(x, (int8_t *)y, n, c, h, w, q->alpha[0], q->bits[0], 1, NULL));
+    else
+        B200_CALL(b200_quantize_u8(x, y, n, c, h, w, q->alpha[0], q->zp[0], q->bits[0], 1, NULL));
 }
 
 static void op_b200_dequantize_run(op_t *op)
@@ -802,7 +836,10 @@ static void op_b200_dequantize_run(op_t *op)
     if (ti->mem->tp == b200_mem_tp)
         in_nhwc = ((b200_mem_t *)ti->mem)->nhwc;   /* mem_data() may have re-uploaded NCHW bytes */
     float *y = (float *)output_dev(&op->output_tensors[0], false);
-    B200_CALL(b200_dequantize_u8(x, y, n, c, h, w, q->alpha[0], q->zp[0], in_nhwc ? 1 : 0, NULL));
+    if (q->qtype == SETTING_QUANT_SYMMETRIC)
+        B200_CALL(b200_dequantize_s8((const int8_t *)x, y, n, c, h, w, q->alpha[0], in_nhwc ? 1 : 0, NULL));
+    else
+        B200_CALL(b200_dequantize_u8(x, y, n, c, h, w, q->alpha[0], q->zp[0], in_nhwc ? 1 : 0, NULL));
 }
 
 void op_b200_quantize_tp_prepare(op_t *op)
@@ -811,8 +848,9 @@ void op_b200_quantize_tp_prepare(op_t *op)
     alloc_io(op);
     CHECK(op->input_tensors[0]->dtype == dtFLOAT32);
     int32_t key = q->qtype << 8 | q->bits[0];
-    if (key != 0x0008 && key != 0x0108)   /* quantize.c:233-236: DEFAULT / BIASED, 8 bits -> uint8 */
-        LOG_error("b200: quantization of %d bits with type %d is not built (uint8 only)\n", q->bits[0], q->qtype);
+    /* quantize.c:233-245: DEFAULT / BIASED with 8 bits -> uint8; SYMMETRIC with 2, 3, 4, 6, 7 or 8 bits -> int8 */
+    if (!qdq_key_built(key))
+        LOG_error("b200: quantization of %d bits with type %d is not built (uint8, and int8 of 2..8 bits)\n", q->bits[0], q->qtype);
     op->run_func = op_b200_quantize_run;
 }
 
@@ -821,8 +859,8 @@ void op_b200_dequantize_tp_prepare(op_t *op)
     op_b200_qdq_t *q = (op_b200_qdq_t *)op;
     alloc_io(op);
     int32_t key = q->qtype << 8 | q->bits[0];
-    if (key != 0x0008 && key != 0x0108)
-        LOG_error("b200: dequantization of %d bits with type %d is not built (uint8 only)\n", q->bits[0], q->qtype);
+    if (!qdq_key_built(key))
+        LOG_error("b200: dequantization of %d bits with type %d is not built (uint8, and int8 of 2..8 bits)\n", q->bits[0], q->qtype);
     op->run_func = op_b200_dequantize_run;
 }
 

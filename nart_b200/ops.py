@@ -14,7 +14,7 @@ import numpy as np
 import torch
 
 from . import _lib
-from ._lib import ALGO_AUTO, ALGO_DIRECT, ALGO_IGEMM, POOL_AVE, POOL_MAX, ConvParams, check, lib
+from ._lib import ACT_S8, ACT_U8, ALGO_AUTO, ALGO_DIRECT, ALGO_IGEMM, POOL_AVE, POOL_MAX, ConvParams, check, lib
 
 
 def _stream() -> int:
@@ -24,6 +24,12 @@ def _stream() -> int:
 def _dev_u8(t: torch.Tensor) -> torch.Tensor:
     if not (t.is_cuda and t.dtype == torch.uint8 and t.is_contiguous()):
         raise ValueError("expected a contiguous uint8 CUDA tensor")
+    return t
+
+
+def _dev_s8(t: torch.Tensor) -> torch.Tensor:
+    if not (t.is_cuda and t.dtype == torch.int8 and t.is_contiguous()):
+        raise ValueError("expected a contiguous int8 CUDA tensor")
     return t
 
 
@@ -47,9 +53,13 @@ class Conv2d:
     ``[K]`` or None; ``in_hw``: input height and width the plan is prepared for.
     """
 
-    def __init__(self, weight, bias, *, in_hw, stride=(1, 1), pad=(0, 0), group=1, ialpha, izp,
-                 walpha, wzp=128, oalpha, ozp, obits=8, relu=False, algo=ALGO_AUTO):
-        w = np.ascontiguousarray(weight, dtype=np.uint8)
+    def __init__(self, weight, bias, *, in_hw, stride=(1, 1), pad=(0, 0), group=1, ialpha, izp=0,
+                 walpha, wzp=128, oalpha, ozp=0, obits=8, relu=False, algo=ALGO_AUTO, signed=False,
+                 s8_wrap=False):
+        """``signed`` True selects the reference's int8 (dtINT8) path: int8 weights, int8 NHWC activations in
+        and out, no zero points; ``s8_wrap`` accepts obits == 8 with the reference's wrapping cast."""
+        self.signed = bool(signed)
+        w = np.ascontiguousarray(weight, dtype=np.int8 if signed else np.uint8)
         k, cg, r, s = w.shape
         self.k, self.c = k, cg * group
         wa = _walpha_array(walpha, k)
@@ -60,6 +70,7 @@ class Conv2d:
         p.ialpha, p.izp, p.wzp, p.ozp, p.obits, p.oalpha = ialpha, izp, wzp, ozp, obits, oalpha
         p.walpha = wa.ctypes.data_as(C.POINTER(C.c_float))
         p.n_walpha, p.relu, p.algo = wa.size, int(relu), algo
+        p.act_type, p.s8_wrap = (ACT_S8 if signed else ACT_U8), int(s8_wrap)
         self._h = C.c_void_p()
         check(lib.b200_conv2d_create(
             C.byref(p), w.ctypes.data, None if b is None else b.ctypes.data, C.byref(self._h)))
@@ -69,11 +80,11 @@ class Conv2d:
         self.algo = lib.b200_conv2d_algo(self._h)
 
     def __call__(self, x: torch.Tensor, return_acc: bool = False):
-        _dev_u8(x)
+        _dev_s8(x) if self.signed else _dev_u8(x)
         n, h, w, c = x.shape
         if (h, w) != self.in_hw or c != self.c:
             raise ValueError("input %s does not match the prepared plan" % (tuple(x.shape),))
-        y = torch.empty((n, self.out_hw[0], self.out_hw[1], self.k), dtype=torch.uint8, device=x.device)
+        y = torch.empty((n, self.out_hw[0], self.out_hw[1], self.k), dtype=x.dtype, device=x.device)
         if return_acc:
             acc = torch.empty(y.shape, dtype=torch.int32, device=x.device)
             check(lib.b200_conv2d_run_acc(self._h, x.data_ptr(), n, y.data_ptr(), acc.data_ptr(), _stream()))
@@ -130,6 +141,46 @@ class InnerProduct(Conv2d):
             ozp, obits, wt.ctypes.data, None if b is None else b.ctypes.data, C.byref(self._h)))
         self.in_hw, self.out_hw = (h, w), (1, 1)
         self.algo = lib.b200_conv2d_algo(self._h)
+
+
+class InnerProductS8(Conv2d):
+    """ip of the quant module on int8 activations (op_quant_ip_i8xi8_run): ``weight`` int8 ``[K, C*H*W]``."""
+
+    def __init__(self, weight, bias, *, in_chw, ialpha, walpha, oalpha, obits=7, s8_wrap=False):
+        c, h, w = in_chw
+        wt = np.ascontiguousarray(weight, dtype=np.int8)
+        k = wt.shape[0]
+        self.k, self.c, self.signed = k, c, True
+        wa = _walpha_array(walpha, k)
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.int32)
+        self._h = C.c_void_p()
+        check(lib.b200_ip_create_s8(
+            c, h, w, k, ialpha, wa.ctypes.data_as(C.POINTER(C.c_float)), wa.size, oalpha, obits, int(s8_wrap),
+            wt.ctypes.data, None if b is None else b.ctypes.data, C.byref(self._h)))
+        self.in_hw, self.out_hw = (h, w), (1, 1)
+        self.algo = lib.b200_conv2d_algo(self._h)
+
+
+def quantize_s8(x: torch.Tensor, oalpha: float, obits: int = 8, nhwc: bool = True):
+    """quantize with qtype SYMMETRIC: float32 NCHW -> int8 (NHWC by default)."""
+    if not (x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 4):
+        raise ValueError("expected a contiguous float32 NCHW CUDA tensor")
+    n, c, h, w = x.shape
+    y = torch.empty((n, h, w, c) if nhwc else (n, c, h, w), dtype=torch.int8, device=x.device)
+    check(lib.b200_quantize_s8(x.data_ptr(), y.data_ptr(), n, c, h, w, oalpha, obits, int(nhwc), _stream()))
+    return y
+
+
+def dequantize_s8(x: torch.Tensor, ialpha: float, nhwc: bool = True):
+    """dequantize of an int8 tensor (NHWC by default) -> float32 NCHW."""
+    _dev_s8(x)
+    if nhwc:
+        n, h, w, c = x.shape
+    else:
+        n, c, h, w = x.shape
+    y = torch.empty((n, c, h, w), dtype=torch.float32, device=x.device)
+    check(lib.b200_dequantize_s8(x.data_ptr(), y.data_ptr(), n, c, h, w, ialpha, int(nhwc), _stream()))
+    return y
 
 
 def quantize(x: torch.Tensor, oalpha: float, ozp: int, obits: int = 8, nhwc: bool = True):

@@ -139,7 +139,74 @@ class _Common:
         return y
 
 
-class Port(_Common):
+_i8p = C.POINTER(C.c_int8)
+
+
+def _i8(a):
+    a = np.ascontiguousarray(a)
+    assert a.dtype == np.int8, a.dtype
+    return a
+
+
+class _CommonI8:
+    """The int8 (symmetric, no zero points) ops; the C signatures of the two libraries differ only in
+    walpha (one float for the reference, an array for the restatement)."""
+
+    def _wa(self, walpha):
+        wa = np.atleast_1d(np.asarray(walpha, dtype=np.float32)).copy()
+        if self.prefix == "ref":
+            return [C.c_float(float(wa[0]))]
+        return [_p(wa, _f32p), C.c_int(wa.size)]
+
+    def conv2d_i8(self, x, w, bias, stride, pad, group, ialpha, walpha, oalpha, obits=7):
+        x, w = _i8(x), _i8(w)
+        n, c, h, wd = x.shape
+        k, cg, r, s = w.shape
+        assert cg * group == c
+        sh, sw = stride
+        ph, pw = pad
+        oh, ow = conv_out_dim(h, r, ph, sh), conv_out_dim(wd, s, pw, sw)
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.int32)
+        y = np.empty((n, k, oh, ow), np.int8)
+        rc = getattr(self.lib, self.prefix + "_conv2d_i8")(
+            _p(x, _i8p), C.c_int(n), C.c_int(c), C.c_int(h), C.c_int(wd), _p(w, _i8p), _p(b, _i32p),
+            C.c_int(k), C.c_int(r), C.c_int(s), C.c_int(ph), C.c_int(pw), C.c_int(sh), C.c_int(sw),
+            C.c_int(group), C.c_float(ialpha), *self._wa(walpha), C.c_float(oalpha), C.c_uint8(obits), _p(y, _i8p))
+        assert rc == 0
+        return y
+
+    def ip_i8(self, x, w, bias, ialpha, walpha, oalpha, obits=7):
+        x, w = _i8(x), _i8(w)
+        n = x.shape[0]
+        chw = x.size // n
+        k = w.shape[0]
+        b = None if bias is None else np.ascontiguousarray(bias, dtype=np.int32)
+        y = np.empty((n, k), np.int8)
+        rc = getattr(self.lib, self.prefix + "_ip_i8")(
+            _p(x, _i8p), C.c_int(n), C.c_int(chw), _p(w, _i8p), _p(b, _i32p), C.c_int(k), C.c_float(ialpha),
+            *self._wa(walpha), C.c_float(oalpha), C.c_uint8(obits), _p(y, _i8p))
+        assert rc == 0
+        return y
+
+    def quantize_i8(self, x, oalpha, obits=8):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        y = np.empty(x.shape, np.int8)
+        rc = getattr(self.lib, self.prefix + "_quantize_i8")(
+            _p(x, _f32p), C.c_size_t(x.size), C.c_float(oalpha), C.c_uint8(obits), _p(y, _i8p))
+        assert rc == 0
+        return y
+
+    def dequantize_i8(self, x, ialpha, ibits=8):
+        x = _i8(x)
+        y = np.empty(x.shape, np.float32)
+        extra = [C.c_uint8(ibits)] if self.prefix == "ref" else []
+        rc = getattr(self.lib, self.prefix + "_dequantize_i8")(
+            _p(x, _i8p), C.c_size_t(x.size), C.c_float(ialpha), *extra, _p(y, _f32p))
+        assert rc == 0
+        return y
+
+
+class Port(_Common, _CommonI8):
     prefix = "port"
     per_channel = True
 
@@ -198,7 +265,7 @@ class Port(_Common):
         return y
 
 
-class Ref(_Common):
+class Ref(_Common, _CommonI8):
     prefix = "ref"
     per_channel = False
 

@@ -329,3 +329,98 @@ PORT_API int port_dequantize_u8(const uint8_t *x, size_t count, float ialpha, ui
         y[e] = (float)((int)(int16_t)x[e] - (int)izp) * ialpha;
     return 0;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * The int8 ("dtINT8", symmetric) path of the reference: no zero points anywhere.
+ * ------------------------------------------------------------------------------------------ */
+
+/* quant_helper.h:31 and :43-47: clip to +-(2^bits - 1), then the function's int8_t return type
+ * truncates.  For bits <= 7 nothing is lost; for bits == 8 the bound is +-255 and the cast wraps
+ * (200 -> -56), which is what the reference computes. */
+static inline int8_t ssat(int32_t x, uint8_t bits)
+{
+    int32_t m = (1 << bits) - 1;
+    int32_t c = x > m ? m : (x < -m ? -m : x);
+    return (int8_t)(uint8_t)(uint32_t)c;
+}
+
+/* conv_2d, int8 activations and weights (art/modules/quant/src/op/conv_2d_int8_impl.c:34-174):
+ *   acc = bias[k] + sum x * w  over the in-image taps (im2col_i8 writes zeros for the others,
+ *   utils/im2col.cpp:22-116), y = ssat(rshift_rn(acc * mult, shift), obits) with (mult, shift)
+ *   from get_quant_scale_int32(ialpha * walpha / oalpha).
+ * Extensions as in port_conv2d_u8: n > 1, one scale per output channel (n_walpha == k).
+ * x: [n][c][h][w] int8, wt: [k][c/group][r][s] int8, y: [n][k][oh][ow] int8. */
+PORT_API int port_conv2d_i8(
+    const int8_t *x, int n, int c, int h, int w, const int8_t *wt, const int32_t *bias, int k, int r,
+    int s, int pad_h, int pad_w, int stride_h, int stride_w, int group, float ialpha,
+    const float *walpha, int n_walpha, float oalpha, uint8_t obits, int8_t *y)
+{
+    int oh = (h + 2 * pad_h - r) / stride_h + 1;
+    int ow = (w + 2 * pad_w - s) / stride_w + 1;
+    int cg = c / group, kg = k / group;
+    uint32_t *mult = (uint32_t *)malloc(sizeof(uint32_t) * k);
+    int8_t *shift = (int8_t *)malloc(k);
+    if (n_walpha != 1 && n_walpha != k)
+        return -1;
+    for (int ko = 0; ko < k; ++ko)
+        port_get_quant_scale(ialpha * walpha[n_walpha == 1 ? 0 : ko] / oalpha, 32, &mult[ko], &shift[ko]);
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int in = 0; in < n; ++in)
+        for (int ko = 0; ko < k; ++ko) {
+            int g = ko / kg;
+            for (int y0 = 0; y0 < oh; ++y0)
+                for (int x0 = 0; x0 < ow; ++x0) {
+                    int32_t acc = bias ? bias[ko] : 0;
+                    for (int ci = 0; ci < cg; ++ci)
+                        for (int rr = 0; rr < r; ++rr) {
+                            int iy = y0 * stride_h + rr - pad_h;
+                            if (iy < 0 || iy >= h)
+                                continue;
+                            for (int ss = 0; ss < s; ++ss) {
+                                int ix = x0 * stride_w + ss - pad_w;
+                                if (ix < 0 || ix >= w)
+                                    continue;
+                                acc += (int32_t)x[(((size_t)in * c + g * cg + ci) * h + iy) * w + ix]
+                                    * (int32_t)wt[(((size_t)ko * cg + ci) * r + rr) * s + ss];
+                            }
+                        }
+                    int64_t v = port_rshift_rn((int64_t)acc * (int64_t)mult[ko], (uint8_t)shift[ko]);
+                    y[(((size_t)in * k + ko) * oh + y0) * ow + x0] = ssat((int32_t)v, obits);
+                }
+        }
+    free(mult);
+    free(shift);
+    return 0;
+}
+
+/* ip, int8 path (art/modules/quant/src/op/ip.cpp:210-274). x: [n][chw], wt: [k][chw]. */
+PORT_API int port_ip_i8(
+    const int8_t *x, int n, int chw, const int8_t *wt, const int32_t *bias, int k, float ialpha,
+    const float *walpha, int n_walpha, float oalpha, uint8_t obits, int8_t *y)
+{
+    return port_conv2d_i8(x, n, chw, 1, 1, wt, bias, k, 1, 1, 0, 0, 1, 1, 1, ialpha, walpha, n_walpha, oalpha, obits, y);
+}
+
+/* quantize float32 -> int8, qtype SYMMETRIC (quantize.c:159-185): alpha = 1. / oalpha is a double
+ * division narrowed to float; x * alpha is a float product that `round` (half away from zero)
+ * takes as a double; the result is clipped to +-(2^(bits-1) - 1) by the int-typed clip of
+ * quant_helper.h:31, whose double argument converts to int by truncation. */
+PORT_API int port_quantize_i8(const float *x, size_t count, float oalpha, uint8_t obits, int8_t *y)
+{
+    volatile float alpha = (float)(1. / (double)oalpha);
+    int l = (int)((1l << (obits - 1)) - 1);
+    for (size_t e = 0; e < count; ++e) {
+        volatile float prod = x[e] * alpha;
+        int v = (int)round((double)prod);
+        y[e] = (int8_t)(v > l ? l : (v < -l ? -l : v));
+    }
+    return 0;
+}
+
+/* dequantize int8 -> float32 (dequantize.c:124-136): the int8 value converted to float, times alpha. */
+PORT_API int port_dequantize_i8(const int8_t *x, size_t count, float ialpha, float *y)
+{
+    for (size_t e = 0; e < count; ++e)
+        y[e] = (float)x[e] * ialpha;
+    return 0;
+}

@@ -367,6 +367,140 @@ REF_API int ref_dequantize_u8(const uint8_t *x, size_t count, float ialpha, uint
 }
 
 /* ------------------------------------------------------------------------------------------
+ * The int8 (dtINT8, symmetric) path: conv_2d (conv_2d_int8_impl.c:34-174), ip (ip.cpp:210-274),
+ * quantize with qtype SYMMETRIC (quantize.c:159-185), dequantize (dequantize.c:124-136).
+ * Zero points are not read on this path; ibits = wbits = 8 selects gemm_i8xi8 (conv_2d.c:120-142).
+ * The conv sizes its int32 scratch for one image (conv_2d_int8_impl.c:22-31): one image per run.
+ * ------------------------------------------------------------------------------------------ */
+REF_API int ref_conv2d_i8(
+    const int8_t *x, int n, int c, int h, int w, const int8_t *wt, const int32_t *bias, int k, int r,
+    int s, int pad_h, int pad_w, int stride_h, int stride_w, int group, float ialpha, float walpha,
+    float oalpha, uint8_t obits, int8_t *y)
+{
+    int per_run = g_whole_batch ? n : 1;
+    int xd[4] = { per_run, c, h, w }, wd[4] = { k, c / group, r, s }, bd[1] = { k };
+    tensor_t *tx = new_tensor(dtINT8, 4, xd);
+    tensor_t *tw = new_tensor(dtINT8, 4, wd);
+    tensor_t *tb = new_tensor(dtINT32, 1, bd);
+    tensor_t *in[3] = { tx, tw, tb };
+    float ia[3] = { ialpha, walpha, 1.f };
+    uint8_t iz[3] = { 0, 0, 0 }, ib[3] = { 8, 8, 32 };
+    size_t xsz = (size_t)per_run * c * h * w, ysz;
+    int i;
+    op_t *op;
+    memcpy(mem_cpu_data(tw->mem), wt, (size_t)k * (c / group) * r * s);
+    if (bias)
+        memcpy(mem_cpu_data(tb->mem), bias, sizeof(int32_t) * k);
+    else
+        memset(mem_cpu_data(tb->mem), 0, sizeof(int32_t) * k);
+    op = workspace_new_op(ws(), OP_CONV_2D, 3, in);
+    if (!op)
+        return -1;
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_NUM_OUTPUT, dtUINT32, (uint32_t)k));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_KERNEL_H, dtUINT32, (uint32_t)r));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_KERNEL_W, dtUINT32, (uint32_t)s));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_PAD_H, dtUINT32, (uint32_t)pad_h));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_PAD_W, dtUINT32, (uint32_t)pad_w));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_STRIDE_H, dtUINT32, (uint32_t)stride_h));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_STRIDE_W, dtUINT32, (uint32_t)stride_w));
+    CHECK(op_setting_single_set(op, SETTING_CONV_2D_GROUP, dtUINT32, (uint32_t)group));
+    set_in_quant(op, 3, ia, iz, ib);
+    set_w_quant(op, walpha, 0, 8);
+    set_out_quant(op, oalpha, 0, obits);
+    CHECK(op_config(op));
+    op_prepare(op);
+    ysz = shape_count(&op->output_tensors[0].shape);
+    for (i = 0; i < n; i += per_run) {
+        memcpy(mem_cpu_data(tx->mem), x + xsz * (i / per_run), xsz);
+        op_run(op);
+        memcpy(y + ysz * (i / per_run), mem_cpu_data(op->output_tensors[0].mem), ysz);
+    }
+    op_delete(op);
+    tensor_delete(tx);
+    tensor_delete(tw);
+    tensor_delete(tb);
+    return 0;
+}
+
+REF_API int ref_ip_i8(
+    const int8_t *x, int n, int chw, const int8_t *wt, const int32_t *bias, int k, float ialpha,
+    float walpha, float oalpha, uint8_t obits, int8_t *y)
+{
+    int xd[4] = { n, chw, 1, 1 }, wd[4] = { k, chw, 1, 1 }, bd[1] = { k };
+    tensor_t *tx = new_tensor(dtINT8, 4, xd);
+    tensor_t *tw = new_tensor(dtINT8, 4, wd);
+    tensor_t *tb = new_tensor(dtINT32, 1, bd);
+    tensor_t *in[3] = { tx, tw, tb };
+    float ia[3] = { ialpha, walpha, 1.f };
+    uint8_t iz[3] = { 0, 0, 0 }, ib[3] = { 8, 8, 32 };
+    op_t *op = workspace_new_op(ws(), OP_IP, 3, in);
+    if (!op)
+        return -1;
+    CHECK(op_setting_single_set(op, SETTING_IP_NUM_OUTPUT, dtUINT32, (uint32_t)k));
+    set_in_quant(op, 3, ia, iz, ib);
+    set_w_quant(op, walpha, 0, 8);
+    set_out_quant(op, oalpha, 0, obits);
+    CHECK(op_config(op));
+    memcpy(mem_cpu_data(tw->mem), wt, (size_t)k * chw);
+    if (bias)
+        memcpy(mem_cpu_data(tb->mem), bias, sizeof(int32_t) * k);
+    else
+        memset(mem_cpu_data(tb->mem), 0, sizeof(int32_t) * k);
+    op_prepare(op);
+    memcpy(mem_cpu_data(tx->mem), x, (size_t)n * chw);
+    op_run(op);
+    memcpy(y, mem_cpu_data(op->output_tensors[0].mem), (size_t)n * k);
+    op_delete(op);
+    tensor_delete(tx);
+    tensor_delete(tw);
+    tensor_delete(tb);
+    return 0;
+}
+
+REF_API int ref_quantize_i8(const float *x, size_t count, float oalpha, uint8_t obits, int8_t *y)
+{
+    int d[4] = { 1, (int)count, 1, 1 };
+    tensor_t *tx = new_tensor(dtFLOAT32, 4, d);
+    tensor_t *in[1] = { tx };
+    op_t *op = workspace_new_op(ws(), OP_QUANT_QUANTIZE, 1, in);
+    if (!op)
+        return -1;
+    memcpy(mem_cpu_data(tx->mem), x, count * sizeof(float));
+    set_out_quant(op, oalpha, 0, obits);
+    CHECK(op_setting_single_set(op, SETTING_QUANT_QTYPE, dtINT32, (int32_t)SETTING_QUANT_SYMMETRIC));
+    CHECK(op_config(op));
+    if (op->output_tensors[0].dtype != dtINT8)
+        return -2;
+    op_prepare(op);
+    op_run(op);
+    memcpy(y, mem_cpu_data(op->output_tensors[0].mem), count);
+    op_delete(op);
+    tensor_delete(tx);
+    return 0;
+}
+
+REF_API int ref_dequantize_i8(const int8_t *x, size_t count, float ialpha, uint8_t ibits, float *y)
+{
+    int d[4] = { 1, (int)count, 1, 1 };
+    tensor_t *tx = new_tensor(dtINT8, 4, d);
+    tensor_t *in[1] = { tx };
+    uint8_t iz = 0;
+    op_t *op = workspace_new_op(ws(), OP_QUANT_DEQUANTIZE, 1, in);
+    if (!op)
+        return -1;
+    memcpy(mem_cpu_data(tx->mem), x, count);
+    set_in_quant(op, 1, &ialpha, &iz, &ibits);
+    CHECK(op_setting_single_set(op, SETTING_QUANT_QTYPE, dtINT32, (int32_t)SETTING_QUANT_SYMMETRIC));
+    CHECK(op_config(op));
+    op_prepare(op);
+    op_run(op);
+    memcpy(y, mem_cpu_data(op->output_tensors[0].mem), count * sizeof(float));
+    op_delete(op);
+    tensor_delete(tx);
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------------
  * A serialized case (engine.bin, format v2: art/src/serialize_v2.c:26-103) through the
  * reference's own loader and parade, the way its drivers do it (tools/promark.cpp:58-72):
  * deserialize_parade with the current module's workspace, parade_prepare, then per run copy the

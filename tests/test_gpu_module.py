@@ -95,3 +95,28 @@ def test_plugin_other_ops(plugin):
     assert_same(plugin.quantize_u8(f, 0.037, 117), GOLD["quantize"], "quantize")
     assert_same(plugin.dequantize_u8(a, 0.037, 117).view(np.uint32), GOLD["dequantize"].view(np.uint32), "dequantize")
     assert_same(plugin.ip_u8(xi, wi, bi, 0.02, 100, 0.005, 128, 0.1, 50), GOLD["ip"], "ip")
+
+
+def test_plugin_int8_path(ref, monkeypatch):
+    """dtINT8 tensors through the plugin: conv_2d and ip dispatch on the dtype of input 0, quantize /
+    dequantize on qtype SYMMETRIC, exactly as the reference module does; the bytes are the reference's
+    (fixtures produced by the compiled reference)."""
+    if not os.path.exists(PLUGIN):
+        pytest.skip("plugin not built")
+    from cases import S8_SHAPES, conv_inputs_s8, s8_oalpha
+    from test_oracle_pin_s8 import s8_float_inputs
+    S8 = np.load(os.path.join(os.path.dirname(__file__), "golden", "quant_ref_s8.npz"))
+    monkeypatch.setenv("NART_B200_S8_WRAP", "1")          # the obits = 8 case of the list wraps, as in the reference
+    ref.use_module(PLUGIN, "b200_module_tp", whole_batch=True)
+    try:
+        for i, (n, c, h, w, k, r, s, st, pd, g, ob) in enumerate(S8_SHAPES):
+            x, wt, bias, walpha = conv_inputs_s8(300 + i, n, c, h, w, k, r, s, g)
+            y = ref.conv2d_i8(x, wt, bias, (st, st), (pd, pd), g, 0.02, float(walpha[0]), s8_oalpha(c, g, r, s), ob)
+            assert_same(y, S8["conv%d_scalar" % i], "plugin int8 conv %d" % i)
+        xi, wi, bi, f, q = s8_float_inputs()
+        assert_same(ref.ip_i8(xi, wi, bi, 0.02, 0.005, 0.4, 7), S8["ip"], "plugin int8 ip")
+        for ob in (8, 7, 4):
+            assert_same(ref.quantize_i8(f, 0.05, ob), S8["quantize_%d" % ob], "plugin int8 quantize %d" % ob)
+        assert_same(ref.dequantize_i8(q, 0.037).view(np.uint32), S8["dequantize"].view(np.uint32), "plugin int8 dequantize")
+    finally:
+        ref.use_module()
