@@ -274,6 +274,125 @@ def conv_bytes_ops(spec, batch):
     return out
 
 
+def measure_int8_peak(lib, check, stream, local):
+    """The dense int8 rate of the tensor pipe on this GPU: a short burst (best of five launches of about
+    half a millisecond) and a sustained run of about a second, with the clocks seen during the latter."""
+    import ctypes as C
+    ms, ops = C.c_float(0), C.c_double(0)
+
+    def run(mmas):
+        check(lib.b200_measure_mma_i8_peak(int(mmas), C.byref(ms), C.byref(ops), stream))
+        return ops.value / (ms.value * 1e-3) / 1e12, ms.value
+
+    run(4096)
+    burst = max(run(4096)[0] for _ in range(5))
+    tops, t = run(1 << 17)
+    per_ms = (1 << 17) / t
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.15)
+    sustained, t_long = run(min(int(per_ms * 1000), 30000000))
+    clocks = sampler.stop()
+    return dict(burst_tops=burst, sustained_tops=sustained, sustained_ms=t_long, clocks_sustained=clocks,
+                shape="tcgen05.mma kind::i8 M128 N256 K32, operands resident in shared memory, all SMs")
+
+
+def conv_sweep_rows(peaks, int8_peak_tops, batch=256):
+    """The 16 single-conv shapes (C = K in 64/128/256/512 on 56/28/14/7 pixel maps, 1x1 and 3x3, stride 1 and 2)
+    at `batch`: device time per launch from a CUDA-graph replay of 20 launches, TOP/s on the true dims,
+    algorithmic GB/s, and the fraction of the roof that binds the shape (the larger of ops / measured int8
+    rate and bytes / measured copy bandwidth, over the measured time)."""
+    from nart_b200 import conv_bench
+    rows = []
+    for c, k, hw in conv_bench.SWEEP_SHAPES:
+        for ks in (1, 3):
+            for stride in (1, 2):
+                r = conv_bench.time_conv(c, k, hw, ks, stride, batch, iters=20, warmup=3, graph=True)
+                ops = r["tops"] * 1e12 * r["ms"] * 1e-3
+                byts = r["gbs"] * 1e9 * r["ms"] * 1e-3
+                t_tensor = ops / (int8_peak_tops * 1e12) * 1e3
+                t_hbm = byts / (peaks["hbm_gbs"] * 1e9) * 1e3
+                rows.append(dict(c=c, k=k, hw=hw, ks=ks, stride=stride, batch=batch, ms=round(r["ms"], 5),
+                                 tops=round(r["tops"], 1), gbs=round(r["gbs"], 1),
+                                 bound="tensor" if t_tensor > t_hbm else "hbm",
+                                 roof_frac=round(max(t_tensor, t_hbm) / r["ms"], 3)))
+    return rows
+
+
+def time_network(spec, batch, hw, steps=10):
+    """One of the other benchmark networks: images/s of the CUDA-graph replay with the batch resident."""
+    import torch
+    from nart_b200 import nets
+    from nart_b200._lib import check, lib
+    cs, _ = nets.to_case(spec, batch)
+    side = torch.cuda.Stream()
+    x = torch.from_numpy(np.random.default_rng(7).integers(0, 256, (batch, 3, hw, hw), dtype=np.uint8)).pin_memory()
+    check(lib.b200_memcpy_h2d(cs.io_device_ptr(False, 0), x.data_ptr(), x.numel(), side.cuda_stream))
+    cs.use_graph(True)
+    for _ in range(4):
+        cs.run_device(batch, side.cuda_stream)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(side)
+    for _ in range(steps):
+        cs.run_device(batch, side.cuda_stream)
+    e1.record(side)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    cs.close()
+    return dict(network=spec["name"], batch=batch, ms_per_step=round(ms, 4), images_per_sec=round(batch / ms * 1e3, 1),
+                conv_tops=round(nets.conv_ops_per_image(spec) * batch / ms / 1e9, 1))
+
+
+def plugin_e2e(spec, batch, steps, x_ref, logits_ref):
+    """The drop-in route: the network written as an engine.bin and run by the reference's own loader and
+    parade (deserialize_parade / parade_prepare / parade_run, art/src/parade.c:169-197) with
+    libart_module_b200.so as the only workspace, op by op on the default stream, the way the reference's
+    promark drives a case (tools/promark.cpp:457-492).  A step marks the input's host view as written
+    (so parade_run uploads it: the host->device copy is inside the step), runs the parade and takes the
+    output's host view (device->host).  Needs the art core (compiled unmodified into oracle/_ref); the
+    logits must equal the case runner's bit for bit."""
+    import tempfile
+    plugin = os.path.join(ROOT, "nart_b200", "libart_module_b200.so")
+    try:
+        import oracle
+        if not (oracle.have_ref() and os.path.exists(plugin)):
+            return dict(unavailable="the art core (oracle/_ref) or libart_module_b200.so is not present")
+        from nart_b200 import engine
+        R = oracle.ref()
+        with tempfile.TemporaryDirectory() as d:
+            path = os.path.join(d, "engine.bin")
+            engine.write_engine(spec, path, batch=batch, per_channel=True, conv_relu_flag=True)
+            R.use_module(plugin, "b200_module_tp", whole_batch=True)
+            try:
+                h = R.open_engine(path)
+                try:
+                    R.engine_input(h, 0)[:] = x_ref.reshape(-1)
+                    R.engine_run(h)
+                    got = R.engine_output(h, 0).copy()
+                    same = bool(np.array_equal(got.view(np.uint32), logits_ref.reshape(-1).view(np.uint32)))
+                    for _ in range(2):
+                        R.engine_input(h, 0)
+                        R.engine_run(h)
+                        R.engine_output(h, 0)
+                    t = time.perf_counter()
+                    for _ in range(steps):
+                        R.engine_input(h, 0)          # host view requested: the next run uploads the batch again
+                        R.engine_run(h)
+                        R.engine_output(h, 0)         # downloads the logits, synchronizes
+                    dt = time.perf_counter() - t
+                finally:
+                    R.close_engine(h)
+            finally:
+                R.use_module()
+        return dict(value=batch * steps / dt, unit="images/s", ms_per_step=dt / steps * 1e3, steps=steps,
+                    logits_equal_case_runner=same, clock="host (perf_counter) around input view / parade_run / output view",
+                    host_runtime="the reference's art core (loader, parade and op loop), compiled unmodified; every op "
+                                 "dispatches to libart_module_b200.so")
+    except Exception as e:       # the main line must not depend on this leg
+        return dict(unavailable="%s: %s" % (type(e).__name__, e))
+
+
 def run_gpu_arm(a):
     import torch
     import torch.distributed as dist
@@ -392,8 +511,21 @@ def run_gpu_arm(a):
     for _ in range(a.steps):
         cs.run_host_ptrs(batch, [x_host.data_ptr()], [y_host.data_ptr()], stream)
     wall_ms = (time.perf_counter() - w0) * 1e3
-    clocks = sampler.stop() if rank == 0 else None
     logits_checksum = float(y_host.double().abs().sum().item())
+    # ---- single-GPU extras, inside the clock-sampled region ------------------------------------------
+    extras = {}
+    if rank == 0 and world == 1 and not a.no_extras:
+        peaks0 = measured_peaks()
+        torch.cuda.synchronize()
+        extras["int8_peak"] = measure_int8_peak(lib, check, stream, local)
+        extras["conv_sweep_batch256"] = conv_sweep_rows(peaks0, extras["int8_peak"]["burst_tops"])
+        extras["other_networks"] = [time_network(nets.resnet(18, seed=SEED), 64, 224),
+                                    time_network(nets.mobilenet_v2(seed=SEED), 256, 224)]
+        xv = torch.from_numpy(np.random.default_rng(4242).integers(0, 256, (batch, 3, 224, 224), dtype=np.uint8)).pin_memory()
+        yv = torch.zeros((batch, 1000), dtype=torch.float32).pin_memory()
+        cs.run_host_ptrs(batch, [xv.data_ptr()], [yv.data_ptr()], stream)
+        extras["e2e_plugin"] = plugin_e2e(spec, batch, max(3, a.steps // 2), xv.numpy(), yv.numpy())
+    clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
         peaks = measured_peaks()
@@ -405,6 +537,11 @@ def run_gpu_arm(a):
         hbm_ach = igemm_bytes / sec / 1e9
         tops_ach = igemm_ops / sec / 1e12
         int8_peak = 2.0 * peaks["bf16"]
+        int8_src = "2 x bf16_tflops_sustained of %s (no int8 entry in MEASURED_PEAKS.json)" % peaks["src"]
+        if "int8_peak" in extras:
+            int8_peak = extras["int8_peak"]["sustained_tops"]
+            int8_src = ("measured in this run: %.0f TOP/s sustained over %.0f ms (%.0f burst), resident-operand kind::i8 loop"
+                        % (int8_peak, extras["int8_peak"]["sustained_ms"], extras["int8_peak"]["burst_tops"]))
         cpu_val, cpu_kind, cpu_procs, cpu_dt = (None, None, None, None)
         cpu = None
         if world == 1 and not a.no_cpu:
@@ -435,7 +572,7 @@ def run_gpu_arm(a):
                           peak_source=peaks["src"]),
             roofline_tensor=dict(bound="tensor", achieved=tops_ach, peak=int8_peak / 1.0, unit="TOP/s",
                                  frac=tops_ach / int8_peak,
-                                 peak_source="2 x bf16_tflops_sustained of %s (no int8 entry in MEASURED_PEAKS.json)" % peaks["src"]),
+                                 peak_source=int8_src),
             cpu_baseline=cpu,
             e2e=dict(value=e2e_value, unit="images/s", h2d_bytes_per_step=in_bytes, d2h_bytes_per_step=out_bytes,
                      api="b200_case_submit_host + b200_case_wait (copy of step i+1 overlaps the kernels of step i)",
@@ -443,6 +580,7 @@ def run_gpu_arm(a):
                      blocking_run_host_ms_per_step=wall_ms / a.steps),
             gpu_launches=n_launch * a.steps,
             clocks=clocks)
+        line.update(extras)
         print(json.dumps(line))
     cs.close()
     if world > 1:
@@ -459,6 +597,8 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch op by op instead of replaying a CUDA graph")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the single-GPU extras (int8 peak, conv sweep, other networks, plugin route)")
     a = ap.parse_args()
     if a.impl == "reference":
         return run_reference_arm(a)

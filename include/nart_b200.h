@@ -91,6 +91,15 @@ B200_API int b200_device_status(b200_stream_t stream, int *status_word);
  * modules have no device-side waits (art/modules/cuda_quant/src/cuda_quant_workspace.c). */
 B200_API int b200_selftest_wait_expiry(uint64_t limit_cycles, b200_stream_t stream);
 
+/* The tensor pipe's dense int8 rate on this GPU, measured: every SM issues `mmas_per_sm` back-to-back
+ * tcgen05 kind::i8 MMAs of M128 x N256 x K32 on operands resident in shared memory -- the convolution
+ * kernel's instruction without its loads and its epilogue.  *ms is the launch's device time (CUDA
+ * events on `stream`, which the call synchronizes), *ops the integer operations performed (2 per
+ * multiply-add); ops / ms is the ceiling the convolution's TOP/s are compared with.  A few thousand
+ * MMAs give the burst rate, a second or more of them the rate under the power cap.  No counterpart in
+ * the reference. */
+B200_API int b200_measure_mma_i8_peak(int32_t mmas_per_sm, float *ms, double *ops, b200_stream_t stream);
+
 /* ---- scale decomposition -------------------------------------------------------------------
  * get_quant_scale_int32 / get_quant_scale_int16 / get_quant_scale
  * (art/modules/quant/include/art/quant/quant_helper.h:60-118): `bits` 32, -16 (the uint16

@@ -53,6 +53,7 @@ SIGNATURES = {
     "b200_stream_synchronize": (C.c_int, [vp]),
     "b200_device_status": (C.c_int, [vp, C.POINTER(C.c_int)]),
     "b200_selftest_wait_expiry": (C.c_int, [C.c_uint64, vp]),
+    "b200_measure_mma_i8_peak": (C.c_int, [i32, C.POINTER(f32), C.POINTER(C.c_double), vp]),
     "b200_get_quant_scale": (None, [f32, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int8)]),
     "b200_conv2d_create": (C.c_int, [C.POINTER(ConvParams), vp, vp, C.POINTER(vp)]),
     "b200_conv2d_out_dims": (C.c_int, [vp, pi32, pi32]),

@@ -38,6 +38,10 @@ inline cudaStream_t as_stream(b200_stream_t s) { return reinterpret_cast<cudaStr
 // Per-device int the kernels with bounded waits write a code into when a wait runs out.
 int status_word_ptr(int **dev_ptr);
 
+// Device copy of a 256-byte lookup table, uploaded the first time this table is seen on the current device
+// and cached for the life of the process (runtime.cu).
+int lut_cache_get(const uint8_t lut[256], const uint8_t **dev_ptr);
+
 // Number of SMs of the current device (cached).
 int sm_count();
 

@@ -1101,6 +1101,83 @@ __global__ void __launch_bounds__(32) wait_expiry_probe_kernel(int *status, long
     }
 }
 
+// The tensor pipe's own rate for this kernel's instruction: every SM issues `mmas` MMAs of the shape the
+// 256-wide tiles use (kind::i8, M128 x N256 x K32, u8 x s8 -> s32) back to back on operands that stay in
+// shared memory (pseudo-random bytes: all-zero operands would draw less power and run at other clocks),
+// alternating between two accumulators every 32 MMAs.  No loads, no epilogue: the number it gives is the
+// ceiling the convolution's mainloop is measured against.
+constexpr int kPeakGroup = 32;   // MMAs per commit
+__global__ void __launch_bounds__(128, 1) mma_i8_peak_kernel(int mmas, int *status)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t *smem = smem_raw + (base - raw_addr);
+    constexpr uint32_t kA = 128 * 128, kB = 256 * 128;
+    __shared__ __align__(8) unsigned long long bars[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    for (uint32_t i = threadIdx.x; i < (kA + kB) / 4; i += blockDim.x)
+        reinterpret_cast<uint32_t *>(smem)[i] = (i + blockIdx.x) * 2654435761u;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bars[0]), 1);
+        mbar_init(smem_u32(&bars[1]), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fence_async_smem();
+    if (threadIdx.x < 32) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    if (threadIdx.x < 32) {
+        const uint32_t lead = threadIdx.x == 0 ? 1u : 0u;
+        const uint64_t adesc = make_smem_desc(base, 128), bdesc = make_smem_desc(base + kA, 128);
+        const uint32_t desc_hi = (uint32_t)(adesc >> 32), a_lo = (uint32_t)adesc, b_lo = (uint32_t)bdesc;
+        const uint32_t idesc = (2u << 4) | (0u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+        const int groups = mmas / kPeakGroup;
+        uint32_t phase[2] = { 0, 0 };
+        bool ok = true;
+        for (int gi = 0; gi < groups && ok; ++gi) {
+            const int b = gi & 1;
+            if (gi >= 2) {     // the group two back has drained: at most two groups are queued
+                if (!mbar_wait(smem_u32(&bars[b]), phase[b], &abort_flag)) {
+                    if (lead)
+                        atomicCAS(status, 0, kErrSelfTestWait);
+                    ok = false;
+                    break;
+                }
+                phase[b] ^= 1;
+            }
+            const uint32_t d = tmem_base + (uint32_t)b * 256u;
+#pragma unroll 4
+            for (int j = 0; j < kPeakGroup; ++j)
+                mma_i8(d, a_lo + 2 * (j & 3), b_lo + 2 * (j & 3), desc_hi, idesc, j ? 1u : 0u, lead);
+            mma_commit(smem_u32(&bars[b]), lead);
+        }
+        // the last groups must have finished before tensor memory goes back
+        for (int t = groups < 2 ? 0 : groups - 2; t < groups && ok; ++t) {
+            const int b = t & 1;
+            if (!mbar_wait(smem_u32(&bars[b]), phase[b], &abort_flag)) {
+                if (lead)
+                    atomicCAS(status, 0, kErrSelfTestWait);
+                ok = false;
+            }
+            phase[b] ^= 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 // ---- host side -------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(
     CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -1756,6 +1833,34 @@ int conv_igemm_warm()
     B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
     B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
     B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
+    return B200_OK;
+}
+
+int mma_i8_peak_launch(int mmas_per_sm, float *ms, double *ops, cudaStream_t st)
+{
+    int *status = nullptr;
+    B200_TRY(status_word_ptr(&status));
+    const int mmas = mmas_per_sm / kPeakGroup * kPeakGroup;
+    const size_t smem = 128 * 128 + 256 * 128 + 1024;
+    B200_CUDA_TRY(cudaFuncSetAttribute(mma_i8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    cudaEvent_t e0, e1;
+    B200_CUDA_TRY(cudaEventCreate(&e0));
+    B200_CUDA_TRY(cudaEventCreate(&e1));
+    const int sms = sm_count();
+    B200_CUDA_TRY(cudaEventRecord(e0, st));
+    mma_i8_peak_kernel<<<sms, 128, smem, st>>>(mmas, status);
+    cudaError_t le = cudaGetLastError();
+    B200_CUDA_TRY(cudaEventRecord(e1, st));
+    cudaError_t se = cudaEventSynchronize(e1);
+    float t = 0.f;
+    if (le == cudaSuccess && se == cudaSuccess)
+        se = cudaEventElapsedTime(&t, e0, e1);
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    B200_CUDA_TRY(le);
+    B200_CUDA_TRY(se);
+    *ms = t;
+    *ops = (double)sms * (double)mmas * 2.0 * 128.0 * 256.0 * 32.0;
     return B200_OK;
 }
 

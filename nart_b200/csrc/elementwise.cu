@@ -637,15 +637,9 @@ int b200_relu_u8(
     B200_TRY(relu_build_lut(ialpha, izp, oalpha, ozp, obits, lut));
     if (count == 0)
         return B200_OK;
-    // The table is tiny; it is staged through a stream-ordered allocation so the call stays
-    // asynchronous and needs no per-op state.
-    uint8_t *lut_dev = nullptr;
-    cudaStream_t st = as_stream(stream);
-    B200_CUDA_TRY(cudaMallocAsync((void **)&lut_dev, 256, st));
-    B200_CUDA_TRY(cudaMemcpyAsync(lut_dev, lut, 256, cudaMemcpyHostToDevice, st));
-    int rc = lut_u8_launch(x, y, count, lut_dev, st);
-    B200_CUDA_TRY(cudaFreeAsync(lut_dev, st));
-    return rc;
+    const uint8_t *lut_dev = nullptr;
+    B200_TRY(lut_cache_get(lut, &lut_dev));   // uploaded once per distinct table, then reused
+    return lut_u8_launch(x, y, count, lut_dev, as_stream(stream));
 }
 
 }  // extern "C"

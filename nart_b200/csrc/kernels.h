@@ -141,6 +141,9 @@ void conv_igemm_set_reverse(ConvIgemmPlan *plan, int reverse);
 // Per-process / per-device set-up of the tensor-core kernels (driver entry point, shared-memory
 // attribute): done by the first launch otherwise; plan creation calls it so that runs do not.
 int conv_igemm_warm();
+// Times `mmas_per_sm` back-to-back kind::i8 M128 x N256 x K32 MMAs on every SM (operands resident in shared
+// memory); *ops is the number of integer operations (2 per multiply-add) the launch performed.
+int mma_i8_peak_launch(int mmas_per_sm, float *ms, double *ops, cudaStream_t st);
 // Launches the one-warp kernel whose bounded wait cannot be satisfied (see b200_selftest_wait_expiry).
 int wait_expiry_probe_launch(long long limit_cycles, cudaStream_t st);
 // Resolves the device address of the static scratch array for the current device (conv_static_scratch.cu).

@@ -397,15 +397,10 @@ int b200_pool_u8(
         h, w, method, kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, ceil_mode, ialpha, izp,
         oalpha, ozp, obits, &g, lut, &tab));
     cudaStream_t st = as_stream(stream);
-    uint8_t *lut_dev = nullptr;
-    if (method == 0) {
-        B200_CUDA_TRY(cudaMallocAsync((void **)&lut_dev, 256, st));
-        B200_CUDA_TRY(cudaMemcpyAsync(lut_dev, lut, 256, cudaMemcpyHostToDevice, st));
-    }
-    int rc = pool_launch(x, y, n, c, method, g, lut_dev, tab, st);
-    if (lut_dev)
-        B200_CUDA_TRY(cudaFreeAsync(lut_dev, st));
-    return rc;
+    const uint8_t *lut_dev = nullptr;
+    if (method == 0)
+        B200_TRY(lut_cache_get(lut, &lut_dev));   // uploaded once per distinct table, then reused
+    return pool_launch(x, y, n, c, method, g, lut_dev, tab, st);
 }
 
 }  // extern "C"

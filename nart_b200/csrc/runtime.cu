@@ -4,6 +4,9 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <mutex>
+#include <vector>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -45,6 +48,38 @@ int status_word_ptr(int **dev_ptr)
         g_status_words[dev] = p;
     }
     *dev_ptr = g_status_words[dev];
+    return B200_OK;
+}
+
+// 256-byte lookup tables (relu, max pool) of the flat C-ABI calls: uploaded once per distinct table and
+// device and kept for the life of the process, so that a steady-state call allocates and copies nothing.
+namespace {
+struct LutEntry {
+    int device;
+    uint8_t bytes[256];
+    uint8_t *dev;
+};
+std::mutex g_lut_mutex;
+std::vector<LutEntry> g_luts;
+}  // namespace
+
+int lut_cache_get(const uint8_t lut[256], const uint8_t **dev_ptr)
+{
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_lut_mutex);
+    for (const auto &e : g_luts)
+        if (e.device == dev && memcmp(e.bytes, lut, 256) == 0) {
+            *dev_ptr = e.dev;
+            return B200_OK;
+        }
+    LutEntry e;
+    e.device = dev;
+    memcpy(e.bytes, lut, 256);
+    B200_CUDA_TRY(cudaMalloc((void **)&e.dev, 256));
+    B200_CUDA_TRY(cudaMemcpy(e.dev, lut, 256, cudaMemcpyHostToDevice));
+    g_luts.push_back(e);
+    *dev_ptr = e.dev;
     return B200_OK;
 }
 
@@ -247,6 +282,13 @@ int b200_selftest_wait_expiry(uint64_t limit_cycles, b200_stream_t stream)
     if (limit_cycles == 0 || limit_cycles > 2000000000ull)
         return fail(B200_ERR_INVALID, "selftest: limit of %llu cycles outside 1..2e9 (about one second)", (unsigned long long)limit_cycles);
     return wait_expiry_probe_launch((long long)limit_cycles, as_stream(stream));
+}
+
+int b200_measure_mma_i8_peak(int32_t mmas_per_sm, float *ms, double *ops, b200_stream_t stream)
+{
+    if (!ms || !ops || mmas_per_sm < 64 || mmas_per_sm > 40000000)
+        return fail(B200_ERR_INVALID, "measure_mma_i8_peak: bad argument (64 .. 4e7 MMAs per SM)");
+    return mma_i8_peak_launch(mmas_per_sm, ms, ops, as_stream(stream));
 }
 
 void b200_get_quant_scale(float x, int bits, uint32_t *mult, int8_t *shift)

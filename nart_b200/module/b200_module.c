@@ -53,7 +53,10 @@ typedef struct b200_mem_t {
     mem_t m;
     size_t sz;
     void *dev;
-    void *host;
+    void *host;         /* pinned mirror, allocated the first time the host asks for the data */
+    size_t host_sz;
+    void *nchw_tmp;     /* device staging for cpu_data() of an NHWC tensor, kept between calls */
+    size_t nchw_tmp_sz;
     bool gpu_updated;   /* the device copy is the current one */
     bool nhwc;          /* the device copy is NHWC uint8 with the dims below (set by the op that wrote it) */
     int n, c, h, w;
@@ -70,11 +73,17 @@ static void b200_mem_free(b200_mem_t *m)
 {
     if (m->sz > 0) {
         B200_CALL(b200_free(m->dev));
-        free(m->host);
         m->dev = NULL;
-        m->host = NULL;
         m->sz = 0;
     }
+    if (m->host)
+        B200_CALL(b200_free_host(m->host));
+    if (m->nchw_tmp)
+        B200_CALL(b200_free(m->nchw_tmp));
+    m->host = NULL;
+    m->host_sz = 0;
+    m->nchw_tmp = NULL;
+    m->nchw_tmp_sz = 0;
 }
 
 static void b200_mem_delete(b200_mem_t *m)
@@ -93,17 +102,35 @@ static bool b200_mem_alloc(b200_mem_t *m, size_t sz)
     /* 256 spare bytes: vector loads of a ragged last pixel may read past the tensor */
     B200_CALL(b200_malloc(&m->dev, sz + 256));
     B200_CALL(b200_memset(m->dev, 0, sz + 256, NULL));
-    m->host = realloc(m->host, sz);
-    CHECK_NE(NULL, m->host);
     m->sz = sz;
     m->gpu_updated = false;
     m->nhwc = false;
     return true;
 }
 
+/* The host mirror exists only for tensors the host touches (case inputs and outputs, weights): it is
+ * pinned, so that the copies of b200_mem_data / b200_mem_cpu_data run at full PCIe speed, and sized on
+ * first use.  Intermediate tensors of a parade never get one. */
+static void host_mirror(b200_mem_t *m)
+{
+    if (m->host_sz >= m->sz && m->host)
+        return;
+    void *fresh = NULL;
+    B200_CALL(b200_malloc_host(&fresh, m->sz));
+    CHECK_NE(NULL, fresh);
+    if (m->host) {
+        memcpy(fresh, m->host, m->host_sz);
+        B200_CALL(b200_free_host(m->host));
+    }
+    if (m->sz > m->host_sz)
+        memset((char *)fresh + m->host_sz, 0, m->sz - m->host_sz);
+    m->host = fresh;
+    m->host_sz = m->sz;
+}
+
 static void *b200_mem_data(b200_mem_t *m)
 {
-    if (!m->gpu_updated) {
+    if (!m->gpu_updated && m->host) {
         B200_CALL(b200_memcpy_h2d(m->dev, m->host, m->sz, NULL));
         B200_CALL(b200_stream_synchronize(NULL));
         m->gpu_updated = true;
@@ -114,16 +141,21 @@ static void *b200_mem_data(b200_mem_t *m)
 
 static void *b200_mem_cpu_data(b200_mem_t *m)
 {
+    host_mirror(m);
     if (m->gpu_updated) {
         size_t count = (size_t)m->n * m->c * m->h * m->w;
         if (m->nhwc && count <= m->sz && m->c > 1 && m->h * m->w > 1) {
             /* bring the device copy back to the reference's NCHW before the host reads it */
-            void *tmp = NULL;
-            B200_CALL(b200_malloc(&tmp, count));
+            if (m->nchw_tmp_sz < count) {
+                if (m->nchw_tmp)
+                    B200_CALL(b200_free(m->nchw_tmp));
+                B200_CALL(b200_malloc(&m->nchw_tmp, count));
+                m->nchw_tmp_sz = count;
+            }
+            void *tmp = m->nchw_tmp;
             B200_CALL(b200_nhwc_to_nchw_u8(m->dev, tmp, m->n, m->c, m->h, m->w, m->c, NULL));
             B200_CALL(b200_memcpy_d2h(m->host, tmp, count, NULL));
             B200_CALL(b200_stream_synchronize(NULL));
-            B200_CALL(b200_free(tmp));
         } else {
             B200_CALL(b200_memcpy_d2h(m->host, m->dev, m->sz, NULL));
             B200_CALL(b200_stream_synchronize(NULL));
@@ -203,28 +235,41 @@ static void dims_of(const tensor_t *t, int *n, int *c, int *h, int *w)
 /* Device pointer to a uint8 input in NHWC.  Tensors written by this module's ops already are;
  * tensors the host (or another module) wrote are in the reference's NCHW and are transposed into
  * `scratch` first.  Foreign mem types are uploaded from their host view. */
-static const uint8_t *input_nhwc(tensor_t *t, scratch_t *scratch)
+static const uint8_t *input_nhwc_padded(tensor_t *t, scratch_t *scratch, int c_pad, uint8_t fill)
 {
     int n, c, h, w;
     dims_of(t, &n, &c, &h, &w);
-    size_t count = (size_t)n * c * h * w;
+    if (c_pad < c)
+        c_pad = c;
+    size_t count = (size_t)n * c * h * w, padded = (size_t)n * c_pad * h * w;
     if (t->mem->tp != b200_mem_tp) {
-        scratch_reserve(scratch, 2 * count);
-        uint8_t *stage = (uint8_t *)scratch->buf + count;
+        scratch_reserve(scratch, padded + count);
+        uint8_t *stage = (uint8_t *)scratch->buf + padded;
         B200_CALL(b200_memcpy_h2d(stage, mem_cpu_data(t->mem), count, NULL));
-        if (c == 1 || h * w == 1)
+        if (c_pad == c && (c == 1 || h * w == 1))
             return stage;
-        B200_CALL(b200_nchw_to_nhwc_u8(stage, (uint8_t *)scratch->buf, n, c, h, w, c, 0, NULL));
+        B200_CALL(b200_nchw_to_nhwc_u8(stage, (uint8_t *)scratch->buf, n, c, h, w, c_pad, fill, NULL));
         return (const uint8_t *)scratch->buf;
     }
     b200_mem_t *m = (b200_mem_t *)t->mem;
     const uint8_t *dev = (const uint8_t *)mem_data(t->mem);
-    if (m->nhwc || c == 1 || h * w == 1)
+    if (c_pad == c && (m->nhwc || c == 1 || h * w == 1))
         return dev;
-    scratch_reserve(scratch, count);
-    B200_CALL(b200_nchw_to_nhwc_u8(dev, (uint8_t *)scratch->buf, n, c, h, w, c, 0, NULL));
+    if (m->nhwc) {
+        /* an NHWC tensor of this module (a quantize op ahead of the first conv) that needs more channels:
+         * back to NCHW, then out again with the padding; image-sized, once per run */
+        scratch_reserve(scratch, padded + count);
+        uint8_t *stage = (uint8_t *)scratch->buf + padded;
+        B200_CALL(b200_nhwc_to_nchw_u8(dev, stage, n, c, h, w, c, NULL));
+        B200_CALL(b200_nchw_to_nhwc_u8(stage, (uint8_t *)scratch->buf, n, c, h, w, c_pad, fill, NULL));
+        return (const uint8_t *)scratch->buf;
+    }
+    scratch_reserve(scratch, padded);
+    B200_CALL(b200_nchw_to_nhwc_u8(dev, (uint8_t *)scratch->buf, n, c, h, w, c_pad, fill, NULL));
     return (const uint8_t *)scratch->buf;
 }
+
+static const uint8_t *input_nhwc(tensor_t *t, scratch_t *scratch) { return input_nhwc_padded(t, scratch, 0, 0); }
 
 /* Device pointer of an output tensor; tags its mem as freshly written on the device. */
 static void *output_dev(tensor_t *t, bool nhwc)
@@ -298,6 +343,7 @@ typedef struct {
     qsettings_t q;
     b200_conv_t *plan;
     int plan_c, plan_h, plan_w;
+    int c_pad;              /* channels the plan was built for: 4 for an image of fewer channels, else c */
     scratch_t in_scratch;
 } op_b200_conv_2d_t;
 
@@ -362,7 +408,7 @@ static void op_b200_conv_2d_run(op_t *op)
     op_b200_conv_2d_t *c = (op_b200_conv_2d_t *)op;
     int n, ch, h, w;
     dims_of(op->input_tensors[0], &n, &ch, &h, &w);
-    const uint8_t *x = input_nhwc(op->input_tensors[0], &c->in_scratch);
+    const uint8_t *x = input_nhwc_padded(op->input_tensors[0], &c->in_scratch, c->c_pad, c->q.izp[0]);
     uint8_t *y = (uint8_t *)output_dev(&op->output_tensors[0], true);
     B200_CALL(b200_conv2d_run(c->plan, x, n, y, NULL));
 }
@@ -404,7 +450,25 @@ void op_b200_conv_2d_tp_prepare(op_t *op)
     }
     const uint8_t *wt = (const uint8_t *)mem_cpu_data(op->input_tensors[1]->mem);
     const int32_t *bias = op->input_size == 3 ? (const int32_t *)mem_cpu_data(op->input_tensors[2]->mem) : NULL;
+    /* An image of fewer than four channels (the network's first conv) is padded to four on its way to
+     * NHWC, with weights equal to the zero point -- i.e. zero -- on the added channel: four channels are
+     * what the library's row-lowered tensor-core path for image stems takes. */
+    uint8_t *wpad = NULL;
+    c->c_pad = ch;
+    if (ch < 4 && p.group == 1 && p.act_type == B200_ACT_U8) {
+        const size_t taps = (size_t)p.r * p.s;
+        int k, cc;
+        wpad = (uint8_t *)malloc((size_t)p.k * 4 * taps);
+        memset(wpad, p.wzp, (size_t)p.k * 4 * taps);
+        for (k = 0; k < p.k; ++k)
+            for (cc = 0; cc < ch; ++cc)
+                memcpy(wpad + ((size_t)k * 4 + cc) * taps, wt + ((size_t)k * ch + cc) * taps, taps);
+        p.c = 4;
+        c->c_pad = 4;
+        wt = wpad;
+    }
     B200_CALL(b200_conv2d_create(&p, wt, bias, &c->plan));
+    free(wpad);
     c->plan_c = ch; c->plan_h = h; c->plan_w = w;
     op->run_func = op_b200_conv_2d_run;
 }

@@ -132,7 +132,7 @@ class InnerProduct(Conv2d):
         c, h, w = in_chw
         wt = np.ascontiguousarray(weight, dtype=np.uint8)
         k = wt.shape[0]
-        self.k, self.c = k, c
+        self.k, self.c, self.signed = k, c, False
         wa = _walpha_array(walpha, k)
         b = None if bias is None else np.ascontiguousarray(bias, dtype=np.int32)
         self._h = C.c_void_p()

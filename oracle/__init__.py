@@ -300,6 +300,45 @@ class Ref(_Common, _CommonI8):
         v = self.lib.ref_constant(name.encode(), C.byref(found))
         return int(v) if found.value else None
 
+    def open_engine(self, path):
+        """Loads a serialized case with the reference's deserializer and prepares its parade on the module
+        selected by use_module.  Returns a handle for engine_input / engine_run / engine_output / close_engine:
+        the reference's own calling sequence (host view of the inputs, parade_run, host view of the outputs)."""
+        L = self.lib
+        L.ref_parade_open.restype = C.c_void_p
+        L.ref_parade_open.argtypes = [C.c_char_p]
+        L.ref_parade_io_bytes.restype = C.c_size_t
+        L.ref_parade_io_bytes.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.ref_parade_input_ptr.restype = C.c_void_p
+        L.ref_parade_input_ptr.argtypes = [C.c_void_p, C.c_int]
+        L.ref_parade_output_ptr.restype = C.c_void_p
+        L.ref_parade_output_ptr.argtypes = [C.c_void_p, C.c_int]
+        L.ref_parade_run_only.restype = None
+        L.ref_parade_run_only.argtypes = [C.c_void_p]
+        L.ref_parade_close.argtypes = [C.c_void_p]
+        h = L.ref_parade_open(os.fsencode(path))
+        if not h:
+            raise RuntimeError("the reference could not load %s" % path)
+        return h
+
+    def engine_input(self, h, index, dtype=np.uint8):
+        """The host view of input `index` as a numpy array (no copy); asking for it marks it as written."""
+        n = self.lib.ref_parade_io_bytes(h, 0, index)
+        p = self.lib.ref_parade_input_ptr(h, index)
+        return np.ctypeslib.as_array((C.c_uint8 * n).from_address(p)).view(dtype)
+
+    def engine_run(self, h):
+        self.lib.ref_parade_run_only(h)
+
+    def engine_output(self, h, index, dtype=np.float32):
+        """The host view of output `index` (downloads it from the module's memory if that is newer)."""
+        n = self.lib.ref_parade_io_bytes(h, 1, index)
+        p = self.lib.ref_parade_output_ptr(h, index)
+        return np.ctypeslib.as_array((C.c_uint8 * n).from_address(p)).view(dtype)
+
+    def close_engine(self, h):
+        self.lib.ref_parade_close(h)
+
     def run_engine(self, path, inputs, output_dtypes):
         """Loads a serialized case with the reference's own deserializer and parade, bound to the
         module selected by use_module, and runs it once.  inputs: numpy arrays in the file's input

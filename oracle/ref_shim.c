@@ -583,6 +583,28 @@ REF_API int ref_parade_run(parade_t *parade, const void *const *inputs, void *co
     return 0;
 }
 
+/* The three steps of ref_parade_run on their own, for a driver that keeps its data in the tensors' host
+ * views the way the reference's promark does (tools/promark.cpp:457-492): the host view of an input
+ * (asking for it makes the host copy the current one, so the next run uploads it), parade_run, and the
+ * host view of an output (which downloads it). */
+REF_API void *ref_parade_input_ptr(parade_t *parade, int index)
+{
+    size_t count = 0;
+    tensor_array_t arr = NULL;
+    parade_get_input_tensors(parade, &count, &arr);
+    return index >= 0 && (size_t)index < count ? mem_cpu_data(arr[index]->mem) : NULL;
+}
+
+REF_API void ref_parade_run_only(parade_t *parade) { parade_run(parade); }
+
+REF_API void *ref_parade_output_ptr(parade_t *parade, int index)
+{
+    size_t count = 0;
+    tensor_array_t arr = NULL;
+    parade_get_output_tensors(parade, &count, &arr);
+    return index >= 0 && (size_t)index < count ? mem_cpu_data(arr[index]->mem) : NULL;
+}
+
 REF_API void ref_parade_close(parade_t *parade)
 {
     if (parade)
