@@ -123,6 +123,7 @@ B200_API void b200_get_quant_scale(float x, int bits, uint32_t *mult, int8_t *sh
  *   B200_IGEMM_KGROUP=<1..10>                k-blocks per pipeline stage (must divide a tile's k-blocks)
  *   B200_IGEMM_MMA_WARPS=<1|2>               MMA-issuing warps
  *   B200_IGEMM_PAIR=0                        never pair tiles on one weight tile
+ *   B200_IGEMM_CTA_PAIR=<0|1>                never / wherever possible run on CTA pairs (tcgen05 cta_group::2)
  *   B200_IGEMM_EPI_CONST=0                   never use the uniform-shift epilogue (per-channel constants as kernel parameters)
  * and by b200_case_prepare:
  *   B200_CASE_ZIGZAG=0                       every op walks its tiles first to last (default: each op walks against the
@@ -173,6 +174,8 @@ B200_API int b200_conv2d_create(
 B200_API int b200_conv2d_out_dims(const b200_conv_t *conv, int32_t *oh, int32_t *ow);
 /* The algorithm the plan resolved to (B200_CONV_ALGO_DIRECT or _IGEMM). */
 B200_API int b200_conv2d_algo(const b200_conv_t *conv);
+/* One line of text naming the kernel variant and tiling the plan resolved to (for logs and tuning). */
+B200_API int b200_conv2d_describe(const b200_conv_t *conv, char *buf, size_t len);
 /* x: device NHWC [n][h][w][c]; y: device NHWC [n][oh][ow][k].  Plans with a scratch tensor (the
  * row-lowered 4-channel stem; window sums for wzp != 128) grow it, with a device synchronization,
  * the first time a larger batch arrives; the old tensor is freed then. */

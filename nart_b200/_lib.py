@@ -58,6 +58,7 @@ SIGNATURES = {
     "b200_conv2d_create": (C.c_int, [C.POINTER(ConvParams), vp, vp, C.POINTER(vp)]),
     "b200_conv2d_out_dims": (C.c_int, [vp, pi32, pi32]),
     "b200_conv2d_algo": (C.c_int, [vp]),
+    "b200_conv2d_describe": (C.c_int, [vp, C.c_char_p, sz]),
     "b200_conv2d_run": (C.c_int, [vp, vp, i32, vp, vp]),
     "b200_conv2d_run_acc": (C.c_int, [vp, vp, i32, vp, vp, vp]),
     "b200_conv2d_reserve": (C.c_int, [vp, i32]),

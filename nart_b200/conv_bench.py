@@ -65,7 +65,7 @@ def time_conv(c, k, hw, ks, stride, batch, group=1, algo=ops.ALGO_AUTO, iters=20
     assert ops.device_status() == 0
     ops_count = 2.0 * batch * oh * ow * k * (c // group) * ks * ks
     byts = in_bytes + out_bytes + w.size + 4 * k
-    return dict(c=c, k=k, hw=hw, ks=ks, stride=stride, batch=batch, group=group,
+    return dict(c=c, k=k, hw=hw, ks=ks, stride=stride, batch=batch, group=group, plan=conv.describe(),
                 algo={1: "cuda_core", 2: "tcgen05_igemm"}[conv.algo], ms=ms, tops=ops_count / ms / 1e9,
                 gbs=byts / ms / 1e6, intensity_op_per_byte=ops_count / byts, buffers=nbuf,
                 timing="cuda graph replay" if graph else "eager launches")

@@ -126,6 +126,12 @@ struct IgemmArgs {
     // 1: the M tiles are visited from the last image / row / column tile down to the first, so that a layer
     // starts on the part of its input that the layer before wrote last (and that still sits in L2)
     int rev;
+    // CTA pair (MODE 3): two CTAs of a cluster share every MMA (tcgen05 cta_group::2, M = 256): CTA r of the
+    // pair owns M tile 2 * pm + r of pair tile pm and loads that tile's activations and half r of the
+    // weight tile; the pair tiles are walked as (nt fastest, pm) with the digits step_nt, step_pm of the
+    // number of clusters.
+    int pm_tiles;            // pair tiles along M: ceil(m_tiles / 2)
+    int step_pm;
 };
 
 // Per-channel constants of the uniform-shift epilogue for layers with one channel tile (<= 256 channels).
@@ -139,6 +145,22 @@ struct EpiTab {
 // digits of gridDim.x (computed on the host) with carries, so no role divides inside its loop.
 struct TileWalker {
     int nt, twi, thi, tni;
+    int pm = 0, rank = -1;   // CTA-pair mode (rank >= 0): pair tile index along M and this CTA's rank in its pair
+    __device__ __forceinline__ void decode_pair(const IgemmArgs &g)
+    {
+        int mt = 2 * pm + rank;          // an M tile past the last one decodes to an image index past the batch
+        twi = mt % g.tiles_w;
+        mt /= g.tiles_w;
+        thi = mt % g.tiles_h;
+        tni = mt / g.tiles_h;
+    }
+    __device__ __forceinline__ void init_pair(const IgemmArgs &g, int pair_tile, int cta_rank)
+    {
+        rank = cta_rank;
+        nt = pair_tile % g.n_tiles_n;
+        pm = pair_tile / g.n_tiles_n;
+        decode_pair(g);
+    }
     __device__ __forceinline__ void init(const IgemmArgs &g, int tile)
     {
         nt = tile % g.n_tiles_n;
@@ -150,6 +172,14 @@ struct TileWalker {
     }
     __device__ __forceinline__ void advance(const IgemmArgs &g)
     {
+        if (rank >= 0) {
+            nt += g.step_nt;
+            int carry = 0;
+            if (nt >= g.n_tiles_n) { nt -= g.n_tiles_n; carry = 1; }
+            pm += g.step_pm + carry;
+            decode_pair(g);
+            return;
+        }
         nt += g.step_nt;
         int carry = 0;
         if (nt >= g.n_tiles_n) { nt -= g.n_tiles_n; carry = 1; }
@@ -164,7 +194,8 @@ struct TileWalker {
     // tile coordinates as the roles use them (reversed traversal mirrors every M digit)
     __device__ __forceinline__ int wi(const IgemmArgs &g) const { return g.rev ? g.tiles_w - 1 - twi : twi; }
     __device__ __forceinline__ int hi(const IgemmArgs &g) const { return g.rev ? g.tiles_h - 1 - thi : thi; }
-    __device__ __forceinline__ int ni(const IgemmArgs &g) const { return g.rev ? g.tiles_n - 1 - tni : tni; }
+    // (an M tile past the end -- the odd tail of a CTA pair -- keeps its out-of-range image index)
+    __device__ __forceinline__ int ni(const IgemmArgs &g) const { return (g.rev && tni < g.tiles_n) ? g.tiles_n - 1 - tni : tni; }
 };
 
 // ---- PTX wrappers --------------------------------------------------------------------------------
@@ -246,6 +277,38 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
         ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
+// Loads of a CTA pair: the data lands in this CTA's shared memory, the bytes are counted on the mbarrier of
+// the pair's leading CTA (`bar` is a shared::cluster address).  Plain tiled loads -- every CTA fetches its own box.
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+// The shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t addr, uint32_t rank)
+{
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2, int c3)
 {
     asm volatile(
@@ -277,6 +340,45 @@ __device__ __forceinline__ void tmem_relinquish()
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols)
 {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// The same three for a CTA pair: one warp of each CTA of the pair issues them.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// One MMA over both CTAs of a pair (M = 256): rows 0..127 of A and D live in the leading CTA, rows 128..255 in
+// its peer, each CTA holds half of B's rows; the descriptors are this (the leading) CTA's shared addresses.
+__device__ __forceinline__ void mma_i8_pair(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi, uint32_t idesc,
+                                            uint32_t accumulate, uint32_t issue)
+{
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "setp.ne.b32 q, %6, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "@q tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate), "r"(issue)
+        : "memory");
+}
+// Arrival on `bar` (a shared::cluster address, this CTA's or the peer's) when every MMA of the pair issued so
+// far has completed.  One such commit per CTA that has to hear of it: no multicast form is used.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint32_t issue)
+{
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(bar), "r"(issue)
+        : "memory");
 }
 // D[tmem] (+)= A[smem] * B[smem]^T, 8-bit integer operands, int32 accumulate.  The descriptors
 // come as low words plus the high word both share; `issue` predicates the instruction.
@@ -549,14 +651,16 @@ struct SmemLayout {
 };
 // b_slots: B tiles held in shared memory -- one per pipeline stage, or every k-block of the layer
 // when the weights stay resident.
-__host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int bk, int bn, int groups)
+__host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int bk, int bn, int groups, int bn_b = 0)
 {
+    if (bn_b == 0)
+        bn_b = bn;      // rows of a B tile in this CTA's shared memory (half of bn in a CTA pair)
     SmemLayout L;
     uint32_t o = 0;
     L.a = o;
     o += (uint32_t)a_slots * kTileM * bk;
     L.b = o;
-    uint32_t b_tile = ((uint32_t)bn * bk + 1023u) & ~1023u;
+    uint32_t b_tile = ((uint32_t)bn_b * bk + 1023u) & ~1023u;
     o += (uint32_t)b_slots * b_tile;
     L.out = o;
     o += (uint32_t)groups * kTileM * bn;   // one output staging buffer per epilogue group
@@ -581,7 +685,7 @@ __host__ __device__ inline SmemLayout smem_layout(int a_slots, int b_slots, int 
 //   2: the CTA's tiles go in pairs that share every weight k-block: a stage holds the activation
 //      tiles of both and ONE weight tile, each warp issues the MMAs of its own tile of the pair.
 template <bool HAS_RES, bool HAS_WZP = false, int MODE = 0>
-__global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const __grid_constant__ IgemmArgs g, const __grid_constant__ EpiTab tab)
+__global__ void __launch_bounds__((MODE == 1 || MODE == 2) ? kThreads2 : kThreads, 1) conv_igemm_i8_kernel(const __grid_constant__ IgemmMaps maps, const __grid_constant__ IgemmArgs g, const __grid_constant__ EpiTab tab)
 {
     extern __shared__ uint8_t smem_raw[];
     // the swizzle patterns are functions of the absolute shared address: align the base to 1024
@@ -590,12 +694,18 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
     uint8_t *smem = smem_raw + (base - raw_addr);
     const int kblocks_all = g.r * g.s * (g.c / g.bk);
     const int slots = g.stages * g.kgroup;
-    const SmemLayout L = smem_layout(MODE == 2 ? 2 * slots : slots, g.b_resident ? kblocks_all : slots, g.bk, g.bn, g.groups);
+    constexpr bool PAIR = MODE == 3;
+    uint32_t cta_rank = 0;
+    if (PAIR)
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta_rank));
+    const bool leader = !PAIR || cta_rank == 0;
+    const int bnl = PAIR ? g.bn >> 1 : g.bn;     // rows of B this CTA holds
+    const SmemLayout L = smem_layout(MODE == 2 ? 2 * slots : slots, g.b_resident ? kblocks_all : slots, g.bk, g.bn, g.groups, bnl);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t a_tile_bytes = (uint32_t)kTileM * g.bk;
-    const uint32_t b_tile_bytes = ((uint32_t)g.bn * g.bk + 1023u) & ~1023u;
+    const uint32_t b_tile_bytes = ((uint32_t)bnl * g.bk + 1023u) & ~1023u;
     const uint32_t bar0 = base + L.bars;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (kMaxStages + s); };
@@ -613,7 +723,9 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
         mbar_init(bres_bar, 1);
         for (int s = 0; s < g.acc_stages; ++s) {
             mbar_init(tfull_bar(s), 1);
-            mbar_init(tempty_bar(s), kEpiWarps / g.groups);   // one arrival per warp of the stage's epilogue group
+            // one arrival per warp of the stage's epilogue group (of both CTAs of a pair: the leading CTA's
+            // barrier tells its MMA warp that the accumulator halves of both are free)
+            mbar_init(tempty_bar(s), (kEpiWarps / g.groups) * (PAIR ? 2 : 1));
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -622,16 +734,32 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
         prefetch_map(&maps.y);
     }
     if (warp == 1) {
-        tmem_alloc(base + L.tmem_slot, g.tmem_cols);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(base + L.tmem_slot, g.tmem_cols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(base + L.tmem_slot, g.tmem_cols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR)
+        cluster_sync_all();     // the peer's barriers are initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
     const int m_tiles = g.tiles_w * g.tiles_h * g.tiles_n;
-    const int total_tiles = m_tiles * g.n_tiles_n;
+    // the tile sequence of this CTA: tile0, tile0 + tstride, ...  (a CTA pair walks pair tiles together)
+    const int total_tiles = PAIR ? g.pm_tiles * g.n_tiles_n : m_tiles * g.n_tiles_n;
+    const int tile0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int tstride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    auto walker_init = [&](TileWalker &w) {
+        if (PAIR)
+            w.init_pair(g, tile0, (int)cta_rank);
+        else
+            w.init(g, tile0);
+    };
     const int cchunks = g.c / g.bk;
     const int kblocks = g.r * g.s * cchunks;
 
@@ -654,15 +782,17 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
         // the pair's two tiles and the one weight tile both use (the host has checked that the two
         // tiles share their channel tile).
         constexpr int rings = MODE == 1 ? 2 : 1;
-        constexpr int tiles_per_step = MODE == 0 ? 1 : 2;   // tiles a lane moves on by when its k-block wraps
+        constexpr int tiles_per_step = (MODE == 0 || MODE == 3) ? 1 : 2;   // tiles a lane moves on by when its k-block wraps
         const int ring_slots = slots / rings;
-        if (lane < slots && blockIdx.x < total_tiles) {
+        if (lane < slots && tile0 < total_tiles) {
             const int stage = lane / g.kgroup;
             const int ring = lane / ring_slots, rl = lane - ring * ring_slots;
             const bool first = lane == stage * g.kgroup;
             const uint32_t fb = full_bar(stage), eb = empty_bar(stage);
             const uint32_t a_dst = base + L.a + lane * a_tile_bytes * (MODE == 2 ? 2 : 1), b_dst = base + L.b + lane * b_tile_bytes;
-            const uint32_t tx_bytes = (a_tile_bytes + (g.b_resident ? 0u : (uint32_t)g.bn * g.bk)) * (uint32_t)g.kgroup;
+            // a CTA pair: the leading CTA's barrier counts the bytes of both CTAs
+            const uint32_t tx_bytes = (a_tile_bytes + (g.b_resident ? 0u : (uint32_t)bnl * g.bk)) * (uint32_t)g.kgroup * (PAIR ? 2u : 1u);
+            const uint32_t fb_lead = PAIR ? cluster_addr(fb, 0) : fb;
             if (g.b_resident && lane == 0) {
                 // one channel tile and weights that fit: every k-block of B is loaded once and stays
                 mbar_expect_tx(bres_bar, (uint32_t)kblocks * g.bn * g.bk);
@@ -672,11 +802,11 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
             const int sh_h = g.stride_h - 1, sh_w = g.stride_w - 1;   // strides are 1 or 2
             // this lane's first k-block
             int kb = rl % kblocks;
-            int tile = blockIdx.x;
+            int tile = tile0;
             TileWalker tw;
-            tw.init(g, tile);
+            walker_init(tw);
             for (int i = (rl / kblocks) * tiles_per_step + ring; i > 0; --i) {
-                tile += gridDim.x;
+                tile += tstride;
                 tw.advance(g);
             }
             uint32_t phase = 0;
@@ -705,7 +835,12 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
                         const int xw = (tw.wi(g) << g.tw_sh) + ((dw - pw) >> sh_w);
                         const int n0 = tw.ni(g) * g.tn;
                         const CUtensorMap *amap = &maps.a[ph * 2 + pw];
-                        if (MODE == 2) {
+                        if (PAIR) {
+                            if (first && leader)
+                                mbar_expect_tx(fb, tx_bytes);
+                            tma_load_4d_pair(a_dst, amap, fb_lead, cc, xw, yh, n0);
+                            tma_load_2d_pair(b_dst, &maps.b, fb_lead, kb * g.bk, tw.nt * g.bn + (int)cta_rank * bnl);
+                        } else if (MODE == 2) {
                             // the pair's second tile (absent behind an odd number of tiles): same tap, its own pixels
                             const bool second = tile + (int)gridDim.x < total_tiles;
                             mbar_expect_tx(fb, tx_bytes + (second ? a_tile_bytes : 0u));
@@ -724,14 +859,14 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
                         else
                             tma_load_4d(a_dst, amap, fb, cc, xw, yh, n0);
                         }
-                        if (!g.b_resident)
+                        if (!g.b_resident && !PAIR)
                             tma_load_2d(b_dst, &maps.b, fb, kb * g.bk, tw.nt * g.bn);
                         phase ^= 1;
                         kb += ring_slots;
                         while (kb >= kblocks) {
                             kb -= kblocks;
                             for (int i = 0; i < tiles_per_step; ++i) {
-                                tile += gridDim.x;
+                                tile += tstride;
                                 tw.advance(g);
                             }
                         }
@@ -746,18 +881,19 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
                 }
             }
         }
-    } else if (warp == 1 || (MODE != 0 && warp == kMma2Warp)) {
+    } else if (warp == 1 || ((MODE == 1 || MODE == 2) && warp == kMma2Warp)) {
         // ================= MMA issuer =================
         // The whole warp walks the loop (uniform control flow); lane 0 alone issues.  Descriptors of
         // one operand differ only in the start-address field, so only their low words are computed.
-        {
+        // In a CTA pair the leading CTA's warp issues for both; the peer's has nothing to do.
+        if (leader) {
             const uint32_t lead = lane == 0 ? 1u : 0u;
             // warp r of `rings` issuing warps takes the CTA's tiles r, r + rings, ... and the stages
             // [r * ring_stages, (r + 1) * ring_stages); accumulator stages advance by `rings` as well
             // In pair mode both warps walk the whole ring, stage by stage together: warp r issues for the
             // r-th tile of each pair, on the r-th activation tile of the stage and the shared weight tile.
             constexpr int rings = MODE == 1 ? 2 : 1;
-            constexpr int tile_step = MODE == 0 ? 1 : 2;
+            constexpr int tile_step = (MODE == 0 || MODE == 3) ? 1 : 2;
             const int ring = warp == 1 ? 0 : 1;
             const int ring_stages = g.stages / rings, stage0 = MODE == 1 ? ring * ring_stages : 0;
             int stage = stage0;
@@ -774,14 +910,14 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
             const int ksteps = g.bk / 32;
             const int groups = kblocks / g.kgroup;
             const uint32_t idesc = g.idesc;
-            if (g.b_resident && blockIdx.x < total_tiles && !mbar_wait(bres_bar, 0, abort_flag)) {
+            if (g.b_resident && tile0 < total_tiles && !mbar_wait(bres_bar, 0, abort_flag)) {
                 if (lead)
                     atomicCAS(g.status, 0, kErrMmaFullWait);
                 *abort_flag = 1;
                 ok = false;
             }
-            for (int tile = blockIdx.x + ring * gridDim.x; (MODE == 2 ? tile - ring * (int)gridDim.x : tile) < total_tiles && ok;
-                 tile += tile_step * gridDim.x) {
+            for (int tile = tile0 + ring * tstride; (MODE == 2 ? tile - ring * tstride : tile) < total_tiles && ok;
+                 tile += tile_step * tstride) {
                 // pair mode: the second warp of a pair without a second tile still takes part in the
                 // stage hand-over (its commits arrive at once), it just issues nothing
                 const bool have_tile = MODE != 2 || tile < total_tiles;
@@ -808,6 +944,17 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
                     uint32_t b_lo = b_lo0 + (g.b_resident ? grp : stage) * b_grp;
                     for (int j = 0; j < g.kgroup; ++j, a_lo += a_step, b_lo += b_step) {
                         // a k-block is 1, 2 or 4 MMAs of K = 32 bytes: +2 (16-byte units) inside the swizzle atom
+                        if (PAIR) {
+                            mma_i8_pair(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate, issue);
+                            if (ksteps >= 2)
+                                mma_i8_pair(d_tmem, a_lo + 2, b_lo + 2, desc_hi, idesc, 1, issue);
+                            if (ksteps == 4) {
+                                mma_i8_pair(d_tmem, a_lo + 4, b_lo + 4, desc_hi, idesc, 1, issue);
+                                mma_i8_pair(d_tmem, a_lo + 6, b_lo + 6, desc_hi, idesc, 1, issue);
+                            }
+                            accumulate = 1;
+                            continue;
+                        }
                         mma_i8(d_tmem, a_lo, b_lo, desc_hi, idesc, accumulate, issue);
                         accumulate = 1;
                         if (ksteps >= 2)
@@ -817,6 +964,11 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
                             mma_i8(d_tmem, a_lo + 6, b_lo + 6, desc_hi, idesc, 1, issue);
                         }
                     }
+                    if (PAIR) {
+                        // the stage is free again in both CTAs once these MMAs are done: one commit per CTA
+                        mma_commit_pair(cluster_addr(empty_bar(stage), 0), lead);
+                        mma_commit_pair(cluster_addr(empty_bar(stage), 1), lead);
+                    } else
                     mma_commit(empty_bar(stage), lead);   // frees the smem stage when the group's MMAs are done
                     if (++stage == stage0 + ring_stages) {
                         stage = stage0;
@@ -825,6 +977,10 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
                 }
                 if (!ok)
                     break;
+                if (PAIR) {
+                    mma_commit_pair(cluster_addr(tfull_bar(as), 0), issue);   // both CTAs' halves of the accumulator
+                    mma_commit_pair(cluster_addr(tfull_bar(as), 1), issue);
+                } else
                 mma_commit(tfull_bar(as), issue);         // accumulator complete
                 as += tile_step;
                 if (as >= g.acc_stages) {
@@ -880,10 +1036,17 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
         bool failed = false;   // a wait ran out: skip the work of the remaining tiles, keep meeting the group barriers
 
         TileWalker tw;
-        tw.init(g, blockIdx.x);
+        walker_init(tw);
         for (int i = 0; i < group; ++i)
             tw.advance(g);
-        for (int tile = blockIdx.x + group * gridDim.x; tile < total_tiles; tile += g.groups * gridDim.x) {
+        // a CTA pair's accumulator stages are handed back on the leading CTA's barrier
+        auto tempty_arrive = [&](int stage_idx) {
+            if (PAIR && !leader)
+                mbar_arrive_cluster(cluster_addr(tempty_bar(stage_idx), 0));
+            else
+                mbar_arrive(tempty_bar(stage_idx));
+        };
+        for (int tile = tile0 + group * tstride; tile < total_tiles; tile += g.groups * tstride) {
             const int nt = tw.nt;
             const int ow0 = tw.wi(g) << g.tw_sh, oh0 = tw.hi(g) << g.th_sh, n0 = tw.ni(g) * g.tn;
             const int k0 = nt * g.bn;
@@ -1024,7 +1187,7 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0)
-                        mbar_arrive(tempty_bar(as));
+                        tempty_arrive(as);
                 }
 
                 if (g.use_tma_store) {
@@ -1074,9 +1237,14 @@ __global__ void __launch_bounds__(MODE ? kThreads2 : kThreads, 1) conv_igemm_i8_
     // ---- common exit: every role gets here (all waits are bounded) ---------------------------------
     tc_fence_before();
     __syncthreads();
+    if (PAIR)
+        cluster_sync_all();     // neither CTA leaves (or gives tensor memory back) while its peer still works on the pair
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, g.tmem_cols);
+        if (PAIR)
+            tmem_dealloc_pair(tmem_base, g.tmem_cols);
+        else
+            tmem_dealloc(tmem_base, g.tmem_cols);
     }
 }
 
@@ -1228,6 +1396,12 @@ struct ConvIgemmPlan {
     int groups = 2, acc_stages = 2;
     int cpad = 0;                   // input channels rounded up to a multiple of 32
     int bk = 0, bn = 0, stages = 0, kgroup = 1, ob = 0, kpad = 0, b_resident = 0, a_wide = 0, mma_warps = 1, pair = 0;
+    // Two CTAs of a cluster per MMA (kernel MODE 3).  Whether a launch uses it depends on the batch: the pair
+    // wins 3-6 % once every cluster walks many tiles and loses a little on short launches (cluster launch,
+    // two cluster-wide syncs), so the plan carries both configurations and build_launch picks.
+    int pair_ok = 0, pair_want = -1, stages_pair = 0;
+    int cta_pair = 0;               // the configuration of the current launch
+    int max_clusters = 0;           // co-resident CTA pairs of that kernel on this device
     int n_row_cls = 0, n_col_cls = 0;
     int generic_requant = 0;
     int8_t *w_dev = nullptr;        // [kpad][r][s][c]
@@ -1266,6 +1440,8 @@ struct ConvIgemmPlan {
         IgemmMaps maps;
         IgemmArgs args;
         dim3 grid;
+        size_t smem;
+        int cta_pair;
     };
     static constexpr size_t kMaxSaved = 8;
     std::vector<Saved> saved;
@@ -1459,6 +1635,29 @@ int conv_igemm_create(
                 stages = st;
             }
         }
+        // CTA pair (the kernel's MODE 3): two CTAs of a cluster run every MMA together (cta_group::2, M = 256),
+        // each loading its own activation tile and half of the weight tile.  A 256-wide MMA of one CTA reads
+        // 12 KB of operands from shared memory while TMA writes the next 12 KB into it, which is more than the
+        // shared memory moves per MMA time; the pair halves the weight bytes per SM on both sides.  For the
+        // layers whose mainloop sets the pace: 256-wide tiles with at least 1 KB of reduction per pixel.
+        {
+            const char *e = getenv("B200_IGEMM_CTA_PAIR");     // tuning aid: 0 never, 1 wherever possible
+            p->pair_want = e ? atoi(e) : -1;
+            const bool can = !p->b_resident && !p->a_wide && !p->pair && p->bn % 32 == 0 && p->bn >= 64 && g.wzp_d == 0;
+            const bool automatic = p->bn == 256 && kblocks * p->bk >= 1024;
+            if (can && (p->pair_want == 1 || (p->pair_want == -1 && automatic))) {
+                auto fits_p = [&](int st, int kg) {
+                    return smem_layout(st * kg, st * kg, p->bk, p->bn, p->groups, p->bn / 2).total + 1024 <= 227 * 1024;
+                };
+                int st = kMaxStages;
+                while (st > 2 && (!fits_p(st, kgroup) || st * kgroup > 32))
+                    --st;
+                if (fits_p(st, kgroup) && p->mma_warps == 1) {
+                    p->pair_ok = 1;
+                    p->stages_pair = st;
+                }
+            }
+        }
         p->stages = stages;
         p->kgroup = kgroup;
     }
@@ -1610,6 +1809,17 @@ static void choose_tile(int ow, int oh, int n, int *tw, int *th, int *tn, int mi
         }
 }
 
+void conv_igemm_describe(const ConvIgemmPlan *p, char *buf, size_t len)
+{
+    const char *mode = p->cta_pair ? "cta-pair (cta_group::2, M=256)" : p->pair ? "tile pairs on one weight tile"
+        : p->pair_ok ? "one issuing warp (cta pairs on long launches)"
+        : p->mma_warps == 2 ? "two issuing warps" : "one issuing warp";
+    snprintf(buf, len, "tcgen05 igemm: bn=%d bk=%d stages=%d kgroup=%d groups=%d acc_stages=%d %s%s%s%s", p->bn, p->bk,
+             p->cta_pair ? p->stages_pair : p->stages, p->kgroup, p->groups, p->acc_stages, mode, p->b_resident ? ", weights resident" : "",
+             (p->epi_const && !p->cta_pair) ? ", uniform-shift epilogue" : (p->generic_requant ? ", generic requantize" : ""),
+             p->rev ? ", reversed" : "");
+}
+
 void conv_igemm_set_reverse(ConvIgemmPlan *p, int reverse)
 {
     if (p->rev != (reverse ? 1 : 0)) {
@@ -1625,6 +1835,7 @@ int conv_igemm_set_residual(ConvIgemmPlan *p, const EltwiseArgs &e, int conv_inp
     // whole 32-channel chunks stored through TMA
     if (p->generic_requant || p->g.qmax != 255 || p->g.k % 32 != 0 || p->bn % 32 != 0)
         return fail(B200_ERR_UNSUPPORTED, "conv(igemm): residual add needs the fast requantize form and Cout %% 32 == 0");
+    p->pair_ok = 0;     // the kernel variant with the residual add runs one CTA per tile
     if (e.n_in != 2 || e.qmax != 255 || conv_input < 0 || conv_input > 1)
         return fail(B200_ERR_UNSUPPORTED, "conv(igemm): residual add takes a two-input, 8-bit eltwise SUM");
     const int other = 1 - conv_input;
@@ -1645,6 +1856,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     IgemmArgs &a = p->args;
     memset(&a, 0, sizeof(a));
     a.n = n; a.oh = g.oh; a.ow = g.ow; a.cout = g.k;
+    p->cta_pair = 0;
     a.r = g.r; a.s = g.s; a.pad_h = g.pad_h; a.pad_w = g.pad_w; a.stride_h = g.stride_h; a.stride_w = g.stride_w;
     a.c = p->cpad;
     if (p->a_wide)   // whole swizzle atoms (8 pixels) per row segment, at most 256 8-byte elements
@@ -1655,7 +1867,34 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.tiles_h = (g.oh + a.th - 1) / a.th;
     a.tiles_n = (n + a.tn - 1) / a.tn;
     a.n_tiles_n = p->kpad / p->bn;
-    a.bk = p->bk; a.bn = p->bn; a.stages = p->stages; a.kgroup = p->kgroup; a.groups = p->groups; a.acc_stages = p->acc_stages;
+    const int sms = sm_count();
+    if (!p->attr_set) {
+        B200_TRY(conv_igemm_warm());
+        p->attr_set = true;
+    }
+    if (p->pair_ok) {
+        if (p->max_clusters == 0) {
+            cudaLaunchConfig_t cfg = {};
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+            cfg.gridDim = dim3((unsigned)(sms & ~1));
+            cfg.blockDim = dim3(kThreads);
+            cfg.dynamicSmemBytes = smem_layout(p->stages_pair * p->kgroup, p->stages_pair * p->kgroup, p->bk, p->bn, p->groups, p->bn / 2).total + 1024;
+            cfg.attrs = at;
+            cfg.numAttrs = 1;
+            int nc = 0;
+            if (cudaOccupancyMaxActiveClusters(&nc, conv_igemm_i8_kernel<false, false, 3>, &cfg) != cudaSuccess || nc < 1) {
+                cudaGetLastError();
+                nc = sms / 2;
+            }
+            p->max_clusters = nc < sms / 2 ? nc : sms / 2;
+        }
+        const int pair_tiles = (a.tiles_w * a.tiles_h * a.tiles_n + 1) / 2 * (p->kpad / p->bn);
+        // long launches only: at least six pair tiles for every cluster
+        p->cta_pair = (p->pair_want == 1 || pair_tiles >= 6 * p->max_clusters) ? 1 : 0;
+    }
+    a.bk = p->bk; a.bn = p->bn; a.stages = p->cta_pair ? p->stages_pair : p->stages; a.kgroup = p->kgroup; a.groups = p->groups; a.acc_stages = p->acc_stages;
     a.rcp_cchunks = (uint32_t)(((1ull << 30) + (uint64_t)(p->cpad / p->bk) - 1) / (uint64_t)(p->cpad / p->bk));
     a.rcp_s = (uint32_t)(((1ull << 30) + (uint64_t)g.s - 1) / (uint64_t)g.s); a.ob = p->ob; a.b_resident = p->b_resident; a.a_wide = p->a_wide;
     for (a.tw_sh = 0; (1 << a.tw_sh) < a.tw; ++a.tw_sh) {}
@@ -1663,7 +1902,8 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     for (a.ob_sh = 0; (1 << a.ob_sh) < a.ob; ++a.ob_sh) {}
     // instruction descriptor: D = S32 (2 at bit 4), A = unsigned 8-bit (0 at bit 7), B = signed 8-bit
     // (1 at bit 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
-    a.idesc = (2u << 4) | ((g.act_signed ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(p->bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+    a.idesc = (2u << 4) | ((g.act_signed ? 1u : 0u) << 7) | (1u << 10) | ((uint32_t)(p->bn >> 3) << 17)
+        | ((uint32_t)((p->cta_pair ? 2 * kTileM : kTileM) >> 4) << 24);
     uint32_t cols = 32;
     while (cols < (uint32_t)(p->acc_stages * p->bn))
         cols <<= 1;
@@ -1674,7 +1914,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.ozp = g.ozp; a.qmax = g.qmax; a.relu_lo = g.relu_lo;
     a.generic_requant = p->generic_requant;
     a.out_flip = g.act_signed ? 0x80808080u : 0u;
-    a.epi_const = p->epi_const; a.ushift = p->ushift;
+    a.epi_const = p->cta_pair ? 0 : p->epi_const; a.ushift = p->ushift;
     a.rnd_lo = (int)(uint32_t)(unsigned long long)p->rnd; a.rnd_hi = (int)(p->rnd >> 32);
     a.off32 = p->off32_dev;
     a.rev = p->rev;
@@ -1727,7 +1967,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
         const int ktot = g.r * g.s * p->cpad;
         cuuint64_t dims[2] = { (cuuint64_t)ktot, (cuuint64_t)p->kpad };
         cuuint64_t strides[1] = { (cuuint64_t)ktot };
-        cuuint32_t box[2] = { (cuuint32_t)p->bk, (cuuint32_t)p->bn };
+        cuuint32_t box[2] = { (cuuint32_t)p->bk, (cuuint32_t)(p->cta_pair ? p->bn / 2 : p->bn) };   // a CTA of a pair loads half the rows
         B200_TRY(encode(&p->maps.b, p->w_dev, 2, dims, strides, box, sw_ab));
     }
     if (a.use_tma_store) {
@@ -1743,8 +1983,18 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
         p->maps.y = p->maps.b;
     }
     const int total_tiles = a.tiles_w * a.tiles_h * a.tiles_n * a.n_tiles_n;
-    const int sms = sm_count();
     p->grid = dim3((unsigned)(total_tiles < sms ? total_tiles : sms));
+    p->smem = smem_layout((p->pair ? 2 : 1) * a.stages * p->kgroup, p->b_resident ? g.r * g.s * (p->cpad / p->bk) : a.stages * p->kgroup, p->bk, p->bn, p->groups,
+                          p->cta_pair ? p->bn / 2 : 0).total + 1024;
+    if (p->cta_pair) {
+        // pair tiles (two neighbouring M tiles, one channel tile) over the CTA pairs that fit the device at once
+        a.pm_tiles = (a.tiles_w * a.tiles_h * a.tiles_n + 1) / 2;
+        const int pair_tiles = a.pm_tiles * a.n_tiles_n;
+        const int clusters = pair_tiles < p->max_clusters ? pair_tiles : p->max_clusters;
+        p->grid = dim3((unsigned)(2 * clusters));
+        a.step_nt = clusters % a.n_tiles_n;
+        a.step_pm = clusters / a.n_tiles_n;
+    } else
     {
         int gsz = (int)p->grid.x;
         a.step_nt = gsz % a.n_tiles_n;
@@ -1753,11 +2003,6 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
         gsz /= a.tiles_w;
         a.step_h = gsz % a.tiles_h;
         a.step_n = gsz / a.tiles_h;
-    }
-    p->smem = smem_layout((p->pair ? 2 : 1) * p->stages * p->kgroup, p->b_resident ? g.r * g.s * (p->cpad / p->bk) : p->stages * p->kgroup, p->bk, p->bn, p->groups).total + 1024;
-    if (!p->attr_set) {
-        B200_TRY(conv_igemm_warm());
-        p->attr_set = true;
     }
     p->last_x = x;
     p->last_res = res;
@@ -1789,13 +2034,15 @@ int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cud
                 p->maps = sv.maps;
                 p->args = sv.args;
                 p->grid = sv.grid;
+                p->smem = sv.smem;
+                p->cta_pair = sv.cta_pair;
                 p->last_x = x; p->last_y = y; p->last_n = n; p->last_status = status_word; p->last_res = res;
                 hit = true;
                 break;
             }
         if (!hit) {
             B200_TRY(build_launch(p, x, n, y, status_word, res));
-            ConvIgemmPlan::Saved sv = { x, res, y, n, status_word, p->maps, p->args, p->grid };
+            ConvIgemmPlan::Saved sv = { x, res, y, n, status_word, p->maps, p->args, p->grid, p->smem, p->cta_pair };
             if (p->saved.size() < ConvIgemmPlan::kMaxSaved) {
                 p->saved.push_back(sv);
             } else {
@@ -1811,7 +2058,19 @@ int conv_igemm_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, cud
         conv_igemm_i8_kernel<true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args, p->tab);
     else if (wsum != nullptr)
         conv_igemm_i8_kernel<false, true><<<p->grid, kThreads, p->smem, st>>>(p->maps, p->args, p->tab);
-    else if (p->pair)
+    else if (p->cta_pair) {
+        cudaLaunchConfig_t cfg = {};
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.gridDim = p->grid;
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = p->smem;
+        cfg.stream = st;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, conv_igemm_i8_kernel<false, false, 3>, p->maps, p->args, p->tab));
+    } else if (p->pair)
         conv_igemm_i8_kernel<false, false, 2><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args, p->tab);
     else if (p->mma_warps == 2)
         conv_igemm_i8_kernel<false, false, 1><<<p->grid, kThreads2, p->smem, st>>>(p->maps, p->args, p->tab);
@@ -1833,6 +2092,7 @@ int conv_igemm_warm()
     B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
     B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
     B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
+    B200_CUDA_TRY((cudaFuncSetAttribute(conv_igemm_i8_kernel<false, false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)));
     return B200_OK;
 }
 

@@ -309,6 +309,22 @@ int b200_conv2d_out_dims(const b200_conv_t *conv, int32_t *oh, int32_t *ow)
 
 int b200_conv2d_algo(const b200_conv_t *conv) { return conv ? conv->algo : B200_ERR_INVALID; }
 
+int b200_conv2d_describe(const b200_conv_t *conv, char *buf, size_t len)
+{
+    if (!conv || !buf || len == 0)
+        return fail(B200_ERR_INVALID, "conv(describe): bad argument");
+    if (conv->algo == B200_CONV_ALGO_IGEMM && conv->igemm) {
+        conv_igemm_describe(conv->igemm, buf, len);
+        if (conv->lowered) {
+            size_t used = strlen(buf);
+            snprintf(buf + used, len - used, ", on the row-lowered image");
+        }
+    } else {
+        snprintf(buf, len, "CUDA cores (dp4a)%s", conv->g.group == conv->g.c && conv->g.group == conv->g.k ? ", depthwise" : "");
+    }
+    return B200_OK;
+}
+
 int b200_conv2d_run(b200_conv_t *conv, const uint8_t *x, int32_t n, uint8_t *y, b200_stream_t stream)
 {
     if (!conv || n < 0 || (n > 0 && (!x || !y)))

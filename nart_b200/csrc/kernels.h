@@ -138,6 +138,8 @@ void conv_igemm_destroy(ConvIgemmPlan *plan);
 // Direction in which a launch walks its output tiles: 0 first to last, 1 last to first.  Results do not
 // depend on it; a consumer that walks against its producer's direction starts on data still in L2.
 void conv_igemm_set_reverse(ConvIgemmPlan *plan, int reverse);
+// One line of text naming the plan's tiling and kernel variant.
+void conv_igemm_describe(const ConvIgemmPlan *plan, char *buf, size_t len);
 // Per-process / per-device set-up of the tensor-core kernels (driver entry point, shared-memory
 // attribute): done by the first launch otherwise; plan creation calls it so that runs do not.
 int conv_igemm_warm();

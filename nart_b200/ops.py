@@ -92,6 +92,11 @@ class Conv2d:
         check(lib.b200_conv2d_run(self._h, x.data_ptr(), n, y.data_ptr(), _stream()))
         return y
 
+    def describe(self) -> str:
+        buf = C.create_string_buffer(256)
+        check(lib.b200_conv2d_describe(self._h, buf, 256))
+        return buf.value.decode()
+
     def fuse_residual_add(self, conv_input, ialpha, izp, oalpha, ozp, obits=8, coeff=None, relu=False):
         """Folds ``eltwise_sum((conv(x), res)[order], ...)`` into this plan (b200_conv2d_fuse_residual_add);
         raises B200Error (status ERR_UNSUPPORTED) when the plan cannot take it."""

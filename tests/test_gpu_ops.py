@@ -400,3 +400,41 @@ def test_bounded_wait_expiry_is_reported_and_the_context_survives(ops, port):
     assert_same(got.reshape(want.shape).view(np.uint32), want.view(np.uint32), "after an expired wait")
     assert ops.device_status() == 0
     cs.close()
+
+
+@pytest.mark.parametrize("shape", [(256, 256, 14, 3, 1, 5), (512, 256, 7, 3, 2, 3), (1024, 512, 7, 1, 1, 9), (128, 320, 9, 3, 1, 2)])
+def test_conv_on_cta_pairs(ops, port, monkeypatch, shape):
+    """The kernel variant in which two CTAs of a cluster run every MMA together (tcgen05 cta_group::2, M = 256),
+    forced onto small shapes: odd numbers of M tiles (the second CTA of the last pair has no tile), several
+    channel tiles, stride 2, a channel tile narrower than 256."""
+    c, k, h, ks, st, batch = shape
+    monkeypatch.setenv("B200_IGEMM_CTA_PAIR", "1")
+    x, wt, bias, walpha = conv_inputs(700 + c + k + h, batch, c, h, h, k, ks, ks)
+    q = dict(ialpha=0.02, izp=119, wzp=128, oalpha=0.05 * np.sqrt(c * ks * ks) / 8, ozp=3)
+    conv = ops.Conv2d(wt, bias, in_hw=(h, h), stride=(st, st), pad=(ks // 2, ks // 2), algo=ops.ALGO_IGEMM, walpha=walpha,
+                      relu=True, **q)
+    y = conv(to_dev_nhwc(x))
+    assert "cta-pair" in conv.describe(), conv.describe()
+    assert ops.device_status() == 0
+    want = port.conv2d_u8(x, wt, bias, (st, st), (ks // 2, ks // 2), 1, walpha=walpha, relu=True, **q)
+    assert_same(to_host_nchw(y), want, "cta pair %s" % (shape,))
+
+
+def test_conv_picks_cta_pairs_on_long_launches(ops, port):
+    """Without any switch a 256-wide, reduction-heavy layer runs on CTA pairs once the launch is long enough
+    (six pair tiles per cluster), and on single CTAs below that; both give the restatement's bytes."""
+    c = k = 256
+    h, ks = 14, 3
+    x, wt, bias, walpha = conv_inputs(4321, 640, c, h, h, k, ks, ks)
+    q = dict(ialpha=0.02, izp=128, wzp=128, oalpha=0.05 * np.sqrt(c * ks * ks) / 8, ozp=0)
+    conv = ops.Conv2d(wt, bias, in_hw=(h, h), stride=(1, 1), pad=(1, 1), algo=ops.ALGO_IGEMM, walpha=walpha, relu=True, **q)
+    xd = to_dev_nhwc(x)
+    y_small = conv(xd[:8].contiguous())
+    assert "cta-pair (" not in conv.describe(), conv.describe()
+    y = conv(xd)
+    assert "cta-pair (" in conv.describe(), conv.describe()
+    assert ops.device_status() == 0
+    pick = [0, 7, 320, 639]
+    want = port.conv2d_u8(x[pick], wt, bias, (1, 1), (1, 1), 1, walpha=walpha, relu=True, **q)
+    assert_same(to_host_nchw(y[pick]), want, "long launch on cta pairs")
+    assert_same(to_host_nchw(y_small[[0, 7]]), want[:2], "short launch on single CTAs")
