@@ -393,23 +393,36 @@ namespace b200 {
 
 // Images of up to four channels (the network input, C = 3) into 4-channel NHWC pixels: a thread
 // reads four consecutive pixels of every plane (one word each) and writes four pixels (16 bytes).
-// The pixel count of a plane must be a multiple of 4 and the planes word aligned.
+// The pixel count of a plane must be a multiple of 4 and the planes word aligned.  Four such quads
+// per thread and round, a grid stride apart, with all their loads issued before the first is used:
+// one quad per round keeps 12 bytes per thread in flight, too few to cover the memory latency.
 __global__ void __launch_bounds__(256) nchw_to_nhwc_c4_kernel(
     const uint8_t *__restrict__ x, uint4 *__restrict__ y, int c, uint32_t quads_per_image, uint32_t total, uint8_t fill)
 {
+    constexpr int UNR = 4;
     const uint32_t fill4 = (uint32_t)fill * 0x01010101u;
-    for (uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
-        const uint32_t img = idx / quads_per_image, q = idx - img * quads_per_image;
-        const uint32_t *planes = reinterpret_cast<const uint32_t *>(x) + (size_t)img * c * quads_per_image + q;
-        uint32_t p[4];
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t idx0 = blockIdx.x * blockDim.x + threadIdx.x; idx0 < total; idx0 += UNR * stride) {
+        uint32_t p[UNR][4];
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-            p[ch] = ch < c ? __ldg(planes + (size_t)ch * quads_per_image) : fill4;
-        // 4x4 byte transpose: word j of the result holds byte j of every plane
-        const uint32_t t0 = __byte_perm(p[0], p[1], 0x5140), t1 = __byte_perm(p[2], p[3], 0x5140);
-        const uint32_t t2 = __byte_perm(p[0], p[1], 0x7362), t3 = __byte_perm(p[2], p[3], 0x7362);
-        y[idx] = make_uint4(__byte_perm(t0, t1, 0x5410), __byte_perm(t0, t1, 0x7632),
-                            __byte_perm(t2, t3, 0x5410), __byte_perm(t2, t3, 0x7632));
+        for (int u = 0; u < UNR; ++u) {
+            const uint32_t idx = idx0 + u * stride;
+            const uint32_t img = idx / quads_per_image, q = idx - img * quads_per_image;
+            const uint32_t *planes = reinterpret_cast<const uint32_t *>(x) + (size_t)img * c * quads_per_image + q;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch)
+                p[u][ch] = (ch < c && idx < total) ? __ldg(planes + (size_t)ch * quads_per_image) : fill4;
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const uint32_t idx = idx0 + u * stride;
+            // 4x4 byte transpose: word j of the result holds byte j of every plane
+            const uint32_t t0 = __byte_perm(p[u][0], p[u][1], 0x5140), t1 = __byte_perm(p[u][2], p[u][3], 0x5140);
+            const uint32_t t2 = __byte_perm(p[u][0], p[u][1], 0x7362), t3 = __byte_perm(p[u][2], p[u][3], 0x7362);
+            if (idx < total)
+                y[idx] = make_uint4(__byte_perm(t0, t1, 0x5410), __byte_perm(t0, t1, 0x7632),
+                                    __byte_perm(t2, t3, 0x5410), __byte_perm(t2, t3, 0x7632));
+        }
     }
 }
 
@@ -531,9 +544,9 @@ int b200_nchw_to_nhwc_u8(
         return B200_OK;
     const int P = h * w;
     if (c_pad == 4 && P % 4 == 0 && (((uintptr_t)x) & 3) == 0 && (((uintptr_t)y) & 15) == 0
-        && (size_t)n * (P / 4) < 0xffffffffull) {
+        && (size_t)n * (P / 4) < 0xf0000000ull) {   // 32-bit indices, with room for the unrolled rounds past the end
         const uint32_t quads = (uint32_t)(P / 4), total = (uint32_t)n * quads;
-        const int blocks = resident_grid<nchw_to_nhwc_c4_kernel, 256>(((size_t)total + 255) / 256);
+        const int blocks = resident_grid<nchw_to_nhwc_c4_kernel, 256>(((size_t)total + 1023) / 1024);   // four quads per thread and round
         nchw_to_nhwc_c4_kernel<<<blocks, 256, 0, as_stream(stream)>>>(x, reinterpret_cast<uint4 *>(y), c, quads, total, fill);
         B200_CUDA_TRY(cudaGetLastError());
         return B200_OK;

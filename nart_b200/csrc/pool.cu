@@ -39,6 +39,23 @@ __device__ __forceinline__ void store_words(uint8_t *p, const uint32_t (&wv)[(VE
     }
 }
 
+// Byte-wise unsigned maximum without the emulated SIMD-in-a-word intrinsics (__vmaxu4 expands to
+// about eight integer instructions on this architecture): the four bytes of a word are spread over
+// two words of two 16-bit lanes each (one byte-permute apiece), maxima run on those with the native
+// max.u16x2, and one byte-permute packs the result.
+struct U16x4 {
+    uint32_t lo, hi;   // bytes 0, 1 and bytes 2, 3 of the word, zero-extended to 16 bits
+};
+__device__ __forceinline__ U16x4 spread_bytes(uint32_t w) { return { __byte_perm(w, 0, 0x4140), __byte_perm(w, 0, 0x4342) }; }
+__device__ __forceinline__ uint32_t pack_bytes(const U16x4 &v) { return __byte_perm(v.lo, v.hi, 0x6420); }
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b)
+{
+    uint32_t d;
+    asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+    return d;
+}
+__device__ __forceinline__ U16x4 max_u16x4(const U16x4 &a, const U16x4 &b) { return { max_u16x2(a.lo, b.lo), max_u16x2(a.hi, b.hi) }; }
+
 // MAX: running byte-wise maximum starting from 0 (pool.c:140-148), then a 256-entry table that
 // holds sat_u(rshift_rn(mult16 * (max - izp), shift) + ozp) for every possible maximum, built on
 // the host with the exact arithmetic.
@@ -63,19 +80,22 @@ __global__ void __launch_bounds__(256) pool_max_kernel(
         int he = min(hs + g.kernel_h, g.h), we = min(ws + g.kernel_w, g.w);
         hs = max(hs, 0);
         ws = max(ws, 0);
-        uint32_t mx[W];
+        U16x4 run[W];
 #pragma unroll
         for (int j = 0; j < W; ++j)
-            mx[j] = 0;
+            run[j] = { 0u, 0u };
         for (int iy = hs; iy < he; ++iy)
             for (int ix = ws; ix < we; ++ix) {
                 uint32_t v[W];
                 load_words<VEC>(x + (((size_t)n * g.h + iy) * g.w + ix) * g.c + (size_t)ci * VEC, v);
 #pragma unroll
                 for (int j = 0; j < W; ++j)
-                    mx[j] = __vmaxu4(mx[j], v[j]);
+                    run[j] = max_u16x4(run[j], spread_bytes(v[j]));
             }
-        uint32_t o[W];
+        uint32_t mx[W], o[W];
+#pragma unroll
+        for (int j = 0; j < W; ++j)
+            mx[j] = pack_bytes(run[j]);
 #pragma unroll
         for (int j = 0; j < W; ++j) {
             if constexpr (VEC == 1)
@@ -125,20 +145,31 @@ __global__ void __launch_bounds__(256) pool_max_pair_kernel(
                 if ((unsigned)iy < (unsigned)g.h && (unsigned)ix < (unsigned)g.w)
                     q[r][j] = __ldg(img + ((uint32_t)iy * (uint32_t)g.w + (uint32_t)ix) * cv);
             }
-        uint32_t m0[4] = { 0, 0, 0, 0 }, m1[4] = { 0, 0, 0, 0 };
+        // separable: the maximum down each of the UW columns first, then across the KW columns of each
+        // output; the columns the two windows share are reduced once
+        U16x4 col[UW][4];
 #pragma unroll
-        for (int r = 0; r < KH; ++r)
+        for (int j = 0; j < UW; ++j) {
+            col[j][0] = spread_bytes(q[0][j].x); col[j][1] = spread_bytes(q[0][j].y);
+            col[j][2] = spread_bytes(q[0][j].z); col[j][3] = spread_bytes(q[0][j].w);
 #pragma unroll
-            for (int j = 0; j < UW; ++j) {
-                if (j < KW) {
-                    m0[0] = __vmaxu4(m0[0], q[r][j].x); m0[1] = __vmaxu4(m0[1], q[r][j].y);
-                    m0[2] = __vmaxu4(m0[2], q[r][j].z); m0[3] = __vmaxu4(m0[3], q[r][j].w);
-                }
-                if (j >= SW) {
-                    m1[0] = __vmaxu4(m1[0], q[r][j].x); m1[1] = __vmaxu4(m1[1], q[r][j].y);
-                    m1[2] = __vmaxu4(m1[2], q[r][j].z); m1[3] = __vmaxu4(m1[3], q[r][j].w);
-                }
+            for (int r = 1; r < KH; ++r) {
+                col[j][0] = max_u16x4(col[j][0], spread_bytes(q[r][j].x)); col[j][1] = max_u16x4(col[j][1], spread_bytes(q[r][j].y));
+                col[j][2] = max_u16x4(col[j][2], spread_bytes(q[r][j].z)); col[j][3] = max_u16x4(col[j][3], spread_bytes(q[r][j].w));
             }
+        }
+        uint32_t m0[4], m1[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            U16x4 a = col[0][i], b = col[SW][i];
+#pragma unroll
+            for (int j = 1; j < KW; ++j) {
+                a = max_u16x4(a, col[j][i]);
+                b = max_u16x4(b, col[SW + j][i]);
+            }
+            m0[i] = pack_bytes(a);
+            m1[i] = pack_bytes(b);
+        }
         if (!IDENT) {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {

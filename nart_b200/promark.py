@@ -1,7 +1,8 @@
 """Times a serialized case on the GPU case runner, with the options and the report of the
 reference's benchmark driver (tools/promark.cpp:208-522 of ModelTC/NART):
 
-    python -m nart_b200.promark -m engine.bin [-n runs] [-b batch] [-r name:n,c,h,w] [-i input.bin ...] [-s] [-d] [-y]
+    python -m nart_b200.promark -m engine.bin [-c runtime.json] [-n runs] [-b batch] [-r name:n,c,h,w]
+                                [-i input.bin ...] [-s] [-d] [-y] [--gpus N]
 
   -m  the case file (format version 2)
   -n  timed runs (default 10), after one warm-up run
@@ -14,9 +15,14 @@ reference's benchmark driver (tools/promark.cpp:208-522 of ModelTC/NART):
   -y  include the host<->device copies in the timed region (otherwise the device-resident run)
   --fuse  fold residual adds into the convs that feed them
 
-promark's `-c` (runtime JSON choosing the modules) has no meaning here: this driver always runs the
-b200 case runner.  To run the same file through the reference's own parade, list "b200" in the
-runtime JSON of the reference's promark.
+  -c  the runtime JSON of the reference's driver (promark.cpp:136-187, 314-321):
+      {"workspaces": {"b200": {}}, "input_workspace": "b200"}.  This driver has one backend, so the
+      file must list the workspace "b200" and nothing else (any other name is the error the
+      reference reports for a module it cannot find); "b200": {"device": 2} picks the GPU, as the
+      NART_B200_DEVICE variable does for the plugin.  Without -c: the b200 workspace on the current
+      device.
+  --gpus N  one replica of the case per GPU (child processes, each with the full batch on its own
+      device, no communication between them); the report adds the sum of their rates
 """
 from __future__ import annotations
 
@@ -25,6 +31,68 @@ import sys
 import time
 
 import numpy as np
+
+
+def parse_runtime_config(path):
+    """Reads the reference driver's runtime JSON and returns the device the "b200" workspace asks for
+    (None: the current one).  Raises ValueError with the reference's kind of message for a workspace
+    this driver cannot serve or a malformed file."""
+    import json
+    with open(path) as f:
+        try:
+            cfg = json.load(f)
+        except json.JSONDecodeError as e:
+            raise ValueError("runtime config %s is not JSON: %s" % (path, e))
+    ws = cfg.get("workspaces")
+    if not isinstance(ws, dict) or not ws:
+        raise ValueError('runtime config needs a "workspaces" object')
+    for name in ws:
+        if name != "b200":
+            raise ValueError("module [%s] not found: this driver serves the workspace \"b200\" only" % name)
+    if cfg.get("input_workspace", "b200") != "b200":
+        raise ValueError('"input_workspace" must be "b200"')
+    settings = ws["b200"] if isinstance(ws["b200"], dict) else {}
+    dev = settings.get("device")
+    if dev is not None and (not isinstance(dev, int) or dev < 0):
+        raise ValueError('"device" must be a non-negative integer')
+    return dev
+
+
+def run_replicas(a, argv):
+    """--gpus N: N child processes of this driver, child i on device i, same arguments otherwise."""
+    import re
+    import subprocess
+    args = []
+    skip = False
+    for tok in argv:                      # drop --gpus / --device of the parent
+        if skip:
+            skip = False
+            continue
+        if tok in ("--gpus", "--device"):
+            skip = True
+            continue
+        if tok.startswith("--gpus=") or tok.startswith("--device="):
+            continue
+        args.append(tok)
+    import os
+    env = dict(os.environ)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))      # the children import this package too
+    env["PYTHONPATH"] = root + (os.pathsep + env["PYTHONPATH"] if env.get("PYTHONPATH") else "")
+    procs = [subprocess.Popen([sys.executable, "-m", "nart_b200.promark"] + args + ["--device", str(i)], env=env,
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for i in range(a.gpus)]
+    total, failed = 0.0, 0
+    for i, pr in enumerate(procs):
+        out, _ = pr.communicate()
+        m = re.search(r"([0-9.]+) images/s at batch", out)
+        if pr.returncode != 0 or not m:
+            failed += 1
+            print("replica %d failed (exit %d):\n%s" % (i, pr.returncode, out[-2000:]), file=sys.stderr)
+            continue
+        rate = float(m.group(1))
+        total += rate
+        print("replica %d on device %d: %.1f images/s" % (i, i, rate))
+    print("%d replicas: %.1f images/s" % (a.gpus - failed, total))
+    return 1 if failed else 0
 
 
 def main(argv=None):
@@ -38,10 +106,27 @@ def main(argv=None):
     ap.add_argument("-d", dest="random", action="store_true")
     ap.add_argument("-y", dest="copies", action="store_true")
     ap.add_argument("--fuse", action="store_true")
+    ap.add_argument("-c", dest="config", default=None)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--device", type=int, default=None, help=argparse.SUPPRESS)   # set for the children of --gpus
     a = ap.parse_args(argv)
+
+    device = a.device
+    if a.config:
+        try:
+            device_from_cfg = parse_runtime_config(a.config)
+        except ValueError as e:
+            print("Error: %s" % e, file=sys.stderr)
+            return 1
+        if device is None:
+            device = device_from_cfg
+    if a.gpus > 1:
+        return run_replicas(a, sys.argv[1:] if argv is None else list(argv))
 
     import torch
     from . import engine
+    if device is not None:
+        torch.cuda.set_device(device)
     print("parse args ...")
     model = engine.read_engine(a.model)
     inp = model["inputs"][0]

@@ -44,3 +44,29 @@ def test_written_case_runs_on_the_reference_parade(ref, tmp_path):
     (got,) = ref.run_engine(path, [x], [np.float32])
     want, _, _ = run_net(spec, x, ref, per_channel=False)
     np.testing.assert_array_equal(got.view(np.uint32), want.reshape(-1).view(np.uint32))
+
+
+def test_promark_runtime_config(tmp_path):
+    """The reference driver's runtime JSON (tools/promark.cpp:136-187, 314-321) as this driver reads it: the
+    workspace "b200" and no other, an optional device."""
+    import json
+
+    import pytest
+    from nart_b200 import promark
+
+    def write(obj, name="cfg.json"):
+        path = os.path.join(tmp_path, name)
+        with open(path, "w") as f:
+            f.write(obj if isinstance(obj, str) else json.dumps(obj))
+        return path
+
+    assert promark.parse_runtime_config(write({"workspaces": {"b200": {}}, "input_workspace": "b200"})) is None
+    assert promark.parse_runtime_config(write({"workspaces": {"b200": {"device": 3}}})) == 3
+    for bad, text in (({"workspaces": {"quant": {}}, "input_workspace": "quant"}, "module [quant] not found"),
+                      ({"workspaces": {"b200": {}, "default": {}}}, "module [default] not found"),
+                      ({"workspaces": {"b200": {}}, "input_workspace": "cuda"}, "input_workspace"),
+                      ({"workspaces": {}}, "workspaces"),
+                      ({"workspaces": {"b200": {"device": -1}}}, "device"),
+                      ("{not json", "not JSON")):
+        with pytest.raises(ValueError, match=__import__("re").escape(text)):
+            promark.parse_runtime_config(write(bad))

@@ -65,6 +65,25 @@ def test_promark_cli(port, tmp_path, monkeypatch, capsys):
     assert_same(got.view(np.uint32), want.reshape(-1).view(np.uint32), "promark -s")
     assert promark.main(["-m", path, "-n", "2", "-b", "4", "-d"]) == 0      # device-resident timing, other batch
 
+    # -c: the reference driver's runtime JSON; one backend here, so "b200" is the only workspace it may list
+    import json
+    with open(os.path.join(tmp_path, "b200.json"), "w") as f:
+        json.dump({"workspaces": {"b200": {"device": 0}}, "input_workspace": "b200"}, f)
+    with open(os.path.join(tmp_path, "quant.json"), "w") as f:
+        json.dump({"workspaces": {"quant": {}}, "input_workspace": "quant"}, f)
+    capsys.readouterr()
+    assert promark.main(["-m", path, "-c", "b200.json", "-n", "1"]) == 0
+    assert promark.main(["-m", path, "-c", "quant.json", "-n", "1"]) == 1
+    assert "module [quant] not found" in capsys.readouterr().err
+    # --gpus: replicas as child processes (one here: the test asks for no more GPUs than it is sure to have)
+    import torch
+    rc = promark.main(["-m", path, "-n", "2", "-b", "2", "--gpus", "2"])
+    cap = capsys.readouterr()
+    if torch.cuda.device_count() >= 2:
+        assert rc == 0 and "2 replicas:" in cap.out
+    else:       # the second replica finds no device: reported, the first one still counted
+        assert rc == 1 and "replica 1 failed" in cap.err and "replica 0 on device 0:" in cap.out and "1 replicas:" in cap.out
+
 
 def test_promark_reshape(port, tmp_path, monkeypatch, capsys):
     """-r name:n,c,h,w: the recorded input shape is replaced before the case is prepared and every later
