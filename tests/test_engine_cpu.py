@@ -70,3 +70,23 @@ def test_promark_runtime_config(tmp_path):
                       ("{not json", "not JSON")):
         with pytest.raises(ValueError, match=__import__("re").escape(text)):
             promark.parse_runtime_config(write(bad))
+
+
+def test_art_runtime_context(tmp_path):
+    """nart_b200.art mirrors the reference's nart.art (python/nart/art/__init__.py:31-55): a context from the
+    runtime JSON; one backend, so only the workspace "b200" loads."""
+    import json
+
+    from nart_b200 import art
+    path = os.path.join(tmp_path, "engine.bin.json")
+    with open(path, "w") as f:
+        json.dump({"workspaces": {"b200": {}}, "input_workspace": "b200"}, f)
+    ctx = art.create_context_from_json(path)
+    assert ctx.loaded_workspaces == ["b200"] and ctx.input_module == "b200"
+    assert art.create_context_for_target("b200").loaded_workspaces == ["b200"]
+    with pytest.raises(RuntimeError, match="module \\[quant\\] not found"):
+        art.RuntimeContext(["quant"], "quant")
+    with pytest.raises(RuntimeError, match="input workspace"):
+        art.RuntimeContext(["b200"], "default")
+    with pytest.raises(KeyError):
+        art.create_context_for_target("cuda")

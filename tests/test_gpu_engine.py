@@ -111,3 +111,63 @@ def test_promark_reshape(port, tmp_path, monkeypatch, capsys):
     got = np.fromfile(os.path.join(tmp_path, "nart-out-%s.bin" % out_name), dtype=np.float32)
     assert got.size == want.size == 3 * 48 * 6 * 5
     assert_same(got.view(np.uint32), want.reshape(-1).view(np.uint32), "promark -r")
+
+
+def test_art_python_interface(port, tmp_path):
+    """nart_b200.art: the reference's Python runtime interface (python/nart/art/__init__.py, the pybind Parade of
+    python/src/art/module.cpp:285-509) on the case runner -- load, shapes and dtypes, run with dicts of arrays,
+    its argument checks, reshape."""
+    import json
+
+    from nart_b200 import art, engine, nets
+    spec = nets.resnet(18, seed=23, hw=64, width_div=4, spread=True, num_classes=10)
+    path = os.path.join(tmp_path, "engine.bin")
+    engine.write_engine(spec, path, batch=2)
+    with open(path + ".json", "w") as f:
+        json.dump({"workspaces": {"b200": {}}, "input_workspace": "b200"}, f)
+    ctx = art.create_context_from_json(path + ".json")
+    parade = art.load_parade(path, ctx)
+    (iname,), (oname,) = parade.get_input_names(), parade.get_output_names()
+    assert parade.input_shapes() == {iname: [2, 3, 64, 64]} and parade.output_shapes() == {oname: [2, 10, 1, 1]}
+    assert parade.get_tensor_dtype(iname) == "uint8" and parade.get_tensor_dtype(oname) == "float32"
+    assert parade.get_tensor_shape(oname) == [2, 10, 1, 1]
+    inputs, outputs = art.get_empty_io(parade)
+    x = np.random.default_rng(5).integers(0, 256, (2, 3, 64, 64), dtype=np.uint8)
+    inputs[iname][:] = x
+    assert parade.run(inputs, outputs) is True
+    want, _, _ = run_net(spec, x, port)
+    assert_same(outputs[oname].reshape(want.shape).view(np.uint32), want.view(np.uint32), "art.Parade.run")
+    parade.forward()                                       # the device-resident run of the same data
+    # the reference's argument checks
+    with pytest.raises(ValueError, match="input shape not match"):
+        parade.run({iname: x[:1]}, outputs)
+    with pytest.raises(ValueError, match="input dtype not match"):
+        parade.run({iname: x.astype(np.float32)}, outputs)
+    with pytest.raises(ValueError, match="output dtype not match"):
+        parade.run(inputs, {oname: outputs[oname].astype(np.float64)})
+    with pytest.raises(ValueError, match="some output not given"):
+        parade.run(inputs, {})
+    parade.close()
+
+    # reshape: another batch and image size; every later shape follows
+    def build(h, w):
+        b = nets.SpecBuilder(77, (3, h, w), True)
+        t = b.conv("input", 32, 3, 2, 1)
+        t = b.conv(t, 48, 3, 1, 1)
+        t = b.pool(t, nets.POOL_MAX, 2, 2, 0)
+        return b.finish("reshape-net", t)
+
+    small, large = build(16, 16), build(24, 20)
+    engine.write_engine(small, path, batch=2)
+    parade = art.load_parade(path, ctx)
+    (iname,), (oname,) = parade.get_input_names(), parade.get_output_names()
+    assert parade.reshape({"no such input": [1, 3, 8, 8]}) is False
+    assert parade.reshape({iname: [3, 3, 24, 20]}) is True
+    assert parade.input_shapes() == {iname: [3, 3, 24, 20]} and parade.output_shapes() == {oname: [3, 48, 6, 5]}
+    inputs, outputs = art.get_empty_io(parade)
+    x = np.random.default_rng(6).integers(0, 256, (3, 3, 24, 20), dtype=np.uint8)
+    inputs[iname][:] = x
+    parade.run(inputs, outputs)
+    want, _, _ = run_net(large, x, port)
+    assert_same(outputs[oname].reshape(want.shape).view(np.uint32), want.view(np.uint32), "art.Parade.run after reshape")
+    parade.close()
