@@ -127,7 +127,9 @@ B200_API void b200_get_quant_scale(float x, int bits, uint32_t *mult, int8_t *sh
  *   B200_IGEMM_EPI_CONST=0                   never use the uniform-shift epilogue (per-channel constants as kernel parameters)
  * and by b200_case_prepare:
  *   B200_CASE_ZIGZAG=0                       every op walks its tiles first to last (default: each op walks against the
- *                                            direction of the op that wrote its input, to start on what is still in L2) */
+ *                                            direction of the op that wrote its input, to start on what is still in L2)
+ *   B200_CASE_PREFETCH=0                     no L2 prefetch of the next conv's weights while a conv runs (default: every
+ *                                            tensor-core conv of a case asks for the following one's repacked weights) */
 /* Activation type.  B200_ACT_S8 is the reference's dtINT8 path -- op_conv_2d_i8xi8_run
  * (art/modules/quant/src/op/conv_2d_int8_impl.c:34-174), dispatched on the dtype of input 0
  * (conv_2d.c:114-142): activations, weights and outputs are int8, there are no zero points

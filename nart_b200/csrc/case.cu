@@ -488,6 +488,27 @@ int b200_case_prepare(b200_case_t *cs, int32_t max_batch)
             dir[op.out] = rev;
         }
     }
+    // Every tensor-core conv names the weights of the next one, so that they are on their way into L2 while it
+    // runs (B200_CASE_PREFETCH=0 turns that off).
+    {
+        const char *e = getenv("B200_CASE_PREFETCH");
+        const bool on = !(e && atoi(e) == 0);
+        ConvIgemmPlan *prev = nullptr;
+        for (auto &op : cs->ops) {
+            if (op.skipped || op.kind != OpKind::Conv || !op.conv->igemm)
+                continue;
+            if (prev) {
+                const uint8_t *w = nullptr;
+                size_t bytes = 0;
+                if (on)
+                    conv_igemm_weights(op.conv->igemm, &w, &bytes);
+                conv_igemm_set_next_readonly(prev, w, bytes);
+            }
+            prev = op.conv->igemm;
+        }
+        if (prev)
+            conv_igemm_set_next_readonly(prev, nullptr, 0);
+    }
     cs->prepared = true;
     return B200_OK;
 }

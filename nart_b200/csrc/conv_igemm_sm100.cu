@@ -126,6 +126,11 @@ struct IgemmArgs {
     // 1: the M tiles are visited from the last image / row / column tile down to the first, so that a layer
     // starts on the part of its input that the layer before wrote last (and that still sits in L2)
     int rev;
+    // Read-only bytes the launch after this one starts on (the next layer's repacked weights): every CTA asks
+    // for its slice to be brought into L2 while this layer runs, so that the next launch's first weight loads
+    // do not all miss at once.  nullptr / 0: none.
+    const uint8_t *next_ro;
+    uint32_t next_ro_bytes;
     // CTA pair (MODE 3): two CTAs of a cluster share every MMA (tcgen05 cta_group::2, M = 256): CTA r of the
     // pair owns M tile 2 * pm + r of pair tile pm and loads that tile's activations and half r of the
     // weight tile; the pair tiles are walked as (nt fastest, pm) with the digits step_nt, step_pm of the
@@ -748,6 +753,17 @@ __global__ void __launch_bounds__((MODE == 1 || MODE == 2) ? kThreads2 : kThread
         cluster_sync_all();     // the peer's barriers are initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+
+    if (threadIdx.x == 2 * 32 && g.next_ro_bytes != 0) {
+        // this CTA's slice of the next launch's read-only operand, in 16-byte granules
+        const uint32_t granules = g.next_ro_bytes >> 4;
+        const uint32_t per = (granules + gridDim.x - 1) / gridDim.x;
+        const uint32_t first = blockIdx.x * per;
+        if (first < granules) {
+            const uint32_t cnt = min(per, granules - first);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(g.next_ro + ((size_t)first << 4)), "r"(cnt << 4) : "memory");
+        }
+    }
 
     const int m_tiles = g.tiles_w * g.tiles_h * g.tiles_n;
     // the tile sequence of this CTA: tile0, tile0 + tstride, ...  (a CTA pair walks pair tiles together)
@@ -1411,6 +1427,9 @@ struct ConvIgemmPlan {
     uint8_t *row_cls_dev = nullptr, *col_cls_dev = nullptr;
     // uniform-shift epilogue (IgemmArgs::epi_const)
     int rev = 0;                    // reversed tile traversal (conv_igemm_set_reverse)
+    const uint8_t *next_ro = nullptr;   // what the next launch reads first (conv_igemm_set_next_readonly)
+    uint32_t next_ro_bytes = 0;
+    size_t w_bytes = 0;             // size of w_dev
     int epi_const = 0, ushift = 0;
     long long rnd = 0;
     int32_t *off32_dev = nullptr;   // [n_cls][kpad]
@@ -1762,6 +1781,7 @@ int conv_igemm_create(
         B200_CUDA_TRY(cudaMemcpy(*dst, src, bytes, cudaMemcpyHostToDevice));
         return B200_OK;
     };
+    p->w_bytes = wp.size();
     int rc = up(wp.data(), wp.size(), (void **)&p->w_dev);
     if (rc == B200_OK) rc = up(off.data(), off.size() * 8, (void **)&p->off_dev);
     if (rc == B200_OK) rc = up(off32_all.data(), off32_all.size() * 4, (void **)&p->off32_dev);
@@ -1825,6 +1845,26 @@ void conv_igemm_set_reverse(ConvIgemmPlan *p, int reverse)
     if (p->rev != (reverse ? 1 : 0)) {
         p->rev = reverse ? 1 : 0;
         p->last_n = -1;        // cached launch configurations carry the old direction
+        p->saved.clear();
+    }
+}
+
+void conv_igemm_weights(const ConvIgemmPlan *p, const uint8_t **ptr, size_t *bytes)
+{
+    *ptr = reinterpret_cast<const uint8_t *>(p->w_dev);
+    *bytes = p->w_bytes;
+}
+
+void conv_igemm_set_next_readonly(ConvIgemmPlan *p, const uint8_t *ptr, size_t bytes)
+{
+    // 16-byte granules (the bulk prefetch's unit); anything beyond 64 MiB would only evict what the layers between need
+    if (((uintptr_t)ptr & 15) != 0 || bytes > (64u << 20))
+        ptr = nullptr;
+    const uint32_t b = ptr ? (uint32_t)(bytes & ~(size_t)15) : 0u;
+    if (p->next_ro != ptr || p->next_ro_bytes != b) {
+        p->next_ro = ptr;
+        p->next_ro_bytes = b;
+        p->last_n = -1;
         p->saved.clear();
     }
 }
@@ -1918,6 +1958,7 @@ static int build_launch(ConvIgemmPlan *p, const uint8_t *x, int n, uint8_t *y, i
     a.rnd_lo = (int)(uint32_t)(unsigned long long)p->rnd; a.rnd_hi = (int)(p->rnd >> 32);
     a.off32 = p->off32_dev;
     a.rev = p->rev;
+    a.next_ro = p->next_ro; a.next_ro_bytes = p->next_ro_bytes;
     a.use_tma_store = (g.k % 16 == 0) ? 1 : 0;
     a.y = y;
     a.res = res;

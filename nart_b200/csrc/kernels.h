@@ -138,6 +138,10 @@ void conv_igemm_destroy(ConvIgemmPlan *plan);
 // Direction in which a launch walks its output tiles: 0 first to last, 1 last to first.  Results do not
 // depend on it; a consumer that walks against its producer's direction starts on data still in L2.
 void conv_igemm_set_reverse(ConvIgemmPlan *plan, int reverse);
+// The repacked weights of a plan (device pointer, bytes), and the read-only operand of the launch that follows this
+// plan's: the kernel asks for it to be brought into L2 while it runs (nullptr: none).
+void conv_igemm_weights(const ConvIgemmPlan *plan, const uint8_t **ptr, size_t *bytes);
+void conv_igemm_set_next_readonly(ConvIgemmPlan *plan, const uint8_t *ptr, size_t bytes);
 // One line of text naming the plan's tiling and kernel variant.
 void conv_igemm_describe(const ConvIgemmPlan *plan, char *buf, size_t len);
 // Per-process / per-device set-up of the tensor-core kernels (driver entry point, shared-memory
