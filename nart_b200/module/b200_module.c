@@ -58,6 +58,9 @@ typedef struct b200_mem_t {
     void *nchw_tmp;     /* device staging for cpu_data() of an NHWC tensor, kept between calls */
     size_t nchw_tmp_sz;
     bool gpu_updated;   /* the device copy is the current one */
+    bool upload_pending; /* an upload from the host mirror may still be reading it (see b200_mem_data) */
+    bool host_current;  /* the host mirror holds what the device copy holds (set by an upload or a download, cleared
+                         * when an op writes the device copy): b200_mem_cpu_data then has nothing to fetch */
     bool nhwc;          /* the device copy is NHWC uint8 with the dims below (set by the op that wrote it) */
     int n, c, h, w;
 } b200_mem_t;
@@ -131,9 +134,13 @@ static void host_mirror(b200_mem_t *m)
 static void *b200_mem_data(b200_mem_t *m)
 {
     if (!m->gpu_updated && m->host) {
+        /* Asynchronous, from the pinned mirror, on the stream every op of this module runs on: the ops that
+         * follow are queued while the copy is under way instead of after it.  The host gets at the mirror
+         * only through b200_mem_cpu_data, which waits for a pending upload before it hands the pointer out. */
         B200_CALL(b200_memcpy_h2d(m->dev, m->host, m->sz, NULL));
-        B200_CALL(b200_stream_synchronize(NULL));
+        m->upload_pending = true;
         m->gpu_updated = true;
+        m->host_current = true;
         m->nhwc = false;   /* what the host wrote is in the reference's layout */
     }
     return m->dev;
@@ -141,7 +148,15 @@ static void *b200_mem_data(b200_mem_t *m)
 
 static void *b200_mem_cpu_data(b200_mem_t *m)
 {
+    if (m->upload_pending) {
+        B200_CALL(b200_stream_synchronize(NULL));
+        m->upload_pending = false;
+    }
     host_mirror(m);
+    if (m->gpu_updated && m->host_current) {
+        /* the device copy came from this very mirror and nothing has written it since */
+        m->gpu_updated = false;
+    }
     if (m->gpu_updated) {
         size_t count = (size_t)m->n * m->c * m->h * m->w;
         if (m->nhwc && count <= m->sz && m->c > 1 && m->h * m->w > 1) {
@@ -161,6 +176,7 @@ static void *b200_mem_cpu_data(b200_mem_t *m)
             B200_CALL(b200_stream_synchronize(NULL));
         }
         m->gpu_updated = false;
+        m->host_current = true;
     }
     return m->host;
 }
@@ -279,6 +295,7 @@ static void *output_dev(tensor_t *t, bool nhwc)
     dims_of(t, &m->n, &m->c, &m->h, &m->w);
     m->nhwc = nhwc;
     m->gpu_updated = true;
+    m->host_current = false;
     return m->dev;
 }
 
