@@ -1,6 +1,6 @@
 // Bandwidth-bound uint8 ops around the quantized convolution: quantize / dequantize with the
 // NCHW <-> NHWC transpose fused in, plain layout changes, eltwise SUM (add) and relu.  All are
-// CUDA-core kernels judged against HBM bandwidth: every global access is a full-sector,
+// CUDA-core kernels measured against HBM bandwidth: every global access is a full-sector,
 // coalesced or 16-byte vector access.
 #include "common.cuh"
 #include "kernels.h"
