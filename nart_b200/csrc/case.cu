@@ -90,8 +90,11 @@ struct b200_case {
     std::vector<Graph> graphs;
     // pipelined host runs (b200_case_submit_host): a copy stream, a compute stream, and the events
     // that order them
-    cudaStream_t copy_stream = nullptr, comp_stream = nullptr;
+    cudaStream_t copy_stream = nullptr, comp_stream = nullptr, out_stream = nullptr;
     cudaEvent_t h2d_done = nullptr, after_inputs = nullptr;
+    // the results of a submitted step travel to the host on out_stream, behind comp_done; the output kernels of the
+    // next step wait for d2h_done before they overwrite the device staging buffers
+    cudaEvent_t comp_done = nullptr, d2h_done = nullptr;
     bool submitted = false;
 };
 
@@ -195,6 +198,9 @@ int b200_case_destroy(b200_case_t *cs)
             cudaGraphExecDestroy(gr.exec);
     if (cs->h2d_done) cudaEventDestroy(cs->h2d_done);
     if (cs->after_inputs) cudaEventDestroy(cs->after_inputs);
+    if (cs->comp_done) cudaEventDestroy(cs->comp_done);
+    if (cs->d2h_done) cudaEventDestroy(cs->d2h_done);
+    if (cs->out_stream) cudaStreamDestroy(cs->out_stream);
     if (cs->copy_stream) cudaStreamDestroy(cs->copy_stream);
     if (cs->comp_stream) cudaStreamDestroy(cs->comp_stream);
     delete cs;
@@ -566,6 +572,15 @@ int b200_case_tensor_device_ptr(const b200_case_t *cs, int32_t tensor, void **de
 // phase: 0 = whole run, 1 = input layout kernels only, 2 = ops and outputs only
 static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream, int phase = 0);
 
+// The ops (phase 2) and then the output kernels (phase 3), which stay outside a captured graph: they write the
+// device staging buffers that the previous submitted step's device-to-host copy may still be reading.
+static int run_outputs(b200_case_t *cs, int32_t batch, b200_stream_t stream)
+{
+    if (cs->submitted && cs->d2h_done)
+        B200_CUDA_TRY(cudaStreamWaitEvent(as_stream(stream), cs->d2h_done, 0));
+    return run_eager(cs, batch, stream, 3);
+}
+
 int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
 {
     if (!cs || !cs->prepared)
@@ -586,7 +601,8 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         }
         B200_TRY(run_eager(cs, batch, stream, 1));
         B200_CUDA_TRY(cudaEventRecord(cs->after_inputs, as_stream(stream)));
-        return run_eager(cs, batch, stream, 2);
+        B200_TRY(run_eager(cs, batch, stream, 2));
+        return run_outputs(cs, batch, stream);
     }
     // Graph mode: the first run at a batch size is eager (plans build their tensor maps and scratch
     // then), the second is captured, later ones replay the captured launches back to back.
@@ -606,13 +622,14 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         if (cs->after_inputs)
             B200_CUDA_TRY(cudaEventRecord(cs->after_inputs, cst));
         B200_CUDA_TRY(cudaGraphLaunch(gr->exec, cst));
-        return B200_OK;
+        return run_outputs(cs, batch, stream);
     }
     if (gr->runs_seen++ == 0) {
         B200_TRY(run_eager(cs, batch, stream, 1));
         if (cs->after_inputs)
             B200_CUDA_TRY(cudaEventRecord(cs->after_inputs, cst));
-        return run_eager(cs, batch, stream, 2);
+        B200_TRY(run_eager(cs, batch, stream, 2));
+        return run_outputs(cs, batch, stream);
     }
     B200_TRY(run_eager(cs, batch, stream, 1));
     if (cs->after_inputs)
@@ -628,7 +645,8 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         cs->use_graph = false;   // something on the path cannot be captured: stay eager
         if (rc != B200_OK)
             return rc;
-        return run_eager(cs, batch, stream, 2);
+        B200_TRY(run_eager(cs, batch, stream, 2));
+        return run_outputs(cs, batch, stream);
     }
     ce = cudaGraphInstantiate(&gr->exec, graph, 0);
     cudaGraphDestroy(graph);
@@ -636,10 +654,11 @@ int b200_case_run_device(b200_case_t *cs, int32_t batch, b200_stream_t stream)
         gr->exec = nullptr;
         cudaGetLastError();
         cs->use_graph = false;
-        return run_eager(cs, batch, stream, 2);
+        B200_TRY(run_eager(cs, batch, stream, 2));
+        return run_outputs(cs, batch, stream);
     }
     B200_CUDA_TRY(cudaGraphLaunch(gr->exec, cst));
-    return B200_OK;
+    return run_outputs(cs, batch, stream);
 }
 
 static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream, int phase)
@@ -658,8 +677,9 @@ static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream, int p
         }
         return B200_OK;
     };
+    // phase 0: everything; 1: the input layout kernels; 2: the ops; 3: the output kernels
     for (auto &io : cs->inputs) {
-        if (phase == 2)
+        if (phase >= 2)
             break;
         CaseTensor &t = cs->tensors[io.tensor];
         if (io.is_f32)
@@ -674,6 +694,8 @@ static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream, int p
         return B200_OK;
     for (auto &op : cs->ops) {
         int kind = 0;
+        if (phase == 3)
+            break;
         if (op.skipped)
             continue;
         CaseTensor &to = cs->tensors[op.out];
@@ -706,6 +728,8 @@ static int run_eager(b200_case_t *cs, int32_t batch, b200_stream_t stream, int p
         B200_TRY(mark(kind));
     }
     for (auto &io : cs->outputs) {
+        if (phase == 2)
+            break;
         const CaseTensor &t = cs->tensors[io.tensor];
         if (io.is_f32)
             B200_TRY(b200_dequantize_u8(t.dev, (float *)io.staging, batch, t.c, t.h, t.w, io.alpha, io.zp, 1, stream));
@@ -806,6 +830,9 @@ int b200_case_submit_host(b200_case_t *cs, int32_t batch, const void *const *inp
         B200_CUDA_TRY(cudaStreamCreateWithFlags(&cs->comp_stream, cudaStreamNonBlocking));
         B200_CUDA_TRY(cudaEventCreateWithFlags(&cs->h2d_done, cudaEventDisableTiming));
         B200_CUDA_TRY(cudaEventCreateWithFlags(&cs->after_inputs, cudaEventDisableTiming));
+        B200_CUDA_TRY(cudaStreamCreateWithFlags(&cs->out_stream, cudaStreamNonBlocking));
+        B200_CUDA_TRY(cudaEventCreateWithFlags(&cs->comp_done, cudaEventDisableTiming));
+        B200_CUDA_TRY(cudaEventCreateWithFlags(&cs->d2h_done, cudaEventDisableTiming));
     }
     // the input staging buffer is free again once the previous run's layout kernels have read it
     if (cs->submitted)
@@ -816,9 +843,13 @@ int b200_case_submit_host(b200_case_t *cs, int32_t batch, const void *const *inp
     B200_CUDA_TRY(cudaEventRecord(cs->h2d_done, cs->copy_stream));
     B200_CUDA_TRY(cudaStreamWaitEvent(cs->comp_stream, cs->h2d_done, 0));
     B200_TRY(b200_case_run_device(cs, batch, reinterpret_cast<b200_stream_t>(cs->comp_stream)));
+    // the results leave on a stream of their own, so that the next step's kernels do not queue behind the copy
+    B200_CUDA_TRY(cudaEventRecord(cs->comp_done, cs->comp_stream));
+    B200_CUDA_TRY(cudaStreamWaitEvent(cs->out_stream, cs->comp_done, 0));
     for (size_t i = 0; i < cs->outputs.size(); ++i)
         B200_CUDA_TRY(cudaMemcpyAsync(
-            outputs[i], cs->outputs[i].staging, cs->outputs[i].bytes_per_image * batch, cudaMemcpyDeviceToHost, cs->comp_stream));
+            outputs[i], cs->outputs[i].staging, cs->outputs[i].bytes_per_image * batch, cudaMemcpyDeviceToHost, cs->out_stream));
+    B200_CUDA_TRY(cudaEventRecord(cs->d2h_done, cs->out_stream));
     cs->submitted = true;
     return B200_OK;
 }
@@ -831,6 +862,7 @@ int b200_case_wait(b200_case_t *cs)
         return B200_OK;
     B200_CUDA_TRY(cudaStreamSynchronize(cs->copy_stream));
     B200_CUDA_TRY(cudaStreamSynchronize(cs->comp_stream));
+    B200_CUDA_TRY(cudaStreamSynchronize(cs->out_stream));
     int word = 0;
     B200_TRY(b200_device_status(reinterpret_cast<b200_stream_t>(cs->comp_stream), &word));
     if (word != 0)
