@@ -26,10 +26,15 @@
 //   warps 2..17 epilogue, two groups of 8 warps (two per tensor-memory lane quarter) or, for narrow
 //               channel tiles with a short mainloop, four groups of 4 warps; group i
 //               owns accumulator stage i: tcgen05.ld -> requantize -> pack -> swizzled smem -> TMA store
+//   warp 18     a second MMA-issuing warp in the instantiations for narrow tiles (MODE 1, 2)
 // One accumulator stage per group in tensor memory lets the epilogue of tile i overlap the mainloop
-// of the next tiles and their epilogues (the other groups).  No cluster launch, no multicast.  Every wait is bounded: when one runs out the
-// kernel records a code in the status word, all roles leave their loops, tensor memory is freed
-// and the kernel returns.
+// of the next tiles and their epilogues (the other groups).  MODE 3 runs on clusters of two CTAs that
+// share every MMA (tcgen05 cta_group::2, M = 256), each CTA loading its own operands with plain TMA
+// loads; the other instantiations launch without clusters.  No load is multicast.  Two epilogue forms
+// exist: the 64-bit addend above with per-channel shifts, and a uniform-shift form with two 32-bit
+// constants per channel as kernel parameters (see IgemmArgs::epi_const).  Every wait is bounded:
+// when one runs out the kernel records a code in the status word, all roles leave their loops,
+// tensor memory is freed and the kernel returns.
 #include <cuda.h>
 #include <stdlib.h>
 #include <string.h>
